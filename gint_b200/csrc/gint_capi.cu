@@ -1,0 +1,547 @@
+/*
+ * gint_capi.cu -- host side of libgint_b200.so: program analysis and pre-decoding, the per-device context,
+ * and the launch entry points declared in include/gint_b200.h.
+ *
+ * It replaces the reference's Python executor (gint/host/cuda/executor_impl.py, gint/host/cuda/driver.py):
+ * instead of a device-side descriptor buffer refreshed by a 608-byte host-to-device copy before every launch
+ * (executor_impl.py:66-72), descriptors travel as kernel parameters, so a launch is a single cudaLaunchKernel
+ * with no allocation and no copy and every captured launch in a CUDA graph is self-contained.
+ */
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <string.h>
+
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include "../../include/gint_b200.h"
+#include "gint_types.h"
+#include "gint_opcodes.h"
+#include "gint_variants.h"
+
+using gint::IndirectArgs;
+using gint::IndirectEntry;
+using gint::LaunchArgs;
+
+namespace {
+
+struct OpEffect { int8_t min_depth, net; };
+const OpEffect kEffects[GINT_N_OPCODES] = {
+#define GINT_X_EFF(name, num, md, net) {md, net},
+    GINT_OPCODE_LIST(GINT_X_EFF)
+#undef GINT_X_EFF
+};
+
+bool is_tensor_op(int op)
+{
+    return (op >= OP_LoadGlobal1DF32 && op <= OP_LoadGlobal1DU8) || op == OP_LoadGlobal1DF32Indirect ||
+           op == OP_StoreGlobal1DF32Indirect || (op >= OP_LoadGlobal2DTF32 && op <= OP_AdvanceBase);
+}
+
+/* Static walk (gint/host/analyzer.py:187-238) + pool geometry choice (replaces gint/host/executor.py:131-149). */
+int analyze(const int32_t *code, int n_words, gint_bytecode_stats *st)
+{
+    if (!code || !st || n_words < 0 || (n_words & 1)) return GINT_ERR_INVALID_ARGUMENT;
+    memset(st, 0, sizeof(*st));
+    st->error_index = -1;
+    st->max_reg_idx = -1;
+    int depth = 0, n = 0;
+    bool halted = false;
+    for (int i = 0; i + 1 < n_words; i += 2) {
+        const int op = code[i];
+        if (op == OP_Halt) { halted = true; break; }
+        if (op < 0 || op >= GINT_N_OPCODES) { st->error_index = n; return GINT_ERR_UNKNOWN_OPCODE; }
+        if (depth < kEffects[op].min_depth) { st->error_index = n; return GINT_ERR_STACK_UNDERFLOW; }
+        if (op >= OP_FLoadReg0 && op <= OP_FStoreReg7) {
+            const int r = (op - OP_FLoadReg0) & 7;
+            st->regs_used_mask |= 1 << r;
+            if (r > st->max_reg_idx) st->max_reg_idx = r;
+        }
+        const int post = depth + kEffects[op].net;
+        const int peak = post > depth ? post : depth;
+        if (peak > GINT_MAX_STACK) { st->error_index = n; return GINT_ERR_STACK_OVERFLOW; }
+        if (peak > st->max_stack) st->max_stack = peak;
+        if (peak + st->max_reg_idx + 1 > st->min_pool_size) st->min_pool_size = peak + st->max_reg_idx + 1;
+        depth = post;
+        n++;
+    }
+    st->num_instructions = n;
+    if (!halted) { st->error_index = n; return GINT_ERR_NO_HALT; }
+    /* Register n lives in pool[P-1-n] (gint/kernel/interpreter/state.py:38-41), so P is observable only if stack
+     * and registers overlap. Smallest pool that keeps them apart; otherwise the reference's largest layout. */
+    const int need = st->max_stack + st->max_reg_idx + 1;
+    st->pool_size = need <= 4 ? 4 : need <= 7 ? 7 : 12;
+    return GINT_OK;
+}
+
+uint32_t clamp_lane_bytes(uint32_t operand)
+{
+    uint32_t r = 0;
+    for (int w = 0; w < 4; w++) {
+        uint32_t b = (operand >> (8 * w)) & 0xFFu;
+        r |= (b > 3u ? 3u : b) << (8 * w);
+    }
+    return r;
+}
+
+/* {key, operand} pairs: key = depth-before * N_OPCODES + opcode. Width-lane selectors are clamped to 0..3, which is
+ * what the reference's compare tree computes for any operand (gint/kernel/interpreter/instructions/move.py:58-66). */
+int predecode(const int32_t *code, int n_words, int n_tensors, std::vector<uint2> *out)
+{
+    gint_bytecode_stats st;
+    int rc = analyze(code, n_words, &st);
+    if (rc != GINT_OK) return rc;
+    out->clear();
+    out->reserve((size_t)st.num_instructions + 3);
+    int depth = 0;
+    for (int i = 0; i < st.num_instructions; i++) {
+        const int op = code[2 * i];
+        uint32_t operand = (uint32_t)code[2 * i + 1];
+        if (is_tensor_op(op) && (int)(operand & 15u) >= n_tensors) return GINT_ERR_INVALID_ARGUMENT;
+        if (op == OP_DupBroadcastW) {
+            const int32_t s = (int32_t)operand;
+            operand = s < 0 ? 0u : s > 3 ? 3u : (uint32_t)s;
+        } else if (op == OP_FPermW || op == OP_FShuf2) {
+            operand = clamp_lane_bytes(operand);
+        }
+        out->push_back(make_uint2((uint32_t)(depth * GINT_N_OPCODES + op), operand));
+        depth += kEffects[op].net;
+    }
+    out->push_back(make_uint2((uint32_t)(depth * GINT_N_OPCODES + OP_Halt), 0u));
+    out->push_back(make_uint2(OP_Halt, 0u));  // the interpreter fetches one instruction ahead
+    if (out->size() & 1) out->push_back(make_uint2(OP_Halt, 0u));
+    return GINT_OK;
+}
+
+struct Variant {
+    int P, K;
+    const void *fn;
+    int regs;
+    bool ok;
+};
+
+struct Program {
+    bool live = false;
+    uint2 *code_dev = nullptr;
+    uint32_t n_slots = 0;
+    int n_tensors = 0;
+    gint_tensor_info ti;
+    gint_bytecode_stats st;
+};
+
+}  // namespace
+
+struct gint_ctx {
+    int device = -1;
+    int num_sms = 0;
+    int max_smem_optin = 0;
+    std::mutex mu;
+    std::vector<Program *> programs;
+    std::vector<Variant> direct;
+    Variant indirect{12, 1, nullptr, 0, false};
+    std::string last_error;
+    int opt_tiles_per_warp = 0;
+    int opt_max_blocks = 0;
+    /* scratch for indirect launches */
+    void *ind_dev = nullptr;
+    void *ind_host = nullptr;
+    size_t ind_bytes = 0;
+    cudaEvent_t ind_event = nullptr;
+};
+
+namespace {
+
+int fail(gint_ctx *ctx, int status, const char *what, cudaError_t e = cudaSuccess)
+{
+    if (ctx) {
+        char buf[512];
+        if (e != cudaSuccess) snprintf(buf, sizeof(buf), "%s: %s (%s)", what, cudaGetErrorName(e), cudaGetErrorString(e));
+        else snprintf(buf, sizeof(buf), "%s", what);
+        ctx->last_error = buf;
+    }
+    return status;
+}
+
+struct DeviceGuard {
+    int prev = -1;
+    bool switched = false;
+    explicit DeviceGuard(int dev)
+    {
+        if (cudaGetDevice(&prev) == cudaSuccess && prev != dev) switched = cudaSetDevice(dev) == cudaSuccess;
+    }
+    ~DeviceGuard()
+    {
+        if (switched) cudaSetDevice(prev);
+    }
+};
+
+Program *lookup(gint_ctx *ctx, uint64_t handle)
+{
+    std::lock_guard<std::mutex> lk(ctx->mu);
+    if (handle == 0 || handle > ctx->programs.size()) return nullptr;
+    Program *p = ctx->programs[handle - 1];
+    return (p && p->live) ? p : nullptr;
+}
+
+Variant *find_variant(gint_ctx *ctx, int P, int K)
+{
+    for (auto &v : ctx->direct)
+        if (v.P == P && v.K == K && v.ok) return &v;
+    return nullptr;
+}
+
+struct Geometry {
+    Variant *v;
+    uint32_t smem;
+    uint32_t code_smem;
+    int blocks_per_sm;
+    uint32_t grid;
+};
+
+uint32_t direct_smem(const Program *p, int K, uint32_t *code_smem)
+{
+    const uint32_t cs = (p->n_slots * 8u + 127u) & ~127u;
+    *code_smem = cs;
+    return cs + gint::kTensorInfoSmemBytes + (uint32_t)(gint::kWarpsPerBlock * K) * (uint32_t)sizeof(gint::TileInfo);
+}
+
+int plan_direct(gint_ctx *ctx, const Program *p, uint32_t count, Geometry *g)
+{
+    const int P = p->st.pool_size;
+    const int ks[3] = {4, 2, 1};
+    Geometry best{};
+    bool have = false;
+    for (int K : ks) {
+        if (ctx->opt_tiles_per_warp && K > ctx->opt_tiles_per_warp) continue;  // option = upper bound on K
+        Variant *v = find_variant(ctx, P, K);
+        if (!v) continue;
+        Geometry c{};
+        c.v = v;
+        c.smem = direct_smem(p, K, &c.code_smem);
+        if ((int)c.smem > ctx->max_smem_optin) continue;
+        if (c.smem > 48u * 1024u) {
+            cudaError_t e = cudaFuncSetAttribute(v->fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)c.smem);
+            if (e != cudaSuccess) { cudaGetLastError(); continue; }
+        }
+        int bps = 0;
+        cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&bps, v->fn, gint::kThreadsPerBlock, c.smem);
+        if (e != cudaSuccess || bps < 1) { cudaGetLastError(); continue; }
+        c.blocks_per_sm = bps;
+        const uint64_t groups = ((uint64_t)count + (uint64_t)K - 1) / (uint64_t)K;
+        uint64_t blocks_needed = (groups + gint::kWarpsPerBlock - 1) / gint::kWarpsPerBlock;
+        uint64_t resident = (uint64_t)bps * (uint64_t)ctx->num_sms;
+        if (ctx->opt_max_blocks > 0 && (uint64_t)ctx->opt_max_blocks < resident) resident = (uint64_t)ctx->opt_max_blocks;
+        c.grid = (uint32_t)(blocks_needed < resident ? blocks_needed : resident);
+        if (c.grid == 0) c.grid = 1;
+        if (!have) { best = c; have = true; }
+        /* take the widest K that still fills the machine with at least one group per resident warp */
+        if (blocks_needed >= resident || ctx->opt_tiles_per_warp) { best = c; break; }
+        best = c;  // fewer groups than warps: prefer the narrower variant (more warps busy)
+    }
+    if (!have) return fail(ctx, GINT_ERR_TOO_LARGE, "no kernel variant fits this program (shared memory)");
+    *g = best;
+    return GINT_OK;
+}
+
+int launch_direct(gint_ctx *ctx, uint64_t handle, const uint64_t *base_ptrs, int n_tensors, uint32_t first, uint32_t count,
+                  void *stream)
+{
+    if (!ctx || (!base_ptrs && n_tensors > 0)) return fail(ctx, GINT_ERR_INVALID_ARGUMENT, "null argument");
+    Program *p = lookup(ctx, handle);
+    if (!p) return fail(ctx, GINT_ERR_BAD_HANDLE, "unknown program handle");
+    if (n_tensors != p->n_tensors) return fail(ctx, GINT_ERR_ARG_COUNT, "number of arguments does not match the program");
+    if (count == 0) return GINT_OK;
+    if ((uint64_t)first + (uint64_t)count > 0xFFFFFFFFull) return fail(ctx, GINT_ERR_TOO_LARGE, "logical program range overflows 32 bits");
+    DeviceGuard guard(ctx->device);
+    Geometry g;
+    int rc = plan_direct(ctx, p, count, &g);
+    if (rc != GINT_OK) return rc;
+    LaunchArgs a;
+    a.code = p->code_dev;
+    a.n_slots = p->n_slots;
+    a.n_tensors = (uint32_t)p->n_tensors;
+    a.first = first;
+    a.end = first + count;
+    a.code_smem_bytes = g.code_smem;
+    a.reserved = 0;
+    a.ti = p->ti;
+    for (int i = 0; i < n_tensors; i++) a.ti.base_ptr[i] = (int64_t)base_ptrs[i];
+    void *args[1] = {&a};
+    cudaError_t e = cudaLaunchKernel(g.v->fn, dim3(g.grid), dim3(gint::kThreadsPerBlock), args, g.smem, (cudaStream_t)stream);
+    if (e != cudaSuccess) return fail(ctx, GINT_ERR_CUDA, "cudaLaunchKernel", e);
+    return GINT_OK;
+}
+
+}  // namespace
+
+/* ================================================================================================ */
+
+extern "C" {
+
+int gint_version(void) { return 100; }
+
+const char *gint_status_string(int status)
+{
+    switch (status) {
+    case GINT_OK: return "ok";
+    case GINT_ERR_INVALID_ARGUMENT: return "invalid argument";
+    case GINT_ERR_UNKNOWN_OPCODE: return "unknown opcode";
+    case GINT_ERR_STACK_UNDERFLOW: return "stack underflow";
+    case GINT_ERR_STACK_OVERFLOW: return "stack overflow";
+    case GINT_ERR_NO_HALT: return "program is not terminated by Halt";
+    case GINT_ERR_BAD_HANDLE: return "bad program handle";
+    case GINT_ERR_ARG_COUNT: return "number of arguments does not match the program";
+    case GINT_ERR_CUDA: return "CUDA error";
+    case GINT_ERR_NO_DEVICE: return "no usable device or kernel image";
+    case GINT_ERR_TOO_LARGE: return "program or batch too large";
+    case GINT_ERR_OUT_OF_MEMORY: return "out of memory";
+    }
+    return "unknown status";
+}
+
+int gint_sizeof_tensor_info(void) { return (int)sizeof(gint_tensor_info); }
+
+int gint_analyze(const int32_t *code, int n_words, gint_bytecode_stats *out) { return analyze(code, n_words, out); }
+
+int gint_predecode(const int32_t *code, int n_words, uint32_t *out_keys, int max_keys)
+{
+    std::vector<uint2> pre;
+    int rc = predecode(code, n_words, GINT_MAX_TENSORS, &pre);
+    if (rc != GINT_OK) return rc;
+    gint_bytecode_stats st;
+    analyze(code, n_words, &st);
+    const int n = st.num_instructions + 1;
+    if (out_keys) {
+        if (max_keys < n) return GINT_ERR_INVALID_ARGUMENT;
+        for (int i = 0; i < n; i++) out_keys[i] = pre[(size_t)i].x;
+    }
+    return n;
+}
+
+int gint_create(int device, gint_ctx **out)
+{
+    if (!out) return GINT_ERR_INVALID_ARGUMENT;
+    *out = nullptr;
+    int count = 0;
+    if (cudaGetDeviceCount(&count) != cudaSuccess || device < 0 || device >= count) {
+        cudaGetLastError();
+        return GINT_ERR_NO_DEVICE;
+    }
+    DeviceGuard guard(device);
+    cudaDeviceProp prop;
+    if (cudaGetDeviceProperties(&prop, device) != cudaSuccess) { cudaGetLastError(); return GINT_ERR_NO_DEVICE; }
+    gint_ctx *ctx = new gint_ctx();
+    ctx->device = device;
+    ctx->num_sms = prop.multiProcessorCount;
+    ctx->max_smem_optin = (int)prop.sharedMemPerBlockOptin;
+#define GINT_X_VAR(P, K) ctx->direct.push_back(Variant{P, K, gint_kernel_direct_##P##_##K(), 0, false});
+    GINT_DIRECT_VARIANTS(GINT_X_VAR)
+#undef GINT_X_VAR
+    ctx->indirect.fn = gint_kernel_indirect_12();
+    int usable = 0;
+    for (auto &v : ctx->direct) {
+        cudaFuncAttributes attr;
+        cudaError_t e = cudaFuncGetAttributes(&attr, v.fn);
+        if (e == cudaSuccess) { v.regs = attr.numRegs; v.ok = true; usable++; }
+        else cudaGetLastError();
+    }
+    {
+        cudaFuncAttributes attr;
+        if (cudaFuncGetAttributes(&attr, ctx->indirect.fn) == cudaSuccess) { ctx->indirect.regs = attr.numRegs; ctx->indirect.ok = true; }
+        else cudaGetLastError();
+    }
+    if (usable == 0) {  // the library carries sm_100a code only
+        delete ctx;
+        return GINT_ERR_NO_DEVICE;
+    }
+    *out = ctx;
+    return GINT_OK;
+}
+
+void gint_destroy(gint_ctx *ctx)
+{
+    if (!ctx) return;
+    {
+        DeviceGuard guard(ctx->device);
+        for (Program *p : ctx->programs) {
+            if (p) {
+                if (p->code_dev) cudaFree(p->code_dev);
+                delete p;
+            }
+        }
+        if (ctx->ind_dev) cudaFree(ctx->ind_dev);
+        if (ctx->ind_host) cudaFreeHost(ctx->ind_host);
+        if (ctx->ind_event) cudaEventDestroy(ctx->ind_event);
+    }
+    delete ctx;
+}
+
+const char *gint_last_error(gint_ctx *ctx) { return ctx ? ctx->last_error.c_str() : "no context"; }
+
+int gint_program_create(gint_ctx *ctx, const int32_t *code, int n_words, const gint_tensor_info *ti, int n_tensors,
+                        uint64_t *out_handle)
+{
+    if (!ctx || !code || !out_handle || (!ti && n_tensors > 0)) return fail(ctx, GINT_ERR_INVALID_ARGUMENT, "null argument");
+    if (n_tensors < 0 || n_tensors > GINT_MAX_TENSORS) return fail(ctx, GINT_ERR_INVALID_ARGUMENT, "at most 8 tensors");
+    std::vector<uint2> pre;
+    int rc = predecode(code, n_words, n_tensors, &pre);
+    if (rc != GINT_OK) return fail(ctx, rc, gint_status_string(rc));
+    Program *p = new Program();
+    analyze(code, n_words, &p->st);
+    p->n_tensors = n_tensors;
+    p->n_slots = (uint32_t)pre.size();
+    memset(&p->ti, 0, sizeof(p->ti));
+    if (ti) p->ti = *ti;
+    for (int t = 0; t < GINT_MAX_TENSORS; t++) p->ti.base_ptr[t] = 0;
+    {
+        DeviceGuard guard(ctx->device);
+        cudaError_t e = cudaMalloc(&p->code_dev, pre.size() * sizeof(uint2));
+        if (e != cudaSuccess) { delete p; return fail(ctx, GINT_ERR_OUT_OF_MEMORY, "cudaMalloc(program)", e); }
+        e = cudaMemcpy(p->code_dev, pre.data(), pre.size() * sizeof(uint2), cudaMemcpyHostToDevice);
+        if (e != cudaSuccess) { cudaFree(p->code_dev); delete p; return fail(ctx, GINT_ERR_CUDA, "cudaMemcpy(program)", e); }
+    }
+    p->live = true;
+    std::lock_guard<std::mutex> lk(ctx->mu);
+    ctx->programs.push_back(p);
+    *out_handle = (uint64_t)ctx->programs.size();
+    return GINT_OK;
+}
+
+int gint_program_destroy(gint_ctx *ctx, uint64_t handle)
+{
+    if (!ctx) return GINT_ERR_INVALID_ARGUMENT;
+    Program *p = nullptr;
+    {
+        std::lock_guard<std::mutex> lk(ctx->mu);
+        if (handle == 0 || handle > ctx->programs.size() || !ctx->programs[handle - 1]) return fail(ctx, GINT_ERR_BAD_HANDLE, "unknown program handle");
+        p = ctx->programs[handle - 1];
+        ctx->programs[handle - 1] = nullptr;
+    }
+    DeviceGuard guard(ctx->device);
+    /* the program may still be running on some stream: cudaFree waits for the device */
+    if (p->code_dev) cudaFree(p->code_dev);
+    delete p;
+    return GINT_OK;
+}
+
+int gint_program_launch_info(gint_ctx *ctx, uint64_t handle, uint32_t grid_dim, gint_launch_info *out)
+{
+    if (!ctx || !out) return fail(ctx, GINT_ERR_INVALID_ARGUMENT, "null argument");
+    Program *p = lookup(ctx, handle);
+    if (!p) return fail(ctx, GINT_ERR_BAD_HANDLE, "unknown program handle");
+    DeviceGuard guard(ctx->device);
+    Geometry g;
+    int rc = plan_direct(ctx, p, grid_dim ? grid_dim : 1, &g);
+    if (rc != GINT_OK) return rc;
+    memset(out, 0, sizeof(*out));
+    out->pool_size = g.v->P;
+    out->tiles_per_warp = g.v->K;
+    out->warps_per_block = gint::kWarpsPerBlock;
+    out->grid_blocks = (int32_t)g.grid;
+    out->smem_bytes = (int32_t)g.smem;
+    out->regs_per_thread = g.v->regs;
+    out->blocks_per_sm = g.blocks_per_sm;
+    out->num_sms = ctx->num_sms;
+    return GINT_OK;
+}
+
+int gint_execute(gint_ctx *ctx, uint64_t handle, const uint64_t *base_ptrs, int n_tensors, uint32_t grid_dim, void *cuda_stream)
+{
+    return launch_direct(ctx, handle, base_ptrs, n_tensors, 0u, grid_dim, cuda_stream);
+}
+
+int gint_execute_range(gint_ctx *ctx, uint64_t handle, const uint64_t *base_ptrs, int n_tensors, uint32_t first, uint32_t count,
+                       void *cuda_stream)
+{
+    return launch_direct(ctx, handle, base_ptrs, n_tensors, first, count, cuda_stream);
+}
+
+int gint_execute_indirect(gint_ctx *ctx, const uint64_t *handles, int n_programs, const uint64_t *base_ptrs, const int32_t *indices,
+                          uint32_t grid_dim, void *cuda_stream)
+{
+    if (!ctx || !handles || !base_ptrs || !indices || n_programs <= 0) return fail(ctx, GINT_ERR_INVALID_ARGUMENT, "null argument");
+    if (grid_dim == 0) return GINT_OK;
+    if (!ctx->indirect.ok) return fail(ctx, GINT_ERR_NO_DEVICE, "indirect kernel image not usable on this device");
+    std::vector<Program *> progs((size_t)n_programs);
+    int max_tensors = 0;
+    for (int i = 0; i < n_programs; i++) {
+        progs[(size_t)i] = lookup(ctx, handles[i]);
+        if (!progs[(size_t)i]) return fail(ctx, GINT_ERR_BAD_HANDLE, "unknown program handle");
+        if (progs[(size_t)i]->n_tensors > max_tensors) max_tensors = progs[(size_t)i]->n_tensors;
+    }
+    for (uint32_t i = 0; i < grid_dim; i++)
+        if (indices[i] < 0 || indices[i] >= n_programs) return fail(ctx, GINT_ERR_INVALID_ARGUMENT, "program index out of range");
+
+    DeviceGuard guard(ctx->device);
+    cudaStream_t stream = (cudaStream_t)cuda_stream;
+    /* scratch layout: [n_programs x gint_tensor_info | grid_dim x IndirectEntry] */
+    const size_t ti_bytes = (size_t)n_programs * sizeof(gint_tensor_info);
+    const size_t need = ti_bytes + (size_t)grid_dim * sizeof(IndirectEntry);
+    if (need > ctx->ind_bytes) {
+        if (ctx->ind_event) cudaEventSynchronize(ctx->ind_event);
+        if (ctx->ind_dev) { cudaFree(ctx->ind_dev); ctx->ind_dev = nullptr; }
+        if (ctx->ind_host) { cudaFreeHost(ctx->ind_host); ctx->ind_host = nullptr; }
+        ctx->ind_bytes = 0;
+        const size_t cap = need < 65536 ? 65536 : need * 2;
+        cudaError_t e = cudaMalloc(&ctx->ind_dev, cap);
+        if (e != cudaSuccess) return fail(ctx, GINT_ERR_OUT_OF_MEMORY, "cudaMalloc(indirect scratch)", e);
+        e = cudaMallocHost(&ctx->ind_host, cap);
+        if (e != cudaSuccess) { cudaFree(ctx->ind_dev); ctx->ind_dev = nullptr; return fail(ctx, GINT_ERR_OUT_OF_MEMORY, "cudaMallocHost(indirect scratch)", e); }
+        ctx->ind_bytes = cap;
+    }
+    if (!ctx->ind_event) {
+        cudaError_t e = cudaEventCreateWithFlags(&ctx->ind_event, cudaEventDisableTiming);
+        if (e != cudaSuccess) return fail(ctx, GINT_ERR_CUDA, "cudaEventCreate", e);
+    } else {
+        cudaEventSynchronize(ctx->ind_event);  // the previous launch's upload has left the staging buffer
+    }
+    gint_tensor_info *h_ti = (gint_tensor_info *)ctx->ind_host;
+    IndirectEntry *h_tab = (IndirectEntry *)((char *)ctx->ind_host + ti_bytes);
+    const gint_tensor_info *d_ti = (const gint_tensor_info *)ctx->ind_dev;
+    for (int i = 0; i < n_programs; i++) {
+        h_ti[i] = progs[(size_t)i]->ti;
+        for (int t = 0; t < progs[(size_t)i]->n_tensors; t++) h_ti[i].base_ptr[t] = (int64_t)base_ptrs[(size_t)i * GINT_MAX_TENSORS + (size_t)t];
+    }
+    for (uint32_t i = 0; i < grid_dim; i++) {
+        h_tab[i].code = progs[(size_t)indices[i]]->code_dev;
+        h_tab[i].ti = d_ti + indices[i];
+    }
+    cudaError_t e = cudaMemcpyAsync(ctx->ind_dev, ctx->ind_host, need, cudaMemcpyHostToDevice, stream);
+    if (e != cudaSuccess) return fail(ctx, GINT_ERR_CUDA, "cudaMemcpyAsync(indirect tables)", e);
+    cudaEventRecord(ctx->ind_event, stream);
+
+    IndirectArgs a;
+    a.table = (const IndirectEntry *)((const char *)ctx->ind_dev + ti_bytes);
+    a.n_tensors = (uint32_t)max_tensors;
+    a.grid_dim = grid_dim;
+    const uint32_t smem = (uint32_t)(gint::kWarpsPerBlock * sizeof(gint::TileInfo));
+    int bps = 0;
+    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&bps, ctx->indirect.fn, gint::kThreadsPerBlock, smem);
+    if (e != cudaSuccess || bps < 1) return fail(ctx, GINT_ERR_CUDA, "occupancy query (indirect)", e);
+    uint64_t blocks = ((uint64_t)grid_dim + gint::kWarpsPerBlock - 1) / gint::kWarpsPerBlock;
+    const uint64_t resident = (uint64_t)bps * (uint64_t)ctx->num_sms;
+    if (blocks > resident) blocks = resident;
+    void *args[1] = {&a};
+    e = cudaLaunchKernel(ctx->indirect.fn, dim3((unsigned)blocks), dim3(gint::kThreadsPerBlock), args, smem, stream);
+    if (e != cudaSuccess) return fail(ctx, GINT_ERR_CUDA, "cudaLaunchKernel(indirect)", e);
+    return GINT_OK;
+}
+
+int gint_set_option(gint_ctx *ctx, const char *name, int value)
+{
+    if (!ctx || !name) return GINT_ERR_INVALID_ARGUMENT;
+    if (strcmp(name, "tiles_per_warp") == 0) {
+        if (value != 0 && value != 1 && value != 2 && value != 4) return fail(ctx, GINT_ERR_INVALID_ARGUMENT, "tiles_per_warp must be 0, 1, 2 or 4");
+        ctx->opt_tiles_per_warp = value;
+        return GINT_OK;
+    }
+    if (strcmp(name, "max_blocks") == 0) {
+        ctx->opt_max_blocks = value < 0 ? 0 : value;
+        return GINT_OK;
+    }
+    return fail(ctx, GINT_ERR_INVALID_ARGUMENT, "unknown option");
+}
+
+}  // extern "C"

@@ -1,0 +1,5 @@
+// Interpreter kernel for a pool of 12 slots, 2 logical program(s) per warp (see gint_interp.cuh).
+#include "gint_interp.cuh"
+#include "gint_variants.h"
+template __global__ void gint::geval_direct<12, 2>(const __grid_constant__ gint::LaunchArgs);
+extern "C" const void *gint_kernel_direct_12_2(void) { return reinterpret_cast<const void *>(&gint::geval_direct<12, 2>); }

@@ -1,0 +1,699 @@
+/*
+ * gint_interp.cuh -- the gint stack-machine interpreter as hand-written CUDA C++ for sm_100a.
+ *
+ * What it replaces: the reference's llvmlite-generated kernels geval_s7 / geval_l12
+ * (gint/kernel/interpreter/main.py:171-294 and everything under gint/kernel/interpreter/instructions/).
+ * Semantics are kept per opcode; the execution strategy is new:
+ *
+ *   - The program is pre-decoded on the host into {dispatch key, operand} pairs, where the key already
+ *     combines the opcode with the (statically known) stack depth, and is staged ONCE per thread block into
+ *     shared memory. Every warp reads it with warp-uniform addresses, so dispatch never diverges. The
+ *     reference re-reads opcode and operand from global memory in every warp (instruction.py:19-36).
+ *   - The operand stack and the virtual registers live in registers: every handler is instantiated per stack
+ *     depth, so all pool indices are compile-time constants (the reference gets the same effect by cloning
+ *     its dispatch block per depth, main.py:201-257).
+ *   - One warp interprets K logical programs ("tiles") side by side (K = 1, 2 or 4): one fetch/decode/branch
+ *     is amortised over K x 128 values and K independent memory streams are in flight per warp.
+ *   - The four width lanes of a slot are held as two packed f32x2 registers; add/sub/mul/fma use the
+ *     Blackwell packed-f32x2 instructions, halving FP issue.
+ *   - Tile loads/stores take a 128-bit path when the descriptor allows it (2DW rows) and an unpredicated
+ *     4 x 128-byte coalesced path for full unit-stride 1-D tiles.
+ *   - The grid is persistent: blocks loop over groups of K logical programs.
+ *
+ * Tensor cores are not used: none of the opcodes is a contraction.
+ */
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/gint_b200.h"
+#include "gint_opcodes.h"
+#include "gint_types.h"
+
+namespace gint {
+
+/* ------------------------------------------------------------------------------------------------ */
+/* packed f32x2 helpers                                                                              */
+
+struct Slot { u64 a, b; };  // a = width lanes (0,1), b = width lanes (2,3)
+
+__device__ __forceinline__ u64 pack2(float x, float y)
+{
+    u64 r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(x), "f"(y));
+    return r;
+}
+__device__ __forceinline__ void unpack2(u64 v, float &x, float &y)
+{
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(x), "=f"(y) : "l"(v));
+}
+__device__ __forceinline__ u64 add2(u64 x, u64 y)
+{
+    u64 r;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(x), "l"(y));
+    return r;
+}
+__device__ __forceinline__ u64 sub2(u64 x, u64 y)
+{
+    u64 r;
+    asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(x), "l"(y));
+    return r;
+}
+__device__ __forceinline__ u64 mul2(u64 x, u64 y)
+{
+    u64 r;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(x), "l"(y));
+    return r;
+}
+__device__ __forceinline__ u64 fma2(u64 x, u64 y, u64 z)
+{
+    u64 r;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(x), "l"(y), "l"(z));
+    return r;
+}
+__device__ __forceinline__ Slot make_slot(float v0, float v1, float v2, float v3)
+{
+    Slot s;
+    s.a = pack2(v0, v1);
+    s.b = pack2(v2, v3);
+    return s;
+}
+__device__ __forceinline__ void slot_get(const Slot &s, float (&v)[4])
+{
+    unpack2(s.a, v[0], v[1]);
+    unpack2(s.b, v[2], v[3]);
+}
+__device__ __forceinline__ Slot splat(float x)
+{
+    Slot s;
+    s.a = pack2(x, x);
+    s.b = s.a;
+    return s;
+}
+
+/* llvm.maximum / llvm.minimum of the reference (nvptx.py:97-100): NaN if either input is NaN */
+__device__ __forceinline__ float max_nan(float x, float y)
+{
+    float r;
+    asm("max.NaN.f32 %0, %1, %2;" : "=f"(r) : "f"(x), "f"(y));
+    return r;
+}
+__device__ __forceinline__ float min_nan(float x, float y)
+{
+    float r;
+    asm("min.NaN.f32 %0, %1, %2;" : "=f"(r) : "f"(x), "f"(y));
+    return r;
+}
+
+/* ------------------------------------------------------------------------------------------------ */
+/* rarely used, code-heavy math: one out-of-line copy shared by every stack depth                    */
+
+static __device__ __noinline__ float slow_math(int op, float t, float s)
+{
+    switch (op) {
+    case OP_FRem: return fmodf(t, s);
+    case OP_FArcSin: return asinf(t);
+    case OP_FArcCos: return acosf(t);
+    case OP_FArcTan: return atanf(t);
+    case OP_FArcTan2: return atan2f(t, s);
+    case OP_FPow: return powf(t, s);
+    case OP_FErf: return erff(t);
+    case OP_FTan: return __tanf(t);
+    case OP_FLog: return logf(t);
+    case OP_FLog2: return log2f(t);
+    case OP_IDiv: {
+        int a = __float_as_int(t), b = __float_as_int(s);
+        int r = b == 0 ? -1 : (a == INT32_MIN && b == -1) ? INT32_MIN : a / b;
+        return __int_as_float(r);
+    }
+    case OP_IRem: {
+        int a = __float_as_int(t), b = __float_as_int(s);
+        int r = b == 0 ? a : (a == INT32_MIN && b == -1) ? 0 : a % b;
+        return __int_as_float(r);
+    }
+    }
+    return t;
+}
+
+/* ------------------------------------------------------------------------------------------------ */
+/* scalar per-element semantics                                                                      */
+
+template <int OP> __device__ __forceinline__ float scalar_binary(float t, float s, uint32_t operand)
+{
+    if constexpr (OP == OP_FDiv) return __fdiv_rn(t, s);
+    else if constexpr (OP == OP_FRDiv) return __fdiv_rn(s, t);
+    else if constexpr (OP == OP_FGt) return t > s ? 1.0f : 0.0f;
+    else if constexpr (OP == OP_FLt) return t < s ? 1.0f : 0.0f;
+    else if constexpr (OP == OP_FGe) return t >= s ? 1.0f : 0.0f;
+    else if constexpr (OP == OP_FLe) return t <= s ? 1.0f : 0.0f;
+    else if constexpr (OP == OP_FEq) return t == s ? 1.0f : 0.0f;
+    else if constexpr (OP == OP_FNe) return t != s ? 1.0f : 0.0f;  // unordered: true on NaN
+    else if constexpr (OP == OP_FApprox) return fabsf(__fsub_rn(t, s)) < __uint_as_float(operand) ? 1.0f : 0.0f;
+    else if constexpr (OP == OP_IAdd) return __int_as_float(__float_as_int(t) + __float_as_int(s));
+    else if constexpr (OP == OP_IMul) return __int_as_float(__float_as_int(t) * __float_as_int(s));
+    else if constexpr (OP == OP_ISub) return __int_as_float(__float_as_int(t) - __float_as_int(s));
+    else if constexpr (OP == OP_IShl) {
+        uint32_t n = __float_as_uint(s);
+        return __uint_as_float(n >= 32 ? 0u : __float_as_uint(t) << n);
+    } else if constexpr (OP == OP_IShr) {
+        uint32_t n = __float_as_uint(s);
+        return __uint_as_float(n >= 32 ? 0u : __float_as_uint(t) >> n);
+    } else if constexpr (OP == OP_IAnd) return __uint_as_float(__float_as_uint(t) & __float_as_uint(s));
+    else if constexpr (OP == OP_IOr) return __uint_as_float(__float_as_uint(t) | __float_as_uint(s));
+    else if constexpr (OP == OP_IXor) return __uint_as_float(__float_as_uint(t) ^ __float_as_uint(s));
+    else return slow_math(OP, t, s);  // FRem, FArcTan2, FPow, IDiv, IRem
+}
+
+template <int OP> __device__ __forceinline__ float scalar_unary(float t)
+{
+    if constexpr (OP == OP_FSqrt) return __fsqrt_rn(t);
+    else if constexpr (OP == OP_FSin) return __sinf(t);   // the reference maps FSin/FCos/FTan to the fast variants
+    else if constexpr (OP == OP_FCos) return __cosf(t);   // (nvptx.py:108-110)
+    else if constexpr (OP == OP_FExp) return expf(t);
+    else if constexpr (OP == OP_FExp2) return exp2f(t);
+    else if constexpr (OP == OP_FRSqrt) return rsqrtf(t);
+    else if constexpr (OP == OP_FRcp) return __frcp_rn(t);
+    else return slow_math(OP, t, 0.0f);  // FTan, FArcSin, FArcCos, FArcTan, FLog, FLog2, FErf
+}
+
+/* ------------------------------------------------------------------------------------------------ */
+/* memory                                                                                            */
+
+enum { DT_F32 = 0, DT_F16 = 1, DT_BF16 = 2, DT_U8 = 3 };
+enum { LAY_1D = 0, LAY_2DT = 1, LAY_2DW = 2 };
+
+template <int DT> struct ElemSize { static constexpr int value = DT == DT_F32 ? 4 : DT == DT_U8 ? 1 : 2; };
+
+template <int DT> __device__ __forceinline__ float load_elem(const char *p)
+{
+    if constexpr (DT == DT_F32) return *reinterpret_cast<const float *>(p);
+    else if constexpr (DT == DT_F16) return __half2float(*reinterpret_cast<const __half *>(p));
+    else if constexpr (DT == DT_BF16) return __bfloat162float(*reinterpret_cast<const __nv_bfloat16 *>(p));
+    else return (float)*reinterpret_cast<const unsigned char *>(p);
+}
+template <int DT> __device__ __forceinline__ void store_elem(char *p, float v)
+{
+    if constexpr (DT == DT_F32) *reinterpret_cast<float *>(p) = v;
+    else if constexpr (DT == DT_F16) *reinterpret_cast<__half *>(p) = __float2half_rn(v);
+    else if constexpr (DT == DT_BF16) *reinterpret_cast<__nv_bfloat16 *>(p) = __float2bfloat16_rn(v);
+}
+
+/*
+ * One 32 x 4 tile access for one logical program.
+ *   1D  (load_store.py:76-101):   element e = off + lane + 32*w on dim 1, active iff e < shape1
+ *   2DT (load_store.py:104-150):  t = lane + off on dim 1, j = adv + w on dim 2
+ *   2DW (load_store.py:153-158):  t = lane + adv on dim 1, j = off + w on dim 2
+ * Inactive loads give 0.0 (load_store.py:12). off = operand >> 4 (logical), slot = operand & 15.
+ * Index arithmetic is 32-bit, the byte offset is sign-extended to 64 bits, as in the reference's GEPs.
+ */
+template <int LAYOUT, int DT, bool STORE>
+__device__ __forceinline__ void tile_rw(const TileInfo *ti, uint32_t operand, int lane, float (&v)[4])
+{
+    constexpr int ESZ = ElemSize<DT>::value;
+    const int arg = operand & 15;
+    const int off = (int)(operand >> 4);
+    char *base = reinterpret_cast<char *>(ti->ptr[arg]);
+    const int2 s1 = ti->s1[arg];
+
+    if constexpr (LAYOUT == LAY_1D) {
+        const int e = lane + off;
+        if constexpr (DT == DT_F32) {
+            if (s1.y == 1) {  // unit stride: four fully coalesced 128-byte warp accesses
+                float *p = reinterpret_cast<float *>(base) + e;
+                if (off + 128 <= s1.x) {
+#pragma unroll
+                    for (int w = 0; w < 4; w++) {
+                        if constexpr (STORE) p[32 * w] = v[w];
+                        else v[w] = p[32 * w];
+                    }
+                } else {
+#pragma unroll
+                    for (int w = 0; w < 4; w++) {
+                        const bool ok = e + 32 * w < s1.x;
+                        if constexpr (STORE) { if (ok) p[32 * w] = v[w]; }
+                        else v[w] = ok ? p[32 * w] : 0.0f;
+                    }
+                }
+                return;
+            }
+        }
+        char *p = base + (long long)(e * s1.y) * ESZ;
+        const long long pstep = (long long)(s1.y * 32) * ESZ;
+#pragma unroll
+        for (int w = 0; w < 4; w++) {
+            const bool ok = e + 32 * w < s1.x;
+            if constexpr (STORE) { if (ok) store_elem<DT>(p, v[w]); }
+            else v[w] = ok ? load_elem<DT>(p) : 0.0f;
+            p += pstep;
+        }
+    } else {
+        const int2 s2 = ti->s2[arg];
+        const int adv = ti->adv[arg];
+        const int t = LAYOUT == LAY_2DT ? lane + off : lane + adv;
+        const int j0 = LAYOUT == LAY_2DT ? adv : off;
+        const bool tok = t < s1.x;
+        if constexpr (DT == DT_F32 && LAYOUT == LAY_2DW) {
+            // one 128-bit access per thread: rows of 4 consecutive floats, 16-byte aligned
+            if ((ti->flags[arg] & kVecRows) && (j0 & 3) == 0 && j0 + 4 <= s2.x) {
+                float4 *p = reinterpret_cast<float4 *>(base + (long long)(t * s1.y + j0) * 4);
+                if constexpr (STORE) {
+                    if (tok) *p = make_float4(v[0], v[1], v[2], v[3]);
+                } else {
+                    float4 r = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (tok) r = *p;
+                    v[0] = r.x; v[1] = r.y; v[2] = r.z; v[3] = r.w;
+                }
+                return;
+            }
+        }
+        char *p = base + (long long)(t * s1.y + j0 * s2.y) * ESZ;
+        const long long pstep = (long long)s2.y * ESZ;
+#pragma unroll
+        for (int w = 0; w < 4; w++) {
+            const bool ok = tok && (j0 + w < s2.x);
+            if constexpr (STORE) { if (ok) store_elem<DT>(p, v[w]); }
+            else v[w] = ok ? load_elem<DT>(p) : 0.0f;
+            p += pstep;
+        }
+    }
+}
+
+/* gather / scatter of f32 elements by i32 indices taken from the stack (load_store.py:266-288):
+ * active iff idx < shape1 (signed; negative indices are not rejected, as in the reference). */
+template <bool STORE>
+__device__ __forceinline__ void tile_indirect(const TileInfo *ti, uint32_t operand, const float (&idx)[4], float (&v)[4])
+{
+    const int arg = operand & 15;
+    char *base = reinterpret_cast<char *>(ti->ptr[arg]);
+    const int2 s1 = ti->s1[arg];
+#pragma unroll
+    for (int w = 0; w < 4; w++) {
+        const int i = __float_as_int(idx[w]);
+        const bool ok = i < s1.x;
+        float *p = reinterpret_cast<float *>(base + (long long)(i * s1.y) * 4);
+        if constexpr (STORE) { if (ok) *p = v[w]; }
+        else v[w] = ok ? *p : 0.0f;
+    }
+}
+
+/* ------------------------------------------------------------------------------------------------ */
+/* descriptor decode (load_tensor_infos.py:14-54): lane (8k + t) decodes tensor t of tile k           */
+
+template <int K>
+__device__ __forceinline__ void decode_tiles(const gint_tensor_info *__restrict__ ti, int n_tensors, uint32_t first_idx,
+                                             uint32_t end_idx, TileInfo *tiles, int lane)
+{
+    const int k = lane >> 3, t = lane & 7;
+    if (k < K) {
+        const uint32_t bidx = first_idx + (uint32_t)k;
+        u64 ptr = 0;
+        int2 s1 = make_int2(INT32_MIN, 0);  // x < INT32_MIN never holds: every access of this slot is masked
+        int2 s2 = make_int2(INT32_MIN, 0);
+        int flags = 0;
+        if (t < n_tensors && bidx < end_idx) {
+            const int2 bs1 = *reinterpret_cast<const int2 *>(ti->block_shape_stride_1[t]);
+            const int2 bs2 = *reinterpret_cast<const int2 *>(ti->block_shape_stride_2[t]);
+            const int2 gd = *reinterpret_cast<const int2 *>(ti->block_grid_dims[t]);
+            const int2 gs = *reinterpret_cast<const int2 *>(ti->block_grid_steps[t]);
+            uint32_t r = bidx;
+            uint32_t b1 = 0, b2 = 0;
+            if ((uint32_t)gd.x != 1u) { b1 = r % (uint32_t)gd.x; r = r / (uint32_t)gd.x; }
+            if ((uint32_t)gd.y != 1u && r != 0u) { b2 = r % (uint32_t)gd.y; r = r / (uint32_t)gd.y; }
+            uint32_t off = b1 * (uint32_t)gs.x * (uint32_t)bs1.y + b2 * (uint32_t)gs.y * (uint32_t)bs2.y;
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const uint32_t sz = (uint32_t)ti->batch_shape[t][j];
+                if (sz != 1u && r != 0u) {
+                    const uint32_t q = r / sz;
+                    off += (uint32_t)ti->batch_strides[t][j] * (r - q * sz);
+                    r = q;
+                }
+            }
+            ptr = (u64)ti->base_ptr[t] + (u64)off * (u64)(uint32_t)ti->elm_size[t];
+            s1 = make_int2((int)((uint32_t)bs1.x - b1 * (uint32_t)gs.x), bs1.y);
+            s2 = make_int2((int)((uint32_t)bs2.x - b2 * (uint32_t)gs.y), bs2.y);
+            if (bs2.y == 1 && (bs1.y & 3) == 0 && (ptr & 15) == 0) flags |= kVecRows;
+        }
+        TileInfo *o = tiles + k;
+        o->ptr[t] = ptr;
+        o->s1[t] = s1;
+        o->s2[t] = s2;
+        o->adv[t] = 0;
+        o->flags[t] = flags;
+    }
+    __syncwarp();
+}
+
+/* ------------------------------------------------------------------------------------------------ */
+/* one instruction at one stack depth                                                                */
+
+struct Ctx {
+    TileInfo *tiles;  // this warp's K tile descriptors (shared memory)
+    int lane;
+};
+
+template <int OP> struct OpInfo;
+#define GINT_X_INFO(name, num, md, net) \
+    template <> struct OpInfo<num> { static constexpr int min_depth = md; static constexpr int net_effect = net; };
+GINT_OPCODE_LIST(GINT_X_INFO)
+#undef GINT_X_INFO
+
+template <int OP, int SP, int P> __host__ __device__ constexpr bool op_valid()
+{
+    constexpr int limit = P < GINT_MAX_STACK ? P : GINT_MAX_STACK;
+    if (SP < OpInfo<OP>::min_depth) return false;
+    if (SP + OpInfo<OP>::net_effect > limit) return false;
+    if (OP >= OP_FLoadReg0 && OP <= OP_FLoadReg7 && (P - 1 - (OP - OP_FLoadReg0)) < 0) return false;
+    if (OP >= OP_FStoreReg0 && OP <= OP_FStoreReg7 && (P - 1 - (OP - OP_FStoreReg0)) < 0) return false;
+    return true;
+}
+
+/* 4-way select by a 2-bit index; indices are clamped to 0..3 by the host pre-decoder, which makes this equal to
+ * the reference's compare tree (move.py:58-66) */
+__device__ __forceinline__ float sel4(const float (&v)[4], uint32_t i)
+{
+    const float lo = (i & 1u) ? v[1] : v[0];
+    const float hi = (i & 1u) ? v[3] : v[2];
+    return (i & 2u) ? hi : lo;
+}
+
+template <int LAYOUT, int DT, int SP, int P, int K>
+__device__ __forceinline__ void op_load(Slot (&S)[P][K], uint32_t operand, const Ctx &cx)
+{
+#pragma unroll
+    for (int k = 0; k < K; k++) {
+        float v[4];
+        tile_rw<LAYOUT, DT, false>(cx.tiles + k, operand, cx.lane, v);
+        S[SP][k] = make_slot(v[0], v[1], v[2], v[3]);
+    }
+}
+template <int LAYOUT, int DT, int SP, int P, int K>
+__device__ __forceinline__ void op_store(Slot (&S)[P][K], uint32_t operand, const Ctx &cx)
+{
+#pragma unroll
+    for (int k = 0; k < K; k++) {
+        float v[4];
+        slot_get(S[SP - 1][k], v);
+        tile_rw<LAYOUT, DT, true>(cx.tiles + k, operand, cx.lane, v);
+    }
+}
+
+template <int OP, int SP, int P, int K>
+__device__ __forceinline__ void exec(Slot (&S)[P][K], const uint32_t operand, const Ctx &cx)
+{
+    if constexpr (!op_valid<OP, SP, P>()) {
+        return;
+    } else {
+        constexpr int T = SP - 1;  // top of stack
+#define GINT_FOR_K _Pragma("unroll") for (int k = 0; k < K; k++)
+        /* ---- float ALU (arith.py:15-66): binary handlers compute fn(T, S) ---- */
+        if constexpr (OP == OP_Nop) {
+        } else if constexpr (OP == OP_FAdd) {
+            GINT_FOR_K { S[T - 1][k].a = add2(S[T][k].a, S[T - 1][k].a); S[T - 1][k].b = add2(S[T][k].b, S[T - 1][k].b); }
+        } else if constexpr (OP == OP_FMul) {
+            GINT_FOR_K { S[T - 1][k].a = mul2(S[T][k].a, S[T - 1][k].a); S[T - 1][k].b = mul2(S[T][k].b, S[T - 1][k].b); }
+        } else if constexpr (OP == OP_FSub) {
+            GINT_FOR_K { S[T - 1][k].a = sub2(S[T][k].a, S[T - 1][k].a); S[T - 1][k].b = sub2(S[T][k].b, S[T - 1][k].b); }
+        } else if constexpr (OP == OP_FRSub) {
+            GINT_FOR_K { S[T - 1][k].a = sub2(S[T - 1][k].a, S[T][k].a); S[T - 1][k].b = sub2(S[T - 1][k].b, S[T][k].b); }
+        } else if constexpr (OP == OP_FMA) {
+            GINT_FOR_K {
+                S[T - 2][k].a = fma2(S[T][k].a, S[T - 1][k].a, S[T - 2][k].a);
+                S[T - 2][k].b = fma2(S[T][k].b, S[T - 1][k].b, S[T - 2][k].b);
+            }
+        } else if constexpr (OP == OP_FNeg) {
+            GINT_FOR_K { S[T][k].a ^= 0x8000000080000000ull; S[T][k].b ^= 0x8000000080000000ull; }
+        } else if constexpr (OP == OP_FDiv || OP == OP_FRDiv || OP == OP_FRem || (OP >= OP_FGt && OP <= OP_FApprox) ||
+                             OP == OP_FArcTan2 || OP == OP_FPow || (OP >= OP_IAdd && OP <= OP_IXor)) {
+            GINT_FOR_K {
+                float t[4], s[4];
+                slot_get(S[T][k], t);
+                slot_get(S[T - 1][k], s);
+#pragma unroll
+                for (int w = 0; w < 4; w++) s[w] = scalar_binary<OP>(t[w], s[w], operand);
+                S[T - 1][k] = make_slot(s[0], s[1], s[2], s[3]);
+            }
+        } else if constexpr (OP == OP_FSqrt || OP == OP_FSin || OP == OP_FCos || OP == OP_FTan || OP == OP_FArcSin ||
+                             OP == OP_FArcCos || OP == OP_FArcTan || OP == OP_FExp || OP == OP_FExp2 || OP == OP_FLog ||
+                             OP == OP_FLog2 || OP == OP_FRSqrt || OP == OP_FErf || OP == OP_FRcp) {
+            GINT_FOR_K {
+                float t[4];
+                slot_get(S[T][k], t);
+#pragma unroll
+                for (int w = 0; w < 4; w++) t[w] = scalar_unary<OP>(t[w]);
+                S[T][k] = make_slot(t[0], t[1], t[2], t[3]);
+            }
+        }
+        /* ---- immediates (immediate.py:7-61) ---- */
+        else if constexpr (OP == OP_LoadImm) {
+            const Slot v = splat(__uint_as_float(operand));
+            GINT_FOR_K S[SP][k] = v;
+        } else if constexpr (OP == OP_FAddImm) {
+            const u64 imm = pack2(__uint_as_float(operand), __uint_as_float(operand));
+            GINT_FOR_K { S[T][k].a = add2(S[T][k].a, imm); S[T][k].b = add2(S[T][k].b, imm); }
+        } else if constexpr (OP == OP_FMulImm) {
+            const u64 imm = pack2(__uint_as_float(operand), __uint_as_float(operand));
+            GINT_FOR_K { S[T][k].a = mul2(S[T][k].a, imm); S[T][k].b = mul2(S[T][k].b, imm); }
+        } else if constexpr (OP == OP_FMAImm) {  // f16x2: low half = multiplier, high half = addend
+            const float m = __half2float(__ushort_as_half((unsigned short)(operand & 0xFFFFu)));
+            const float c = __half2float(__ushort_as_half((unsigned short)(operand >> 16)));
+            const u64 m2 = pack2(m, m), c2 = pack2(c, c);
+            GINT_FOR_K { S[T][k].a = fma2(S[T][k].a, m2, c2); S[T][k].b = fma2(S[T][k].b, m2, c2); }
+        } else if constexpr (OP == OP_LoadImm4F) {
+            const Slot v = make_slot((float)(signed char)(operand), (float)(signed char)(operand >> 8),
+                                     (float)(signed char)(operand >> 16), (float)(signed char)(operand >> 24));
+            GINT_FOR_K S[SP][k] = v;
+        } else if constexpr (OP == OP_LoadImm4I) {
+            const Slot v = make_slot(__int_as_float((int)(signed char)(operand)), __int_as_float((int)(signed char)(operand >> 8)),
+                                     __int_as_float((int)(signed char)(operand >> 16)), __int_as_float((int)(signed char)(operand >> 24)));
+            GINT_FOR_K S[SP][k] = v;
+        }
+        /* ---- stack moves (move.py:7-55), rightmost = top ---- */
+        else if constexpr (OP == OP_Pop || OP == OP_Pop2) {
+        } else if constexpr (OP == OP_Dup) {
+            GINT_FOR_K S[SP][k] = S[T][k];
+        } else if constexpr (OP == OP_DupX1) {  // [a, b] -> [b, a, b]
+            GINT_FOR_K { const Slot b = S[T][k], a = S[T - 1][k]; S[T - 1][k] = b; S[T][k] = a; S[SP][k] = b; }
+        } else if constexpr (OP == OP_DupX2) {  // [a, b, c] -> [c, a, b, c]
+            GINT_FOR_K {
+                const Slot c = S[T][k], b = S[T - 1][k], a = S[T - 2][k];
+                S[T - 2][k] = c; S[T - 1][k] = a; S[T][k] = b; S[SP][k] = c;
+            }
+        } else if constexpr (OP == OP_Dup2) {  // [a, b] -> [a, b, a, b]
+            GINT_FOR_K { S[SP][k] = S[T - 1][k]; S[SP + 1][k] = S[T][k]; }
+        } else if constexpr (OP == OP_Swap) {
+            GINT_FOR_K { const Slot b = S[T][k]; S[T][k] = S[T - 1][k]; S[T - 1][k] = b; }
+        } else if constexpr (OP == OP_Select) {  // T > 0 ? S : U (predication.py:64-73)
+            GINT_FOR_K {
+                float c[4], x[4], y[4];
+                slot_get(S[T][k], c);
+                slot_get(S[T - 1][k], x);
+                slot_get(S[T - 2][k], y);
+#pragma unroll
+                for (int w = 0; w < 4; w++) y[w] = c[w] > 0.0f ? x[w] : y[w];
+                S[T - 2][k] = make_slot(y[0], y[1], y[2], y[3]);
+            }
+        }
+        /* ---- width-lane moves (move.py:69-135); operand indices pre-clamped to 0..3 ---- */
+        else if constexpr (OP == OP_DupBroadcastW) {
+            GINT_FOR_K {
+                float t[4];
+                slot_get(S[T][k], t);
+                S[SP][k] = splat(sel4(t, operand));
+            }
+        } else if constexpr (OP == OP_FPermW) {
+            GINT_FOR_K {
+                float t[4];
+                slot_get(S[T][k], t);
+                S[T][k] = make_slot(sel4(t, operand), sel4(t, operand >> 8), sel4(t, operand >> 16), sel4(t, operand >> 24));
+            }
+        } else if constexpr (OP == OP_FShuf2) {  // vec2 = T, vec1 = S -> (vec1[x], vec1[y], vec2[z], vec2[w])
+            GINT_FOR_K {
+                float v2[4], v1[4];
+                slot_get(S[T][k], v2);
+                slot_get(S[T - 1][k], v1);
+                S[T - 1][k] = make_slot(sel4(v1, operand), sel4(v1, operand >> 8), sel4(v2, operand >> 16), sel4(v2, operand >> 24));
+            }
+        }
+        /* ---- virtual registers: reg n = pool[P-1-n] (state.py:38-41, reg.py:7-59) ---- */
+        else if constexpr (OP >= OP_FLoadReg0 && OP <= OP_FLoadReg7) {
+            GINT_FOR_K S[SP][k] = S[P - 1 - (OP - OP_FLoadReg0)][k];
+        } else if constexpr (OP >= OP_FStoreReg0 && OP <= OP_FStoreReg7) {
+            GINT_FOR_K S[P - 1 - (OP - OP_FStoreReg0)][k] = S[T][k];
+        }
+        /* ---- warp all-reduce (reduction.py:7-30, nvptx.py:89-104): butterfly 16, 8, 4, 2, 1 per width lane ---- */
+        else if constexpr (OP >= OP_WarpAllReduceSum && OP <= OP_WarpAllReduceProd) {
+            GINT_FOR_K {
+                float t[4];
+                slot_get(S[T][k], t);
+#pragma unroll
+                for (int mask = 16; mask >= 1; mask >>= 1) {
+#pragma unroll
+                    for (int w = 0; w < 4; w++) {
+                        const float o = __shfl_xor_sync(0xffffffffu, t[w], mask);
+                        if constexpr (OP == OP_WarpAllReduceSum) t[w] = __fadd_rn(t[w], o);
+                        else if constexpr (OP == OP_WarpAllReduceMax) t[w] = max_nan(t[w], o);
+                        else if constexpr (OP == OP_WarpAllReduceMin) t[w] = min_nan(t[w], o);
+                        else t[w] = __fmul_rn(t[w], o);
+                    }
+                }
+                S[T][k] = make_slot(t[0], t[1], t[2], t[3]);
+            }
+        }
+        /* ---- global memory (load_store.py) ---- */
+        else if constexpr (OP == OP_LoadGlobal1DF32) op_load<LAY_1D, DT_F32, SP>(S, operand, cx);
+        else if constexpr (OP == OP_StoreGlobal1DF32) op_store<LAY_1D, DT_F32, SP>(S, operand, cx);
+        else if constexpr (OP == OP_LoadGlobal1DF16) op_load<LAY_1D, DT_F16, SP>(S, operand, cx);
+        else if constexpr (OP == OP_StoreGlobal1DF16) op_store<LAY_1D, DT_F16, SP>(S, operand, cx);
+        else if constexpr (OP == OP_LoadGlobal1DBF16) op_load<LAY_1D, DT_BF16, SP>(S, operand, cx);
+        else if constexpr (OP == OP_StoreGlobal1DBF16) op_store<LAY_1D, DT_BF16, SP>(S, operand, cx);
+        else if constexpr (OP == OP_LoadGlobal1DU8) op_load<LAY_1D, DT_U8, SP>(S, operand, cx);
+        else if constexpr (OP == OP_LoadGlobal2DTF32) op_load<LAY_2DT, DT_F32, SP>(S, operand, cx);
+        else if constexpr (OP == OP_StoreGlobal2DTF32) op_store<LAY_2DT, DT_F32, SP>(S, operand, cx);
+        else if constexpr (OP == OP_LoadGlobal2DTF16) op_load<LAY_2DT, DT_F16, SP>(S, operand, cx);
+        else if constexpr (OP == OP_StoreGlobal2DTF16) op_store<LAY_2DT, DT_F16, SP>(S, operand, cx);
+        else if constexpr (OP == OP_LoadGlobal2DTBF16) op_load<LAY_2DT, DT_BF16, SP>(S, operand, cx);
+        else if constexpr (OP == OP_StoreGlobal2DTBF16) op_store<LAY_2DT, DT_BF16, SP>(S, operand, cx);
+        else if constexpr (OP == OP_LoadGlobal2DTU8) op_load<LAY_2DT, DT_U8, SP>(S, operand, cx);
+        else if constexpr (OP == OP_LoadGlobal2DWF32) op_load<LAY_2DW, DT_F32, SP>(S, operand, cx);
+        else if constexpr (OP == OP_StoreGlobal2DWF32) op_store<LAY_2DW, DT_F32, SP>(S, operand, cx);
+        else if constexpr (OP == OP_LoadGlobal2DWF16) op_load<LAY_2DW, DT_F16, SP>(S, operand, cx);
+        else if constexpr (OP == OP_StoreGlobal2DWF16) op_store<LAY_2DW, DT_F16, SP>(S, operand, cx);
+        else if constexpr (OP == OP_LoadGlobal2DWBF16) op_load<LAY_2DW, DT_BF16, SP>(S, operand, cx);
+        else if constexpr (OP == OP_StoreGlobal2DWBF16) op_store<LAY_2DW, DT_BF16, SP>(S, operand, cx);
+        else if constexpr (OP == OP_LoadGlobal2DWU8) op_load<LAY_2DW, DT_U8, SP>(S, operand, cx);
+        else if constexpr (OP == OP_LoadGlobal1DF32Indirect) {  // pops indices, pushes values
+            GINT_FOR_K {
+                float idx[4], v[4];
+                slot_get(S[T][k], idx);
+                tile_indirect<false>(cx.tiles + k, operand, idx, v);
+                S[T][k] = make_slot(v[0], v[1], v[2], v[3]);
+            }
+        } else if constexpr (OP == OP_StoreGlobal1DF32Indirect) {  // indices on top, values below
+            GINT_FOR_K {
+                float idx[4], v[4];
+                slot_get(S[T][k], idx);
+                slot_get(S[T - 1][k], v);
+                tile_indirect<true>(cx.tiles + k, operand, idx, v);
+            }
+        } else if constexpr (OP == OP_AdvanceBlock2D || OP == OP_AdvanceBase) {  // load_store.py:291-321, operand >> 4 is arithmetic
+            __syncwarp();
+            if (cx.lane == 0) {
+                const int arg = operand & 15;
+                const int delta = ((int)operand) >> 4;
+                GINT_FOR_K {
+                    if constexpr (OP == OP_AdvanceBlock2D) cx.tiles[k].adv[arg] += delta;
+                    else cx.tiles[k].ptr[arg] += (u64)(long long)delta;  // bytes
+                }
+            }
+            __syncwarp();
+        }
+#undef GINT_FOR_K
+    }
+}
+
+/* ------------------------------------------------------------------------------------------------ */
+/* fetch / dispatch loop for one group of K logical programs                                          */
+
+template <bool SMEM> __device__ __forceinline__ uint2 fetch(const uint2 *p)
+{
+    if constexpr (SMEM) {
+        uint2 r;
+        const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+        asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(r.x), "=r"(r.y) : "r"(a));
+        return r;
+    } else {
+        return __ldg(p);
+    }
+}
+
+template <int P, int K, bool SMEM_CODE>
+__device__ __forceinline__ void interpret(const uint2 *code, const Ctx &cx)
+{
+    Slot S[P][K];
+#pragma unroll
+    for (int i = 0; i < P; i++)
+#pragma unroll
+        for (int k = 0; k < K; k++) { S[i][k].a = 0ull; S[i][k].b = 0ull; }
+
+    uint2 next = fetch<SMEM_CODE>(code);
+    ++code;
+    for (;;) {
+        const uint2 cur = next;
+        next = fetch<SMEM_CODE>(code);  // the stream is padded with Halt, so reading one ahead is in bounds
+        ++code;
+        switch (cur.x) {
+#define GINT_CASE_SP(num, spv)                                  \
+    case (spv) * GINT_N_OPCODES + (num):                        \
+        if constexpr ((num) == OP_Halt) return;                 \
+        else exec<num, spv, P, K>(S, cur.y, cx);                \
+        break;
+#define GINT_X_CASES(name, num, md, net)                                                                           \
+    GINT_CASE_SP(num, 0) GINT_CASE_SP(num, 1) GINT_CASE_SP(num, 2) GINT_CASE_SP(num, 3) GINT_CASE_SP(num, 4)       \
+    GINT_CASE_SP(num, 5) GINT_CASE_SP(num, 6) GINT_CASE_SP(num, 7) GINT_CASE_SP(num, 8)
+            GINT_OPCODE_LIST(GINT_X_CASES)
+#undef GINT_X_CASES
+#undef GINT_CASE_SP
+        default:
+            return;
+        }
+    }
+}
+
+/* ------------------------------------------------------------------------------------------------ */
+/* kernels                                                                                           */
+
+/* Direct mode: every logical program runs the same bytecode. Persistent blocks of kWarpsPerBlock warps;
+ * shared memory = [program | descriptor block | kWarpsPerBlock x K TileInfo]. */
+template <int P, int K>
+__global__ void __launch_bounds__(kThreadsPerBlock, GINT_MIN_BLOCKS(P, K)) geval_direct(const __grid_constant__ LaunchArgs a)
+{
+    extern __shared__ __align__(16) unsigned char smem[];
+    uint2 *code_s = reinterpret_cast<uint2 *>(smem);
+    gint_tensor_info *ti_s = reinterpret_cast<gint_tensor_info *>(smem + a.code_smem_bytes);
+    TileInfo *tiles_s = reinterpret_cast<TileInfo *>(smem + a.code_smem_bytes + kTensorInfoSmemBytes);
+
+    for (uint32_t i = threadIdx.x; i < a.n_slots; i += kThreadsPerBlock) code_s[i] = a.code[i];
+    {
+        const int *src = reinterpret_cast<const int *>(&a.ti);
+        int *dst = reinterpret_cast<int *>(ti_s);
+        for (uint32_t i = threadIdx.x; i < sizeof(gint_tensor_info) / 4; i += kThreadsPerBlock) dst[i] = src[i];
+    }
+    __syncthreads();
+
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    Ctx cx;
+    cx.tiles = tiles_s + warp * K;
+    cx.lane = lane;
+
+    const uint32_t n_groups = (a.end - a.first + (uint32_t)K - 1u) / (uint32_t)K;
+    for (uint32_t g = blockIdx.x * kWarpsPerBlock + warp; g < n_groups; g += gridDim.x * kWarpsPerBlock) {
+        __syncwarp();  // every lane is done with the previous group's tile descriptors
+        decode_tiles<K>(ti_s, (int)a.n_tensors, a.first + g * (uint32_t)K, a.end, cx.tiles, lane);
+        interpret<P, K, true>(code_s, cx);
+    }
+}
+
+/* Indirect mode (main.py:179-194, flag > 0): logical program i has its own bytecode and descriptors, read
+ * through a per-program table; the bytecode is fetched from global memory through the read-only path. */
+template <int P>
+__global__ void __launch_bounds__(kThreadsPerBlock) geval_indirect(const __grid_constant__ IndirectArgs a)
+{
+    extern __shared__ __align__(16) unsigned char smem[];
+    TileInfo *tiles_s = reinterpret_cast<TileInfo *>(smem);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    Ctx cx;
+    cx.tiles = tiles_s + warp;
+    cx.lane = lane;
+    for (uint32_t g = blockIdx.x * kWarpsPerBlock + warp; g < a.grid_dim; g += gridDim.x * kWarpsPerBlock) {
+        const IndirectEntry e = a.table[g];
+        __syncwarp();
+        decode_tiles<1>(e.ti, (int)a.n_tensors, g, a.grid_dim, cx.tiles, lane);
+        interpret<P, 1, false>(e.code, cx);
+    }
+}
+
+}  // namespace gint

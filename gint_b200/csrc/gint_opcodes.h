@@ -1,0 +1,129 @@
+/*
+ * gint_opcodes.h -- opcode numbers and stack effects of the gint bytecode format, as an X-macro.
+ *
+ * Numbering follows the reference's INSNS table (gint/kernel/interpreter/main.py:61-168); the
+ * (minimum depth, net effect) pairs follow its analyzer (gint/host/analyzer.py:24-135).
+ * X(name, opcode, min_depth, net_effect)
+ */
+#ifndef GINT_OPCODES_H
+#define GINT_OPCODES_H
+
+#define GINT_N_OPCODES 106
+#define GINT_MAX_STACK 8
+#define GINT_NUM_REGS 8
+
+#define GINT_OPCODE_LIST(X) \
+    X(Halt, 0, 0, 0) \
+    X(Nop, 1, 0, 0) \
+    X(FAdd, 2, 2, -1) \
+    X(FMul, 3, 2, -1) \
+    X(FMA, 4, 3, -2) \
+    X(FSub, 5, 2, -1) \
+    X(FRSub, 6, 2, -1) \
+    X(FNeg, 7, 1, 0) \
+    X(FDiv, 8, 2, -1) \
+    X(FRDiv, 9, 2, -1) \
+    X(FRem, 10, 2, -1) \
+    X(LoadImm, 11, 0, 1) \
+    X(FAddImm, 12, 1, 0) \
+    X(FMulImm, 13, 1, 0) \
+    X(FMAImm, 14, 1, 0) \
+    X(LoadGlobal1DF32, 15, 0, 1) \
+    X(StoreGlobal1DF32, 16, 1, -1) \
+    X(LoadGlobal1DF16, 17, 0, 1) \
+    X(StoreGlobal1DF16, 18, 1, -1) \
+    X(LoadGlobal1DBF16, 19, 0, 1) \
+    X(StoreGlobal1DBF16, 20, 1, -1) \
+    X(LoadGlobal1DU8, 21, 0, 1) \
+    X(Pop, 22, 1, -1) \
+    X(Pop2, 23, 2, -2) \
+    X(Dup, 24, 1, 1) \
+    X(DupX1, 25, 2, 1) \
+    X(DupX2, 26, 3, 1) \
+    X(Dup2, 27, 2, 2) \
+    X(FGt, 28, 2, -1) \
+    X(FLt, 29, 2, -1) \
+    X(FGe, 30, 2, -1) \
+    X(FLe, 31, 2, -1) \
+    X(FEq, 32, 2, -1) \
+    X(FNe, 33, 2, -1) \
+    X(FApprox, 34, 2, -1) \
+    X(Select, 35, 3, -2) \
+    X(WarpAllReduceSum, 36, 1, 0) \
+    X(WarpAllReduceMax, 37, 1, 0) \
+    X(WarpAllReduceMin, 38, 1, 0) \
+    X(WarpAllReduceProd, 39, 1, 0) \
+    X(FSqrt, 40, 1, 0) \
+    X(FSin, 41, 1, 0) \
+    X(FCos, 42, 1, 0) \
+    X(FTan, 43, 1, 0) \
+    X(FArcSin, 44, 1, 0) \
+    X(FArcCos, 45, 1, 0) \
+    X(FArcTan, 46, 1, 0) \
+    X(FArcTan2, 47, 2, -1) \
+    X(FPow, 48, 2, -1) \
+    X(FExp, 49, 1, 0) \
+    X(FExp2, 50, 1, 0) \
+    X(FLog, 51, 1, 0) \
+    X(FLog2, 52, 1, 0) \
+    X(FRSqrt, 53, 1, 0) \
+    X(FErf, 54, 1, 0) \
+    X(Swap, 55, 2, 0) \
+    X(IAdd, 56, 2, -1) \
+    X(IMul, 57, 2, -1) \
+    X(ISub, 58, 2, -1) \
+    X(IDiv, 59, 2, -1) \
+    X(IRem, 60, 2, -1) \
+    X(IShl, 61, 2, -1) \
+    X(IShr, 62, 2, -1) \
+    X(IAnd, 63, 2, -1) \
+    X(IOr, 64, 2, -1) \
+    X(IXor, 65, 2, -1) \
+    X(LoadGlobal1DF32Indirect, 66, 1, 0) \
+    X(StoreGlobal1DF32Indirect, 67, 2, -2) \
+    X(LoadImm4F, 68, 0, 1) \
+    X(LoadImm4I, 69, 0, 1) \
+    X(LoadGlobal2DTF32, 70, 0, 1) \
+    X(StoreGlobal2DTF32, 71, 1, -1) \
+    X(LoadGlobal2DTF16, 72, 0, 1) \
+    X(StoreGlobal2DTF16, 73, 1, -1) \
+    X(LoadGlobal2DTBF16, 74, 0, 1) \
+    X(StoreGlobal2DTBF16, 75, 1, -1) \
+    X(LoadGlobal2DTU8, 76, 0, 1) \
+    X(LoadGlobal2DWF32, 77, 0, 1) \
+    X(StoreGlobal2DWF32, 78, 1, -1) \
+    X(LoadGlobal2DWF16, 79, 0, 1) \
+    X(StoreGlobal2DWF16, 80, 1, -1) \
+    X(LoadGlobal2DWBF16, 81, 0, 1) \
+    X(StoreGlobal2DWBF16, 82, 1, -1) \
+    X(LoadGlobal2DWU8, 83, 0, 1) \
+    X(AdvanceBlock2D, 84, 0, 0) \
+    X(AdvanceBase, 85, 0, 0) \
+    X(DupBroadcastW, 86, 1, 1) \
+    X(FLoadReg0, 87, 0, 1) \
+    X(FLoadReg1, 88, 0, 1) \
+    X(FLoadReg2, 89, 0, 1) \
+    X(FLoadReg3, 90, 0, 1) \
+    X(FLoadReg4, 91, 0, 1) \
+    X(FLoadReg5, 92, 0, 1) \
+    X(FLoadReg6, 93, 0, 1) \
+    X(FLoadReg7, 94, 0, 1) \
+    X(FStoreReg0, 95, 1, -1) \
+    X(FStoreReg1, 96, 1, -1) \
+    X(FStoreReg2, 97, 1, -1) \
+    X(FStoreReg3, 98, 1, -1) \
+    X(FStoreReg4, 99, 1, -1) \
+    X(FStoreReg5, 100, 1, -1) \
+    X(FStoreReg6, 101, 1, -1) \
+    X(FStoreReg7, 102, 1, -1) \
+    X(FRcp, 103, 1, 0) \
+    X(FPermW, 104, 1, 0) \
+    X(FShuf2, 105, 2, -1)
+
+enum gint_opcode {
+#define GINT_X_ENUM(name, num, md, net) OP_##name = num,
+    GINT_OPCODE_LIST(GINT_X_ENUM)
+#undef GINT_X_ENUM
+};
+
+#endif /* GINT_OPCODES_H */

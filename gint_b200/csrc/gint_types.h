@@ -1,0 +1,60 @@
+/*
+ * gint_types.h -- structures shared by the interpreter kernels (gint_interp.cuh) and the host side (gint_capi.cu).
+ */
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/gint_b200.h"
+#include "gint_opcodes.h"
+
+namespace gint {
+
+typedef unsigned long long u64;
+
+constexpr int kWarpsPerBlock = 4;
+constexpr int kThreadsPerBlock = kWarpsPerBlock * 32;
+constexpr int kTensorInfoSmemBytes = 640;  // 608-byte descriptor block, padded to a 128-byte multiple
+constexpr int kNumKeys = (GINT_MAX_STACK + 1) * GINT_N_OPCODES;
+
+/* Minimum resident blocks per SM requested from the compiler (caps registers per thread): the pool itself
+ * takes 4*P*K registers. */
+#ifndef GINT_MIN_BLOCKS
+#define GINT_MIN_BLOCKS(P, K) ((P) * (K) <= 7 ? 8 : (P) * (K) <= 16 ? 5 : 4)
+#endif
+
+/* Per logical program, decoded once into shared memory (the reference's BlockTensorInfo,
+ * load_tensor_infos.py:6-11, plus a flags word): 256 bytes. */
+struct __align__(16) TileInfo {
+    u64 ptr[GINT_MAX_TENSORS];   // base pointer with the per-program offset applied
+    int2 s1[GINT_MAX_TENSORS];   // (shape1 clamped to this program's tile, stride1)
+    int2 s2[GINT_MAX_TENSORS];   // (shape2 clamped, stride2)
+    int adv[GINT_MAX_TENSORS];   // AdvanceBlock2D accumulator
+    int flags[GINT_MAX_TENSORS]; // kVecRows: 2DW rows are 16-byte vectorisable
+};
+constexpr int kVecRows = 1;
+
+struct LaunchArgs {
+    const uint2 *code;        // pre-decoded {key, operand}; n_slots entries, padded with Halt
+    uint32_t n_slots;         // entries staged into shared memory (even, so the copy is a 16-byte multiple)
+    uint32_t n_tensors;
+    uint32_t first;           // first logical program of this launch
+    uint32_t end;             // one past the last logical program
+    uint32_t code_smem_bytes; // shared-memory bytes reserved for the program
+    uint32_t reserved;
+    gint_tensor_info ti;      // descriptor block, base pointers patched per call: travels as a kernel parameter
+};
+
+struct IndirectEntry {
+    const uint2 *code;              // pre-decoded program of this logical program
+    const gint_tensor_info *ti;     // its descriptor block in device memory
+};
+
+struct IndirectArgs {
+    const IndirectEntry *table;
+    uint32_t n_tensors;       // maximum over the batch (executor_impl.py:192)
+    uint32_t grid_dim;
+};
+
+}  // namespace gint

@@ -1,0 +1,345 @@
+"""Executor API of gint, backed by the B200 kernels (mirror of ``gint/host/executor.py`` +
+``gint/host/cuda/executor_impl.py``).
+
+Public names, argument meaning and error behaviour follow the reference so that programs, tests and the
+conductor's ``executor.execute(program, tensor_interfaces, grid_dim, cuda_stream=...)`` calls work unchanged:
+
+* ``ProgramTensorInfo`` / ``ProgramData`` / ``TensorInterface``  (``executor.py:14-98``)
+* ``BaseExecutableProgram`` with ``get_program`` / ``cache_policy`` / ``__call__(*, grid_dim)``  (``executor.py:152-197``)
+* ``BaseExecutor.{warp_size, execute, execute_indirect}`` and the ``get_executor()`` singleton  (``executor.py:200-233``)
+
+What differs is below the seam: ``B200Executor`` hands the bytecode and the descriptor template to
+``libgint_b200.so`` once per (program, cache key, device) and each later call is one C call that patches base
+pointers into kernel parameters and launches. There is no CPU path.
+"""
+from __future__ import annotations
+
+import ctypes
+import sys
+import threading
+from collections.abc import Hashable
+from dataclasses import dataclass, field
+from typing import Any, Optional, Sequence, Union
+
+import numpy
+import torch
+
+from ..opcodes import MAX_N_TENSORS, REG_WIDTH
+from . import capi
+from .analyzer import BytecodeStats, analyze_bytecode, select_pool_size
+from .utils import fill_tensor_info
+
+# Kernel geometries of the reference, kept for callers that ask by name (``gint/kernel/interpreter/main.py:34-38``):
+# name -> (pool size, registers, max stack).
+VARIANTS: dict[str, tuple[int, int, int]] = {"s7": (7, 4, 7), "l12": (12, 8, 8)}
+DEFAULT_VARIANT = "l12"
+
+
+@dataclass
+class ProgramTensorInfo:
+    elm_size: int
+    batch_strides: list[int]
+    batch_shape: list[int]
+    block_shape_stride_1: list[int]
+    block_shape_stride_2: list[int]
+    block_grid_dims: list[int]
+    block_grid_steps: list[int]
+
+
+@dataclass
+class ProgramData:
+    program: numpy.ndarray            # int32, flat [opcode, operand, opcode, operand, ...]
+    input_infos: list[ProgramTensorInfo]
+    input_indices: Optional[list[int]] = None   # descriptor slot i reads argument input_indices[i]
+    _stats: Optional[BytecodeStats] = field(default=None, repr=False, compare=False)
+
+    @property
+    def stats(self) -> BytecodeStats:
+        if self._stats is None:
+            self._stats = analyze_bytecode(self.program)
+        return self._stats
+
+
+@dataclass
+class TensorInterface:
+    typechr: str
+    elm_size: int
+    base_ptr: int
+    shape: tuple[int, ...]
+    strides: tuple[int, ...]   # in elements
+
+    @property
+    def ndim(self) -> int:
+        return len(self.shape)
+
+    @property
+    def typestr(self) -> str:
+        return f"{self.typechr}{self.elm_size}"
+
+    @property
+    def __cuda_array_interface__(self) -> dict:
+        return {"version": 2, "data": (self.base_ptr, False), "shape": self.shape,
+                "typestr": f"<{self.typechr}{self.elm_size}", "strides": tuple(s * self.elm_size for s in self.strides)}
+
+    @classmethod
+    def from_cuda_array_interface(cls, obj: Union[dict, Any]) -> "TensorInterface":
+        cai = obj if isinstance(obj, dict) else getattr(obj, "__cuda_array_interface__", None)
+        if cai is None:
+            raise TypeError("__cuda_array_interface__ not found for cuda array interface object.")
+        if "typestr" not in cai:
+            raise TypeError("Invalid __cuda_array_interface__: missing `typestr`")
+        typestr = cai["typestr"]
+        if typestr[0] not in "<|" or sys.byteorder != "little":
+            raise AssertionError("gint does not support big endian yet")
+        if cai["version"] < 2:
+            raise AssertionError(cai["version"])
+        ptr, readonly = cai["data"]
+        if readonly:
+            raise AssertionError("gint does not support readonly")
+        nbytes = int(typestr[2:])
+        shape = tuple(cai["shape"])
+        if cai.get("strides"):
+            strides = tuple(s // nbytes for s in cai["strides"])
+        else:
+            strides, acc = [], 1
+            for extent in reversed(shape):
+                strides.append(acc)
+                acc *= extent
+            strides = tuple(reversed(strides))
+        if len(shape) != len(strides):
+            raise AssertionError((shape, strides, "shape and strides must have the same ndim"))
+        return cls(typestr[1], nbytes, ptr, shape, strides)
+
+
+_TORCH_TYPES = {
+    torch.float32: ("f", 4), torch.float16: ("f", 2), torch.bfloat16: ("f", 2), torch.float64: ("f", 8),
+    torch.int32: ("i", 4), torch.int64: ("i", 8), torch.uint8: ("u", 1), torch.bool: ("b", 1),
+}
+
+
+def _convert_arg(arg) -> TensorInterface:
+    if isinstance(arg, TensorInterface):
+        return arg
+    if isinstance(arg, torch.Tensor):
+        typechr, size = _TORCH_TYPES[arg.dtype]
+        return TensorInterface(typechr, size, arg.data_ptr(), tuple(arg.shape), tuple(arg.stride()))
+    return TensorInterface.from_cuda_array_interface(arg)
+
+
+def select_variant(bytecode_or_pd) -> str:
+    """Name of the reference kernel geometry that would run this program (``gint/host/executor.py:131-149``).
+    The B200 library chooses its own pool size (``ProgramData.stats`` -> ``select_pool_size``); this is for callers
+    and tests that reason in the reference's terms."""
+    stats = bytecode_or_pd.stats if isinstance(bytecode_or_pd, ProgramData) else analyze_bytecode(bytecode_or_pd)
+    for name, (_, regs, stack) in sorted(VARIANTS.items(), key=lambda kv: kv[1][0]):
+        if stats.max_stack <= stack and stats.max_reg_idx + 1 <= regs:
+            return name
+    return DEFAULT_VARIANT
+
+
+class BaseExecutableProgram:
+    REGW = REG_WIDTH
+
+    def get_program(self, *args: TensorInterface, **extra_kwargs) -> ProgramData:
+        raise NotImplementedError()
+
+    def cache_policy(self, *args: TensorInterface, **extra_kwargs) -> Hashable:
+        return tuple((x.shape, x.strides, x.typechr, x.elm_size) for x in args) + tuple(sorted(extra_kwargs.items()))
+
+    def executor_warp_size(self) -> int:
+        return get_executor().warp_size()
+
+    def __call__(self, *args, grid_dim: int, **extra_kwargs):
+        # Calling a gint program from inside a torch.compile trace must not be traced: run it as a graph break.
+        if torch.compiler.is_compiling():
+            return _call_untraced(self, args, grid_dim, extra_kwargs)
+        get_executor().execute(self, [_convert_arg(a) for a in args], grid_dim, **extra_kwargs)
+
+
+@torch.compiler.disable
+def _call_untraced(program, args, grid_dim, extra_kwargs):
+    get_executor().execute(program, [_convert_arg(a) for a in args], grid_dim, **extra_kwargs)
+
+
+class BaseExecutor:
+    def warp_size(self) -> int:
+        raise NotImplementedError
+
+    def execute(self, program: BaseExecutableProgram, args: Sequence[TensorInterface], grid_dim: int, **extra_kwargs):
+        raise NotImplementedError
+
+    def execute_indirect(self, programs: Sequence[BaseExecutableProgram], args_list: Sequence[Sequence[TensorInterface]],
+                         indices: Sequence[int], **extra_kwargs):
+        raise NotImplementedError
+
+
+class _Cacheline:
+    __slots__ = ("handle", "indices", "ptrs", "n", "pd")
+
+    def __init__(self, handle, indices, pd):
+        self.handle = handle
+        self.indices = indices
+        self.n = len(indices)
+        self.ptrs = (ctypes.c_uint64 * MAX_N_TENSORS)()
+        self.pd = pd
+
+
+class B200Executor(BaseExecutor):
+    """Launches gint programs through libgint_b200.so. One library context per CUDA device, created on first use."""
+
+    def __init__(self) -> None:
+        self._lib = capi.load_library()
+        self._ctxs: dict[int, ctypes.c_void_p] = {}
+        self._lock = threading.Lock()
+        self.launches = 0          # number of kernel launches issued through this executor
+
+    # ------------------------------------------------------------------ plumbing
+    def warp_size(self) -> int:
+        return 32
+
+    def _ctx(self, device: Optional[int] = None):
+        if device is None:
+            device = torch.cuda.current_device()
+        ctx = self._ctxs.get(device)
+        if ctx is None:
+            with self._lock:
+                ctx = self._ctxs.get(device)
+                if ctx is None:
+                    if not torch.cuda.is_available():
+                        raise capi.GintError(capi.GINT_ERR_NO_DEVICE, "CUDA is not available; gint_b200 has no CPU path")
+                    torch.cuda.init()
+                    out = ctypes.c_void_p()
+                    rc = self._lib.gint_create(device, ctypes.byref(out))
+                    if rc != 0:
+                        raise capi.GintError(rc, f"gint_create(device={device}): {capi.status_string(rc)}")
+                    ctx = self._ctxs[device] = out
+        return device, ctx
+
+    def _check(self, ctx, rc: int, what: str):
+        if rc == 0:
+            return
+        msg = self._lib.gint_last_error(ctx).decode(errors="replace")
+        if rc == capi.GINT_ERR_ARG_COUNT:
+            raise ValueError("Number of arguments don't match the program.")
+        if rc in (capi.GINT_ERR_UNKNOWN_OPCODE, capi.GINT_ERR_STACK_UNDERFLOW, capi.GINT_ERR_STACK_OVERFLOW, capi.GINT_ERR_NO_HALT):
+            raise ValueError(f"{what}: {msg}")
+        raise capi.GintError(rc, f"{what}: {msg}")
+
+    def _build_cacheline(self, ctx, program, args, extra_kwargs) -> _Cacheline:
+        pd = program.get_program(*args, **extra_kwargs)
+        if pd.input_indices is None:
+            pd.input_indices = list(range(len(pd.input_infos)))
+        if len(pd.input_indices) != len(pd.input_infos):
+            raise AssertionError("Input indices must match input infos")
+        if len(args) != len(pd.input_indices):
+            raise ValueError("Number of arguments don't match the program.")
+        if len(pd.input_infos) > MAX_N_TENSORS:
+            raise ValueError(f"At most {MAX_N_TENSORS} tensors per program")
+        pd.stats  # raises ValueError on unknown opcodes / stack underflow, like the reference's select_variant
+        code = numpy.ascontiguousarray(numpy.asarray(pd.program, dtype=numpy.int32).reshape(-1))
+        ti = capi.HTensorInfo()
+        fill_tensor_info(ti, pd.input_infos)
+        handle = ctypes.c_uint64()
+        rc = self._lib.gint_program_create(ctx, code.ctypes.data_as(ctypes.POINTER(ctypes.c_int32)), int(code.size),
+                                           ctypes.byref(ti), len(pd.input_infos), ctypes.byref(handle))
+        self._check(ctx, rc, "gint_program_create")
+        return _Cacheline(handle.value, list(pd.input_indices), pd)
+
+    def _cacheline(self, program, args, extra_kwargs):
+        device, ctx = self._ctx()
+        cache = program.__dict__.get("_b200")
+        if cache is None:
+            cache = program._b200 = {}
+        key = (device, program.cache_policy(*args, **extra_kwargs))
+        line = cache.get(key)
+        if line is None:
+            line = cache[key] = self._build_cacheline(ctx, program, args, extra_kwargs)
+        return ctx, line
+
+    # ------------------------------------------------------------------ BaseExecutor API
+    def execute(self, program: BaseExecutableProgram, args: Sequence[TensorInterface], grid_dim: int, cuda_stream: int = 0,
+                **extra_kwargs):
+        ctx, line = self._cacheline(program, args, extra_kwargs)
+        ptrs = line.ptrs
+        for i, a in enumerate(line.indices):
+            ptrs[i] = args[a].base_ptr
+        rc = self._lib.gint_execute(ctx, line.handle, ptrs, line.n, grid_dim, cuda_stream)
+        if rc != 0:
+            self._check(ctx, rc, "gint_execute")
+        self.launches += 1
+
+    def execute_range(self, program: BaseExecutableProgram, args: Sequence[TensorInterface], first: int, count: int,
+                      cuda_stream: int = 0, **extra_kwargs):
+        """Run logical programs ``[first, first + count)`` of the program's grid (multi-GPU sharding primitive)."""
+        ctx, line = self._cacheline(program, args, extra_kwargs)
+        ptrs = line.ptrs
+        for i, a in enumerate(line.indices):
+            ptrs[i] = args[a].base_ptr
+        rc = self._lib.gint_execute_range(ctx, line.handle, ptrs, line.n, first, count, cuda_stream)
+        if rc != 0:
+            self._check(ctx, rc, "gint_execute_range")
+        self.launches += 1
+
+    def execute_indirect(self, programs: Sequence[BaseExecutableProgram], args_list: Sequence[Sequence], indices: Sequence[int],
+                         cuda_stream: int = 0):
+        """One launch; logical program ``i`` runs ``programs[indices[i]]`` on ``args_list[indices[i]]``
+        (``gint/host/cuda/executor_impl.py:135-201``)."""
+        if len(programs) != len(args_list):
+            raise AssertionError("programs and args_list must have the same length")
+        n = len(programs)
+        grid_dim = len(indices)
+        handles = (ctypes.c_uint64 * n)()
+        ptrs = (ctypes.c_uint64 * (n * MAX_N_TENSORS))()
+        ctx = None
+        for p, (prog, args) in enumerate(zip(programs, args_list)):
+            conv = [_convert_arg(a) for a in args]
+            ctx, line = self._cacheline(prog, conv, {})
+            handles[p] = line.handle
+            for i, a in enumerate(line.indices):
+                ptrs[p * MAX_N_TENSORS + i] = conv[a].base_ptr
+        idx = (ctypes.c_int32 * grid_dim)(*[int(i) for i in indices])
+        rc = self._lib.gint_execute_indirect(ctx, handles, n, ptrs, idx, grid_dim, cuda_stream)
+        if rc != 0:
+            self._check(ctx, rc, "gint_execute_indirect")
+        self.launches += 1
+
+    # ------------------------------------------------------------------ introspection / tuning
+    def launch_info(self, program: BaseExecutableProgram, args: Sequence, grid_dim: int, **extra_kwargs) -> dict:
+        args = [_convert_arg(a) for a in args]
+        ctx, line = self._cacheline(program, args, extra_kwargs)
+        info = capi.LaunchInfoC()
+        rc = self._lib.gint_program_launch_info(ctx, line.handle, grid_dim, ctypes.byref(info))
+        self._check(ctx, rc, "gint_program_launch_info")
+        return {name: getattr(info, name) for name, _ in capi.LaunchInfoC._fields_ if name != "reserved"}
+
+    def set_option(self, name: str, value: int, device: Optional[int] = None) -> None:
+        _, ctx = self._ctx(device)
+        rc = self._lib.gint_set_option(ctx, name.encode(), int(value))
+        self._check(ctx, rc, f"gint_set_option({name})")
+
+    def close(self) -> None:
+        for ctx in self._ctxs.values():
+            self._lib.gint_destroy(ctx)
+        self._ctxs.clear()
+
+
+executor: Optional[BaseExecutor] = None
+
+
+def get_executor() -> BaseExecutor:
+    """The process-wide executor (``gint/host/executor.py:212-233``); always the B200 one here."""
+    global executor
+    if executor is None:
+        executor = B200Executor()
+    return executor
+
+
+def c_analyze(program) -> dict:
+    """Run the library's own static analysis (``gint_analyze``) on a bytecode array; no GPU needed."""
+    lib = capi.load_library()
+    code = numpy.ascontiguousarray(numpy.asarray(program, dtype=numpy.int32).reshape(-1))
+    st = capi.BytecodeStatsC()
+    rc = lib.gint_analyze(code.ctypes.data_as(ctypes.POINTER(ctypes.c_int32)), int(code.size), ctypes.byref(st))
+    out = {name: getattr(st, name) for name, _ in capi.BytecodeStatsC._fields_ if name != "reserved"}
+    out["status"] = rc
+    return out

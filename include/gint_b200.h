@@ -1,0 +1,158 @@
+/*
+ * gint_b200.h -- C ABI of the B200-native gint bytecode executor (libgint_b200.so).
+ *
+ * The reference (eliphatfs/gint) has no C ABI: its executor is Python over the CUDA driver bindings.
+ * Each entry point below replaces one piece of that Python executor; the citation names the reference
+ * code it stands in for. Plain pointers and sizes only; every function returns GINT_OK (0) or a negative
+ * gint_status, never throws and never aborts. Device pointers are passed as uint64_t, the CUDA stream as
+ * the raw CUstream / cudaStream_t handle (what torch.cuda.current_stream().cuda_stream holds).
+ *
+ * Threading: a gint_ctx may be used from several host threads; program creation/destruction take an
+ * internal lock, launches are lock-free. One gint_ctx per device.
+ */
+#ifndef GINT_B200_H
+#define GINT_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define GINT_MAX_TENSORS 8  /* gint/kernel/platforms/common.py:63 (MAX_N_TENSORS) */
+
+/*
+ * Tensor descriptor block, byte-identical to the reference's host struct HTensorInfo
+ * (gint/kernel/interpreter/structs.py:19-30): struct-of-arrays over 8 tensor slots, 608 bytes.
+ * batch_strides / batch_shape are in REVERSED order (index 0 = innermost batch dim), padded with
+ * stride 0 / shape 1 (gint/host/utils.py:6-27).
+ */
+typedef struct gint_tensor_info {
+    int64_t base_ptr[GINT_MAX_TENSORS];
+    int32_t elm_size[GINT_MAX_TENSORS];
+    int32_t batch_strides[GINT_MAX_TENSORS][4];
+    int32_t batch_shape[GINT_MAX_TENSORS][4];
+    int32_t block_shape_stride_1[GINT_MAX_TENSORS][2];
+    int32_t block_shape_stride_2[GINT_MAX_TENSORS][2];
+    int32_t block_grid_dims[GINT_MAX_TENSORS][2];
+    int32_t block_grid_steps[GINT_MAX_TENSORS][2];
+} gint_tensor_info;
+
+typedef enum gint_status {
+    GINT_OK = 0,
+    GINT_ERR_INVALID_ARGUMENT = -1,  /* null pointer, bad count, odd word count ... */
+    GINT_ERR_UNKNOWN_OPCODE = -2,    /* gint/host/analyzer.py:205-208 raises ValueError */
+    GINT_ERR_STACK_UNDERFLOW = -3,   /* gint/host/analyzer.py:209-213 raises ValueError */
+    GINT_ERR_STACK_OVERFLOW = -4,    /* deeper than any kernel geometry (8) */
+    GINT_ERR_NO_HALT = -5,           /* stream not terminated by opcode 0 */
+    GINT_ERR_BAD_HANDLE = -6,
+    GINT_ERR_ARG_COUNT = -7,         /* gint/host/cuda/executor_impl.py:93-94 raises ValueError */
+    GINT_ERR_CUDA = -8,              /* a CUDA runtime call failed; see gint_last_error() */
+    GINT_ERR_NO_DEVICE = -9,         /* no usable sm_100 device / kernel image */
+    GINT_ERR_TOO_LARGE = -10,        /* program or batch exceeds a documented limit */
+    GINT_ERR_OUT_OF_MEMORY = -11
+} gint_status;
+
+/* Result of the static walk over a straight-line program (gint/host/analyzer.py:137-158, BytecodeStats). */
+typedef struct gint_bytecode_stats {
+    int32_t num_instructions; /* up to, not including, the first Halt */
+    int32_t max_stack;
+    int32_t max_reg_idx;      /* -1 if no virtual register is touched */
+    int32_t min_pool_size;
+    int32_t regs_used_mask;   /* bit n set = register n touched */
+    int32_t error_index;      /* instruction index of the first error, -1 if none */
+    int32_t pool_size;        /* pool geometry this library runs the program with: 4, 7 or 12 */
+    int32_t reserved;
+} gint_bytecode_stats;
+
+/* How a program will be / was launched; for tests, benchmarks and DESIGN notes. */
+typedef struct gint_launch_info {
+    int32_t pool_size;        /* 4, 7, 12 */
+    int32_t tiles_per_warp;   /* logical programs interpreted together by one warp: 1, 2 or 4 */
+    int32_t warps_per_block;
+    int32_t grid_blocks;
+    int32_t smem_bytes;
+    int32_t regs_per_thread;
+    int32_t blocks_per_sm;
+    int32_t num_sms;
+    int32_t staged_row_tensors; /* bit t set = tensor slot t is staged into shared memory */
+    int32_t reserved[7];
+} gint_launch_info;
+
+typedef struct gint_ctx gint_ctx;
+
+/* ---- host-only helpers: no GPU needed ---------------------------------------------------------- */
+
+/* Library version (major*10000 + minor*100 + patch). */
+int gint_version(void);
+
+/* Human-readable name of a status code. */
+const char *gint_status_string(int status);
+
+/* sizeof(gint_tensor_info); lets a binding check its struct layout (608). */
+int gint_sizeof_tensor_info(void);
+
+/* Static analysis of a bytecode stream. Replaces analyze_bytecode (gint/host/analyzer.py:187-238) and
+ * select_variant (gint/host/executor.py:131-149). n_words = 2 * number of instructions. */
+int gint_analyze(const int32_t *code, int n_words, gint_bytecode_stats *out);
+
+/* Pre-decode a stream into the kernel's internal form (for tests): out_keys[i] receives the dispatch key of
+ * instruction i (stack depth * number of opcodes + opcode). Returns the instruction count incl. Halt, or < 0. */
+int gint_predecode(const int32_t *code, int n_words, uint32_t *out_keys, int max_keys);
+
+/* ---- context ------------------------------------------------------------------------------------ */
+
+/* Create the executor state for one device, using that device's primary context (the one PyTorch uses).
+ * Replaces CudaExecutor.__init__ / geval_func_handle (gint/host/cuda/executor_impl.py:14-37) and
+ * current_context/fatbin_load (gint/host/cuda/driver.py:84-95,162-169). */
+int gint_create(int device, gint_ctx **out);
+void gint_destroy(gint_ctx *ctx);
+
+/* Message of the last failure on this context (thread-unsafe convenience, never NULL). */
+const char *gint_last_error(gint_ctx *ctx);
+
+/* ---- programs ----------------------------------------------------------------------------------- */
+
+/* Validate, pre-decode and upload a program together with its static descriptor template
+ * (base_ptr values are ignored here). Replaces the cache-miss half of CudaExecutor.execute,
+ * _build_cacheline (gint/host/cuda/executor_impl.py:76-133) and fill_tensor_info's consumer.
+ * Allocates device memory; call outside stream capture. */
+int gint_program_create(gint_ctx *ctx, const int32_t *code, int n_words, const gint_tensor_info *ti,
+                        int n_tensors, uint64_t *out_handle);
+int gint_program_destroy(gint_ctx *ctx, uint64_t handle);
+
+/* Geometry the library would use to launch `handle` over grid_dim logical programs. */
+int gint_program_launch_info(gint_ctx *ctx, uint64_t handle, uint32_t grid_dim, gint_launch_info *out);
+
+/* ---- launches ----------------------------------------------------------------------------------- */
+
+/* Launch the interpreter over logical programs [0, grid_dim). base_ptrs[i] is the device address for
+ * descriptor slot i. Asynchronous on `cuda_stream`; performs no allocation and no host<->device copy
+ * (descriptors travel as kernel parameters), so it is legal during stream capture and every captured
+ * launch is self-contained. Replaces the cache-hit half of CudaExecutor.execute
+ * (gint/host/cuda/executor_impl.py:63-74: base-pointer patch, 608-byte H2D copy, cuLaunchKernel). */
+int gint_execute(gint_ctx *ctx, uint64_t handle, const uint64_t *base_ptrs, int n_tensors, uint32_t grid_dim,
+                 void *cuda_stream);
+
+/* Same, restricted to logical programs [first, first + count) of the program's grid: the primitive used to
+ * shard one program over several GPUs by its leading dimension (each rank passes base pointers biased by its
+ * shard's byte offset). No counterpart in the reference, which is single-GPU. */
+int gint_execute_range(gint_ctx *ctx, uint64_t handle, const uint64_t *base_ptrs, int n_tensors, uint32_t first,
+                       uint32_t count, void *cuda_stream);
+
+/* One launch in which logical program i runs programs[indices[i]] with that program's own tensors.
+ * base_ptrs holds n_programs rows of GINT_MAX_TENSORS addresses. Replaces CudaExecutor.execute_indirect
+ * (gint/host/cuda/executor_impl.py:135-201). Uses context-owned scratch for the per-warp tables; may grow
+ * it (allocation) on a call with a larger batch than any before, so warm it up before stream capture. */
+int gint_execute_indirect(gint_ctx *ctx, const uint64_t *handles, int n_programs, const uint64_t *base_ptrs,
+                          const int32_t *indices, uint32_t grid_dim, void *cuda_stream);
+
+/* ---- tuning knobs (benchmarks / tests) ---------------------------------------------------------- */
+
+/* Force tiles-per-warp (0 = automatic) and row staging (-1 = automatic, 0 = off, 1 = on) for later launches. */
+int gint_set_option(gint_ctx *ctx, const char *name, int value);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* GINT_B200_H */
