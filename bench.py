@@ -1,0 +1,359 @@
+#!/usr/bin/env python
+"""Benchmark of the bytecode-interpreter hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--programs all|none]
+
+Headline workload: the conductor-lowered RMSNorm bytecode program over x fp32 [16384, 4096] (the configuration the
+metric is quoted on), one "step" = one pass of the program over the whole batch. With N > 1 (launched by torchrun, one
+process per GPU) the rows are split N ways, every rank runs its shard with no data-path collective, and the reported
+value is all ranks' bytes divided by the slowest rank's device time.
+
+Prints ONE JSON line. `value` is achieved HBM GB/s = algorithmic bytes / device time with inputs resident in HBM;
+`e2e` is the same metric through the public executor API with HOST buffers (pinned host -> device copy of the inputs and
+device -> host copy of the result inside the timed region). `roofline` relates the kernel to the measured copy bandwidth,
+`cpu_baseline` times the reference's CPU path (torch eager, the oracle its tests use) on a bounded sample of the same
+workload, and `programs` carries the other named programs for context.
+
+--impl reference runs only that CPU path, with the same metric and config, on this box's host cores.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+FALLBACK_HBM_GBS = 6650.0   # earlier measurement on this pool, used only when MEASURED_PEAKS.json is absent
+NOMINAL_HBM_GBS = 8000.0
+L2_BYTES = 126 * 1024 * 1024
+
+
+def measured_peak():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return FALLBACK_HBM_GBS, "fallback"
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device_index: int):
+        self.device_index = device_index
+        self.proc = None
+        self.lines: list[str] = []
+        self.thread = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                                          "-i", str(self.device_index), "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except Exception:
+            self.proc = None
+            return
+        self.thread = threading.Thread(target=self._pump, daemon=True)
+        self.thread.start()
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons, power = [], [], set(), []
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1]))
+                mx.append(float(parts[2]))
+                power.append(float(parts[3]))
+            except ValueError:
+                continue
+            for n, v in zip(names, parts[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def dist_setup(n_gpus: int):
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        import torch.distributed as dist
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29511")
+        torch.cuda.set_device(local)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    return rank, world, local
+
+
+def barrier(world: int):
+    if world > 1:
+        import torch.distributed as dist
+        dist.barrier()
+    torch.cuda.synchronize()
+
+
+def max_over_ranks(value: float, world: int) -> float:
+    if world == 1:
+        return value
+    import torch.distributed as dist
+    t = torch.tensor([value], dtype=torch.float64, device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def time_device(fn, steps: int, world: int) -> float:
+    """Milliseconds for `steps` calls of fn, CUDA events on the current stream, barrier + synchronize on both sides,
+    max over ranks."""
+    stream = torch.cuda.current_stream()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier(world)
+    start.record(stream)
+    for _ in range(steps):
+        fn()
+    stop.record(stream)
+    barrier(world)
+    return max_over_ranks(start.elapsed_time(stop), world)
+
+
+# ---------------------------------------------------------------------------------------------------- CPU baseline
+
+def cpu_reference(name: str, budget_s: float, steps: int = 1, warmup: int = 1):
+    """Times the reference's CPU path for `name` -- torch eager on fp32 CPU tensors with all host threads, the expression
+    the reference's tests use as their oracle -- on a bounded sample of the workload. Returns (GB/s, description, cores, ms)."""
+    from gint_b200.workloads import EAGER, FULL_SIZES, make_workload
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    full_leading, inner = FULL_SIZES[name]
+    sample = {"add": full_leading, "rmsnorm": 2048, "bmm4x4": 524288, "inv4x4": 524288, "graph": 8192}[name]
+    wl = make_workload(name, sample, inner, device="cpu")
+    fn = EAGER[name]
+    for _ in range(max(1, warmup)):
+        fn(wl.tensors)
+    times = []
+    t_end = time.perf_counter() + budget_s
+    while len(times) < max(steps, 1) or (time.perf_counter() < t_end and len(times) < 50):
+        t0 = time.perf_counter()
+        fn(wl.tensors)
+        times.append(time.perf_counter() - t0)
+        if len(times) >= steps and time.perf_counter() >= t_end:
+            break
+    best = min(times)
+    gbs = wl.algorithmic_bytes / best / 1e9
+    desc = f"torch eager fp32 on CPU, {sample} of {full_leading} leading units x {inner}, best of {len(times)}"
+    return gbs, desc, torch.get_num_threads(), statistics.mean(times) * 1e3, wl
+
+
+def oracle_port_speed(wl_cpu, budget_rows: int = 256):
+    """The C restatement of the interpreter (oracle/), timed on a few hundred logical programs: context for the
+    torch-eager baseline, not a baseline itself."""
+    from oracle import oracle
+    st = wl_cpu.steps[0]
+    grid = min(st.grid_dim, budget_rows)
+    threads = os.cpu_count() or 1
+    t0 = time.perf_counter()
+    oracle.execute(st.program.bytecode, [vars(t) for t in st.program.tensor_infos], [wl_cpu.tensors[r] for r in st.roles], grid,
+                   input_indices=st.program.input_indices, threads=threads)
+    dt = time.perf_counter() - t0
+    bytes_ = wl_cpu.algorithmic_bytes * grid / st.grid_dim
+    return {"value": bytes_ / dt / 1e9, "unit": "GB/s", "cores": threads, "kind": "port",
+            "sample": f"{grid} logical programs of the same bytecode through oracle/gint_oracle.c"}
+
+
+# ---------------------------------------------------------------------------------------------------- GPU side
+
+def run_program_bench(name: str, world: int, rank: int, steps: int, warmup: int, peak_gbs: float):
+    """Device-resident timing of one named program at its benchmark size (sharded `world` ways)."""
+    from gint_b200 import get_executor
+    from gint_b200.workloads import FULL_SIZES, make_workload
+    ex = get_executor()
+    leading, inner = FULL_SIZES[name]
+    leading //= world
+    seed = 42 + rank
+    # a+b is 12 MB and would sit in L2: rotate over enough independent buffer sets to exceed it
+    n_sets = 1
+    wls = [make_workload(name, leading, inner, device="cuda", seed=seed)]
+    if wls[0].algorithmic_bytes < 2 * L2_BYTES:
+        n_sets = int(2 * L2_BYTES // wls[0].algorithmic_bytes) + 1
+        wls += [make_workload(name, leading, inner, device="cuda", seed=seed + 1000 + i) for i in range(n_sets - 1)]
+    stream = torch.cuda.current_stream().cuda_stream
+    state = {"i": 0}
+
+    def step():
+        wls[state["i"] % n_sets].run(ex, stream)
+        state["i"] += 1
+    for _ in range(max(3, warmup)):
+        step()
+    launches0 = ex.launches
+    ms = time_device(step, steps, world)
+    launches = ex.launches - launches0
+    wl = wls[0]
+    total_bytes = wl.algorithmic_bytes * world
+    per_step_ms = ms / steps
+    st = wl.steps[0]
+    info = ex.launch_info(st.program, [wl.tensors[r] for r in st.roles], st.grid_dim)
+    return {
+        "ms_per_step": per_step_ms,
+        "gbs": total_bytes / (per_step_ms * 1e-3) / 1e9,
+        "elements_per_s": wl.elements * world / (per_step_ms * 1e-3),
+        "algorithmic_bytes": total_bytes,
+        "launches": launches,
+        "launches_per_step": wl.launches_per_run(),
+        "l2": "inputs larger than L2" if n_sets == 1 else f"rotating {n_sets} buffer sets (> 2x L2)",
+        "geometry": {k: info[k] for k in ("pool_size", "tiles_per_warp", "grid_blocks", "regs_per_thread", "blocks_per_sm", "smem_bytes")},
+        "frac_of_measured_peak": total_bytes / (per_step_ms * 1e-3) / 1e9 / (peak_gbs * world),
+        "frac_of_8TBs": total_bytes / (per_step_ms * 1e-3) / 1e9 / (NOMINAL_HBM_GBS * world),
+    }, wls
+
+
+def run_e2e(name: str, world: int, rank: int, steps: int, warmup: int):
+    """Same metric through the public API with HOST buffers: every step copies the inputs from pinned host memory,
+    runs the program and copies the result back."""
+    from gint_b200 import get_executor
+    from gint_b200.workloads import FULL_SIZES, make_workload
+    ex = get_executor()
+    leading, inner = FULL_SIZES[name]
+    leading //= world
+    wl = make_workload(name, leading, inner, device="cuda", seed=42 + rank)
+    in_roles = [r for r in wl.tensors if r not in wl.outputs and r not in ("g", "x_rows")]
+    host_in = {r: wl.tensors[r].cpu().pin_memory() for r in in_roles}
+    host_out = {r: torch.empty(wl.tensors[r].shape, dtype=wl.tensors[r].dtype).pin_memory() for r in wl.outputs}
+    stream = torch.cuda.current_stream().cuda_stream
+    h2d = sum(t.numel() * t.element_size() for t in host_in.values())
+    d2h = sum(t.numel() * t.element_size() for t in host_out.values())
+
+    def step():
+        for r in in_roles:
+            wl.tensors[r].copy_(host_in[r], non_blocking=True)
+        wl.run(ex, stream)
+        for r in wl.outputs:
+            host_out[r].copy_(wl.tensors[r], non_blocking=True)
+    for _ in range(max(1, min(warmup, 3))):
+        step()
+    ms = time_device(step, steps, world)
+    per_step = ms / steps
+    return {"value": wl.algorithmic_bytes * world / (per_step * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": per_step,
+            "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--workload", default="rmsnorm", choices=["add", "rmsnorm", "bmm4x4", "inv4x4", "graph"])
+    ap.add_argument("--programs", default="all", choices=["all", "none"], help="also time the other named programs")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    opts = ap.parse_args()
+    warmup = max(opts.warmup, 3)
+    peak, peak_kind = measured_peak()
+    metric = "achieved HBM GB/s per bytecode program (algorithmic bytes / device time)"
+    name = opts.workload
+    from gint_b200.workloads import FULL_SIZES
+    leading, inner = FULL_SIZES[name]
+    config = {"workload": {"add": "configs[0] a+b fp32 [1048576]", "rmsnorm": "configs[1] RMSNorm x fp32 [16384,4096], conductor-lowered bytecode (363 insns)",
+                           "bmm4x4": "configs[2] batched 4x4 matmul [4194304,4,4]", "inv4x4": "configs[3] batched 4x4 inverse [4194304,4,4]",
+                           "graph": "configs[4] conductor graph x [65536,1024]"}[name],
+              "leading": leading, "inner": inner, "sharding": f"rows split {opts.gpus} ways, no collective"}
+
+    if opts.impl == "reference":
+        rank = int(os.environ.get("RANK", "0"))
+        if rank != 0:
+            return 0
+        gbs, desc, cores, ms, _ = cpu_reference(name, budget_s=20.0, steps=opts.steps if opts.steps < 20 else 20, warmup=min(warmup, 3))
+        line = {"impl": "reference", "metric": metric, "value": gbs, "unit": "GB/s", "n_gpus": opts.gpus, "steps": opts.steps,
+                "warmup": warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+                "data": "synthetic (seeded)", "config": config,
+                "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": cores, "kind": "reference", "sample": desc},
+                "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+                "note": "the reference has no CPU bytecode executor; its CPU path for these programs is the torch-eager "
+                        "expression its tests use as oracle"}
+        print(json.dumps(line))
+        return 0
+
+    if not torch.cuda.is_available():
+        print(json.dumps({"error": "no CUDA device: gint_b200 has no CPU path"}))
+        return 1
+    rank, world, local = dist_setup(opts.gpus)
+    torch.cuda.set_device(local)
+
+    sampler = ClockSampler(local) if rank == 0 else None
+    if sampler:
+        sampler.start()
+    res, wls = run_program_bench(name, world, rank, opts.steps, warmup, peak)
+    clocks = sampler.stop() if sampler else None
+    del wls
+    torch.cuda.empty_cache()
+    e2e = run_e2e(name, world, rank, max(3, min(opts.steps, 10)), warmup)
+    torch.cuda.empty_cache()
+
+    programs = {}
+    if opts.programs == "all":
+        for other in ("add", "rmsnorm", "bmm4x4", "inv4x4", "graph"):
+            if other == name:
+                programs[other] = res
+                continue
+            r, w_ = run_program_bench(other, world, rank, max(10, min(opts.steps, 30)), warmup, peak)
+            programs[other] = r
+            del w_
+            torch.cuda.empty_cache()
+
+    if rank == 0:
+        line = {
+            "metric": metric, "value": res["gbs"], "unit": "GB/s", "n_gpus": world, "steps": opts.steps, "warmup": warmup,
+            "ms_per_step": res["ms_per_step"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f32", "data": "synthetic (seeded)",
+            "config": dict(config, l2=res["l2"], elements_per_s=res["elements_per_s"], geometry=res["geometry"]),
+            "clocks": clocks, "e2e": e2e, "gpu_launches": res["launches"],
+            "roofline": {"bound": "hbm", "achieved": res["gbs"] / world, "peak": peak, "unit": "GB/s",
+                         "frac": res["gbs"] / world / peak, "peak_kind": f"of {peak_kind}", "frac_of_8TBs": res["frac_of_8TBs"],
+                         "traffic": None, "algorithmic_bytes_per_launch": res["algorithmic_bytes"] // world,
+                         "kernel_ms": res["ms_per_step"] / res["launches_per_step"]},
+            "programs": {k: {kk: vv for kk, vv in v.items() if kk not in ("launches",)} for k, v in programs.items()},
+        }
+        if not opts.no_cpu:
+            gbs, desc, cores, ms, wl_cpu = cpu_reference(name, budget_s=10.0)
+            line["cpu_baseline"] = {"value": gbs, "unit": "GB/s", "cores": cores, "kind": "reference", "sample": desc}
+            try:
+                line["cpu_oracle_port"] = oracle_port_speed(wl_cpu)
+            except Exception as e:  # the port is context only
+                line["cpu_oracle_port"] = {"error": str(e)}
+        print(json.dumps(line))
+    if world > 1:
+        import torch.distributed as dist
+        dist.barrier()
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,216 @@
+"""Executor-level behaviour on the GPU: the drop-in surface of gint.host (errors, caching, streams, CUDA-graph capture,
+indirect dispatch, range launches for sharding)."""
+import ctypes
+
+import numpy as np
+import pytest
+import torch
+
+import cases as C
+from conftest import bits_equal, mismatch_report
+from gint_b200 import ProgramData, ProgramTensorInfo, TensorInterface, bytecode, cdiv, get_executor
+from gint_b200.host import capi
+from gint_b200.host.executor import BaseExecutableProgram, _convert_arg
+from gint_b200.host.frontend import *  # noqa: F401,F403
+from gint_b200.programs import recorded
+from oracle import oracle
+
+pytestmark = pytest.mark.gpu
+
+
+def test_wrong_argument_count_raises_value_error():
+    # reference: gint/host/cuda/executor_impl.py:93-94
+    a = torch.zeros(256, device="cuda")
+    with pytest.raises(ValueError, match="Number of arguments"):
+        get_executor().execute(recorded("add_n4096"), [_convert_arg(a)] * 2, 1)
+
+
+def test_invalid_programs_raise_before_any_launch():
+    class Bad(BaseExecutableProgram):
+        def __init__(self, bc):
+            self.bc = bc
+
+        def get_program(self, *args):
+            return ProgramData(np.array(self.bc, dtype=np.int32).reshape(-1),
+                               [ProgramTensorInfo(4, [], [], [128, 1], [1, 0], [1, 1], [0, 0])])
+    x = torch.zeros(128, device="cuda")
+    with pytest.raises(ValueError, match="unknown opcode"):
+        Bad([[200, 0], [0, 0]])(x, grid_dim=1)
+    with pytest.raises(ValueError, match="needs depth"):
+        Bad([[FAdd, 0], [0, 0]])(x, grid_dim=1)
+    with pytest.raises(ValueError):                      # deeper than any kernel geometry
+        Bad([[LoadImm, 0]] * 9 + [[0, 0]])(x, grid_dim=1)
+    with pytest.raises(Exception):                       # tensor slot 3 of a 1-tensor program
+        Bad([[LoadGlobal1DF32, 3], [Pop, 0], [0, 0]])(x, grid_dim=1)
+    torch.cuda.synchronize()
+    assert torch.equal(x, torch.zeros(128, device="cuda"))
+
+
+def test_program_is_built_once_per_cache_key():
+    prog = C.VectorAddProgram()
+    calls = []
+    orig = prog.get_program
+    prog.get_program = lambda *a, **k: (calls.append(1), orig(*a, **k))[1]
+    a, b, c = (torch.randn(1000, device="cuda") for _ in range(3))
+    for _ in range(3):
+        prog(a, b, c, grid_dim=cdiv(1000, 256))
+    a2, b2, c2 = (torch.randn(500, device="cuda") for _ in range(3))
+    prog(a2, b2, c2, grid_dim=cdiv(500, 256))
+    torch.cuda.synchronize()
+    assert len(calls) == 2                               # one per shape, as with program._cu in the reference
+    torch.testing.assert_close(c, a + b)
+    torch.testing.assert_close(c2, a2 + b2)
+
+
+def test_launch_on_a_side_stream_is_ordered_with_it():
+    s = torch.cuda.Stream()
+    a, b = torch.randn(1 << 20, device="cuda"), torch.randn(1 << 20, device="cuda")
+    c = torch.zeros(1 << 20, device="cuda")
+    torch.cuda.synchronize()
+    with torch.cuda.stream(s):
+        a2 = a * 2                                        # producer on s
+        C.VectorAddProgram()(a2, b, c, grid_dim=cdiv(1 << 20, 256), cuda_stream=s.cuda_stream)
+        out = c + 1                                       # consumer on s
+    s.synchronize()
+    torch.testing.assert_close(out, a * 2 + b + 1)
+
+
+def test_cuda_graph_capture_and_replay():
+    """Mirror of the reference's tests/test_cuda_graph_capture.py:31-65."""
+    def cubic_ease(x):
+        shape = x.shape
+        x = x.view(-1)
+        y = torch.empty_like(x)
+        C.vector_expr2(x, y, grid_dim=cdiv(len(x), 256), BLOCK=256, cuda_stream=torch.cuda.current_stream().cuda_stream)
+        return (x ** 2 * (3 - 2 * x)).view(shape), y.view(shape)
+
+    torch.manual_seed(42)
+    x1 = torch.rand(12938, 3, device="cuda")
+    x2 = torch.rand(12938, 3, device="cuda")
+    graphed = torch.cuda.make_graphed_callables(cubic_ease, (x2,))
+    r1, y1 = graphed(x1)
+    r1, y1 = r1.clone(), y1.clone()
+    r2, y2 = graphed(x2)
+    torch.testing.assert_close(y1, x1 ** 2 * (3 - 2 * x1))
+    torch.testing.assert_close(y2, x2 ** 2 * (3 - 2 * x2))
+    torch.testing.assert_close(r2, x2 ** 2 * (3 - 2 * x2))
+    # an eager call in between must not disturb what the graph captured (descriptors are kernel parameters)
+    _, ye = cubic_ease(torch.rand(12938, 3, device="cuda"))
+    _, y1b = graphed(x1)
+    torch.testing.assert_close(y1b, x1 ** 2 * (3 - 2 * x1))
+
+
+def test_manual_graph_capture_allocates_nothing():
+    a, b, c = (torch.randn(4096, device="cuda") for _ in range(3))
+    prog = recorded("add_n4096")
+    args = [_convert_arg(t) for t in (c, a, b)]           # roles: out, a, b
+    ex = get_executor()
+    s = torch.cuda.Stream()
+    with torch.cuda.stream(s):
+        ex.execute(prog, args, prog.grid_dim, cuda_stream=s.cuda_stream)   # warm-up: builds the program
+    s.synchronize()
+    g = torch.cuda.CUDAGraph()
+    before = torch.cuda.memory_allocated()
+    with torch.cuda.graph(g, stream=s):
+        ex.execute(prog, args, prog.grid_dim, cuda_stream=torch.cuda.current_stream().cuda_stream)
+    assert torch.cuda.memory_allocated() == before
+    c.zero_()
+    a.copy_(torch.arange(4096.0, device="cuda"))
+    g.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(c, a + b)
+
+
+def test_indirect_dispatch_two_programs_one_launch():
+    """Mirror of the reference's tests/test_indirect.py:34-62, plus a bit-exact check against the oracle's indirect mode."""
+    ex = get_executor()
+    N = 128 * 5
+    g = torch.Generator().manual_seed(0)
+    host = [[torch.randn(N, generator=g), torch.randn(N, generator=g), torch.zeros(N)] for _ in range(2)]
+    dev = [[t.cuda() for t in ts] for ts in host]
+    wpp = cdiv(N, 128)
+    # warp i decodes its descriptors with logical index i (main.py:182-194); with a 5-tile grid, i % 5 is the tile, so
+    # warps 0..4 run program 0 over tiles 0..4 and warps 5..9 run program 1 over tiles 0..4
+    indices = [0] * wpp + [1] * wpp
+    ex.execute_indirect(programs=[C.vec_add_128, C.vec_mul_128], args_list=dev, indices=indices)
+    torch.cuda.synchronize()
+    pds = [p.get_program(*[_convert_arg(t) for t in ts]) for p, ts in zip((C.vec_add_128, C.vec_mul_128), host)]
+    oracle.execute_indirect([pd.program for pd in pds], [[vars(t) for t in pd.input_infos] for pd in pds], host, indices,
+                            [pd.input_indices for pd in pds])
+    for p in range(2):
+        assert bits_equal(dev[p][2], host[p][2]), mismatch_report(dev[p][2], host[p][2])
+    torch.testing.assert_close(dev[0][2], dev[0][0] + dev[0][1])
+    torch.testing.assert_close(dev[1][2], dev[1][0] * dev[1][1])
+
+
+def test_indirect_dispatch_single_tile_programs():
+    """The shape the reference's test uses: N = 128, one warp per program, add then mul."""
+    ex = get_executor()
+    a1, b1, a2, b2 = (torch.randn(128, device="cuda") for _ in range(4))
+    c1, c2 = torch.zeros(128, device="cuda"), torch.zeros(128, device="cuda")
+    # both programs address tile 0 only when their logical index is 0; use one launch per order to cover both
+    ex.execute_indirect([C.vec_add_128], [(a1, b1, c1)], [0])
+    ex.execute_indirect([C.vec_mul_128, C.vec_add_128], [(a2, b2, c2), (a1, b1, c1)], [0])
+    torch.cuda.synchronize()
+    torch.testing.assert_close(c1, a1 + b1)
+    torch.testing.assert_close(c2, a2 * b2)
+
+
+def test_indirect_many_programs():
+    """Many distinct tiny programs in one launch (the superoptimizer's usage pattern): program p computes x * p + p."""
+    ex = get_executor()
+
+    def make(p):
+        @bytecode
+        def prog(x, y, REGW, WARP):
+            xb = make_block_1d(x, 128, 1, 4096, 0)       # every logical program reads the same tile
+            yb = make_block_1d(y, 128 * 300, 1, 300, 128)
+            fldg_1d(0, xb)
+            fmulimm(float(p))
+            faddimm(float(p))
+            fstg_1d(0, yb)
+            halt()
+        return prog
+    n = 300
+    x = torch.randn(128, device="cuda")
+    y = torch.zeros(n * 128, device="cuda")
+    ex.execute_indirect([make(p) for p in range(n)], [(x, y)] * n, list(range(n)))
+    torch.cuda.synchronize()
+    ref = torch.stack([x * p + p for p in range(n)]).reshape(-1)
+    assert torch.equal(y, ref)
+
+
+def test_execute_range_shards_cover_the_grid():
+    """Two half-range launches with biased base pointers give the same bits as one full launch: the multi-GPU
+    sharding primitive, exercised on one device."""
+    from gint_b200.workloads import make_workload
+    ex = get_executor()
+    full = make_workload("rmsnorm", 64, 4096, device="cuda")
+    full.run(ex)
+    torch.cuda.synchronize()
+    want = full.tensors["out"].clone()
+    st = full.steps[0]
+    # shard s owns rows [32 s, 32 s + 32) in its own buffers; pointers are biased so the program's global row r maps there
+    for s in range(2):
+        rows = slice(32 * s, 32 * s + 32)
+        x_loc = full.tensors["x"][rows].clone()
+        out_loc = torch.zeros(32, 4096, device="cuda")
+        bias = 32 * s * 4096 * 4
+        t = {"x": TensorInterface("f", 4, x_loc.data_ptr() - bias, (), ()), "w": _convert_arg(full.tensors["w"]),
+             "out": TensorInterface("f", 4, out_loc.data_ptr() - bias, (), ())}
+        ex.execute_range(st.program, [t[r] for r in st.roles], 32 * s, 32)
+        torch.cuda.synchronize()
+        assert torch.equal(out_loc, want[rows])
+
+
+def test_launch_info_reports_geometry():
+    from gint_b200.workloads import make_workload
+    ex = get_executor()
+    for name, pool in (("rmsnorm", 4), ("bmm4x4", 7), ("inv4x4", 12)):
+        wl = make_workload(name, {"rmsnorm": 64}.get(name, 1000), {"rmsnorm": 4096}.get(name, 16), device="cuda")
+        st = wl.steps[0]
+        info = ex.launch_info(st.program, [wl.tensors[r] for r in st.roles], st.grid_dim)
+        assert info["pool_size"] == pool
+        assert info["tiles_per_warp"] in (1, 2, 4)
+        assert info["num_sms"] == torch.cuda.get_device_properties(0).multi_processor_count
+        assert info["grid_blocks"] >= 1 and info["regs_per_thread"] > 0 and info["smem_bytes"] > 0
