@@ -86,19 +86,23 @@ uint32_t clamp_lane_bytes(uint32_t operand)
     return r;
 }
 
-/* {key, operand} pairs: key = depth-before * N_OPCODES + opcode. Width-lane selectors are clamped to 0..3, which is
- * what the reference's compare tree computes for any operand (gint/kernel/interpreter/instructions/move.py:58-66). */
-int predecode(const int32_t *code, int n_words, int n_tensors, std::vector<uint2> *out)
+/* Pre-decoded stream, skewed for threaded dispatch: entry 0 = {0, opcode of insn 0}; entry i+1 = {operand of insn i,
+ * opcode of insn i+1}; the opcode after the final Halt is Halt again. The stack depth before every instruction is static
+ * (straight-line code) and is baked into the handlers, not the stream. Width-lane
+ * selectors are clamped to 0..3, which is what the reference's compare tree computes for any operand
+ * (gint/kernel/interpreter/instructions/move.py:58-66). */
+int predecode(const int32_t *code, int n_words, int n_tensors, std::vector<uint2> *out, std::vector<int> *depth_out = nullptr)
 {
     gint_bytecode_stats st;
     int rc = analyze(code, n_words, &st);
     if (rc != GINT_OK) return rc;
-    out->clear();
-    out->reserve((size_t)st.num_instructions + 3);
+    const int n = st.num_instructions + 1;  // including the Halt
+    std::vector<uint32_t> keys((size_t)n + 1), operands((size_t)n);
+    std::vector<int> depths((size_t)n + 1, 0);
     int depth = 0;
-    for (int i = 0; i < st.num_instructions; i++) {
-        const int op = code[2 * i];
-        uint32_t operand = (uint32_t)code[2 * i + 1];
+    for (int i = 0; i < n; i++) {
+        const int op = i < st.num_instructions ? code[2 * i] : OP_Halt;
+        uint32_t operand = i < st.num_instructions ? (uint32_t)code[2 * i + 1] : 0u;
         if (is_tensor_op(op) && (int)(operand & 15u) >= n_tensors) return GINT_ERR_INVALID_ARGUMENT;
         if (op == OP_DupBroadcastW) {
             const int32_t s = (int32_t)operand;
@@ -106,21 +110,70 @@ int predecode(const int32_t *code, int n_words, int n_tensors, std::vector<uint2
         } else if (op == OP_FPermW || op == OP_FShuf2) {
             operand = clamp_lane_bytes(operand);
         }
-        out->push_back(make_uint2((uint32_t)(depth * GINT_N_OPCODES + op), operand));
+        keys[(size_t)i] = (uint32_t)op;
+        depths[(size_t)i] = depth;
+        operands[(size_t)i] = operand;
         depth += kEffects[op].net;
     }
-    out->push_back(make_uint2((uint32_t)(depth * GINT_N_OPCODES + OP_Halt), 0u));
-    out->push_back(make_uint2(OP_Halt, 0u));  // the interpreter fetches one instruction ahead
-    if (out->size() & 1) out->push_back(make_uint2(OP_Halt, 0u));
+    keys[(size_t)n] = OP_Halt;
+    out->clear();
+    out->reserve((size_t)n + 4);
+    out->push_back(make_uint2(0u, keys[0]));
+    for (int i = 0; i < n; i++) out->push_back(make_uint2(operands[(size_t)i], keys[(size_t)i + 1]));
+    out->push_back(make_uint2(0u, OP_Halt));  // handlers fetch one entry ahead
+    if (out->size() & 1) out->push_back(make_uint2(0u, OP_Halt));
+    if (depth_out) *depth_out = depths;
     return GINT_OK;
 }
 
 struct Variant {
     int P, K;
-    const void *fn;
+    const void *fn;   // cudaKernel_t of the loaded cubin, usable wherever the runtime takes a kernel function
     int regs;
     bool ok;
 };
+
+/* The embedded cubins are loaded once per process (a cudaLibrary_t is not tied to a device or context). */
+struct KernelImage {
+    const unsigned char *begin;
+    const unsigned char *end;
+    const char *name;
+    int P, K;          // K == 0: indirect kernel
+    cudaLibrary_t lib;
+    cudaKernel_t kernel;
+    bool loaded;
+};
+
+KernelImage g_images[] = {
+#define GINT_X_IMG(P, K) {gint_cubin_direct_##P##_##K, gint_cubin_direct_##P##_##K##_end, "gint_geval_direct_" #P "_" #K, P, K, nullptr, nullptr, false},
+    GINT_DIRECT_VARIANTS(GINT_X_IMG)
+#undef GINT_X_IMG
+#define GINT_X_IMG(P) {gint_cubin_indirect_##P, gint_cubin_indirect_##P##_end, "gint_geval_indirect_" #P, P, 0, nullptr, nullptr, false},
+    GINT_INDIRECT_VARIANTS(GINT_X_IMG)
+#undef GINT_X_IMG
+};
+std::mutex g_images_mu;
+std::string g_images_error;
+
+int load_images()
+{
+    std::lock_guard<std::mutex> lk(g_images_mu);
+    int usable = 0;
+    for (auto &im : g_images) {
+        if (!im.loaded) {
+            cudaError_t e = cudaLibraryLoadData(&im.lib, im.begin, nullptr, nullptr, 0, nullptr, nullptr, 0);
+            if (e == cudaSuccess) e = cudaLibraryGetKernel(&im.kernel, im.lib, im.name);
+            if (e != cudaSuccess) {
+                g_images_error = std::string(im.name) + ": " + cudaGetErrorName(e) + " (" + cudaGetErrorString(e) + ")";
+                cudaGetLastError();
+                continue;
+            }
+            im.loaded = true;
+        }
+        usable++;
+    }
+    return usable;
+}
 
 struct Program {
     bool live = false;
@@ -308,14 +361,15 @@ int gint_analyze(const int32_t *code, int n_words, gint_bytecode_stats *out) { r
 int gint_predecode(const int32_t *code, int n_words, uint32_t *out_keys, int max_keys)
 {
     std::vector<uint2> pre;
-    int rc = predecode(code, n_words, GINT_MAX_TENSORS, &pre);
+    std::vector<int> depths;
+    int rc = predecode(code, n_words, GINT_MAX_TENSORS, &pre, &depths);
     if (rc != GINT_OK) return rc;
     gint_bytecode_stats st;
     analyze(code, n_words, &st);
     const int n = st.num_instructions + 1;
     if (out_keys) {
         if (max_keys < n) return GINT_ERR_INVALID_ARGUMENT;
-        for (int i = 0; i < n; i++) out_keys[i] = pre[(size_t)i].x;
+        for (int i = 0; i < n; i++) out_keys[i] = (uint32_t)depths[(size_t)i] * GINT_N_OPCODES + pre[(size_t)i].y;
     }
     return n;
 }
@@ -336,10 +390,15 @@ int gint_create(int device, gint_ctx **out)
     ctx->device = device;
     ctx->num_sms = prop.multiProcessorCount;
     ctx->max_smem_optin = (int)prop.sharedMemPerBlockOptin;
-#define GINT_X_VAR(P, K) ctx->direct.push_back(Variant{P, K, gint_kernel_direct_##P##_##K(), 0, false});
-    GINT_DIRECT_VARIANTS(GINT_X_VAR)
-#undef GINT_X_VAR
-    ctx->indirect.fn = gint_kernel_indirect_12();
+    if (load_images() == 0) {  // the library carries sm_100a code only
+        delete ctx;
+        return GINT_ERR_NO_DEVICE;
+    }
+    for (auto &im : g_images) {
+        if (!im.loaded) continue;
+        if (im.K == 0) ctx->indirect.fn = (const void *)im.kernel;
+        else ctx->direct.push_back(Variant{im.P, im.K, (const void *)im.kernel, 0, false});
+    }
     int usable = 0;
     for (auto &v : ctx->direct) {
         cudaFuncAttributes attr;
@@ -347,12 +406,12 @@ int gint_create(int device, gint_ctx **out)
         if (e == cudaSuccess) { v.regs = attr.numRegs; v.ok = true; usable++; }
         else cudaGetLastError();
     }
-    {
+    if (ctx->indirect.fn) {
         cudaFuncAttributes attr;
         if (cudaFuncGetAttributes(&attr, ctx->indirect.fn) == cudaSuccess) { ctx->indirect.regs = attr.numRegs; ctx->indirect.ok = true; }
         else cudaGetLastError();
     }
-    if (usable == 0) {  // the library carries sm_100a code only
+    if (usable == 0) {
         delete ctx;
         return GINT_ERR_NO_DEVICE;
     }
@@ -466,11 +525,17 @@ int gint_execute_indirect(gint_ctx *ctx, const uint64_t *handles, int n_programs
     if (!ctx->indirect.ok) return fail(ctx, GINT_ERR_NO_DEVICE, "indirect kernel image not usable on this device");
     std::vector<Program *> progs((size_t)n_programs);
     int max_tensors = 0;
+    uint32_t max_slots = 0;
     for (int i = 0; i < n_programs; i++) {
         progs[(size_t)i] = lookup(ctx, handles[i]);
         if (!progs[(size_t)i]) return fail(ctx, GINT_ERR_BAD_HANDLE, "unknown program handle");
         if (progs[(size_t)i]->n_tensors > max_tensors) max_tensors = progs[(size_t)i]->n_tensors;
+        if (progs[(size_t)i]->n_slots > max_slots) max_slots = progs[(size_t)i]->n_slots;
     }
+    /* each warp keeps its own program in shared memory */
+    const uint32_t code_smem = (max_slots * 8u + 127u) & ~127u;
+    const uint32_t smem = (uint32_t)gint::kWarpsPerBlock * ((uint32_t)sizeof(gint::TileInfo) + (uint32_t)gint::kTensorInfoSmemBytes + code_smem);
+    if ((int)smem > ctx->max_smem_optin) return fail(ctx, GINT_ERR_TOO_LARGE, "a program of this batch is too long for indirect mode (shared memory)");
     for (uint32_t i = 0; i < grid_dim; i++)
         if (indices[i] < 0 || indices[i] >= n_programs) return fail(ctx, GINT_ERR_INVALID_ARGUMENT, "program index out of range");
 
@@ -507,6 +572,8 @@ int gint_execute_indirect(gint_ctx *ctx, const uint64_t *handles, int n_programs
     for (uint32_t i = 0; i < grid_dim; i++) {
         h_tab[i].code = progs[(size_t)indices[i]]->code_dev;
         h_tab[i].ti = d_ti + indices[i];
+        h_tab[i].n_slots = progs[(size_t)indices[i]]->n_slots;
+        h_tab[i].reserved = 0;
     }
     cudaError_t e = cudaMemcpyAsync(ctx->ind_dev, ctx->ind_host, need, cudaMemcpyHostToDevice, stream);
     if (e != cudaSuccess) return fail(ctx, GINT_ERR_CUDA, "cudaMemcpyAsync(indirect tables)", e);
@@ -516,7 +583,12 @@ int gint_execute_indirect(gint_ctx *ctx, const uint64_t *handles, int n_programs
     a.table = (const IndirectEntry *)((const char *)ctx->ind_dev + ti_bytes);
     a.n_tensors = (uint32_t)max_tensors;
     a.grid_dim = grid_dim;
-    const uint32_t smem = (uint32_t)(gint::kWarpsPerBlock * sizeof(gint::TileInfo));
+    a.code_smem_bytes = code_smem;
+    a.reserved = 0;
+    if (smem > 48u * 1024u) {
+        e = cudaFuncSetAttribute(ctx->indirect.fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return fail(ctx, GINT_ERR_CUDA, "cudaFuncSetAttribute(indirect)", e);
+    }
     int bps = 0;
     e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&bps, ctx->indirect.fn, gint::kThreadsPerBlock, smem);
     if (e != cudaSuccess || bps < 1) return fail(ctx, GINT_ERR_CUDA, "occupancy query (indirect)", e);

@@ -29,9 +29,24 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <utility>
+
 #include "../../include/gint_b200.h"
 #include "gint_opcodes.h"
 #include "gint_types.h"
+
+/* GINT_GUARD: debugging aid for changes to the dispatch machinery. Every handler decrements an instruction budget (the
+ * number of stream entries) and the interpreter returns when it runs out, so a mis-wired jump table cannot spin forever. */
+#ifdef GINT_GUARD
+#define GINT_GUARD_STEP                                                                                               \
+    {                                                                                                                 \
+        uint32_t left;                                                                                                \
+        asm volatile("sub.u32 %%gbudget, %%gbudget, 1; mov.u32 %0, %%gbudget;" : "=r"(left));                         \
+        if ((int)left < 0) return;                                                                                    \
+    }
+#else
+#define GINT_GUARD_STEP
+#endif
 
 namespace gint {
 
@@ -348,7 +363,99 @@ __device__ __forceinline__ void decode_tiles(const gint_tensor_info *__restrict_
 }
 
 /* ------------------------------------------------------------------------------------------------ */
-/* one instruction at one stack depth                                                                */
+/* the register pool                                                                                  */
+/*
+ * The operand stack and the virtual registers are 2*P*K 64-bit PTX registers %gs0 .. %gs(2PK-1), declared once at the
+ * top of the kernel and touched only from inline asm, by name. Slot s of tile k is the pair
+ * (%gs[(s*K+k)*2], %gs[(s*K+k)*2+1]) = width lanes (0,1) and (2,3). Keeping them out of the C++ value world matters:
+ * as C++ variables they are loop-carried through a ~950-way switch, and the compiler's phi copies for every slot on
+ * every path (which ptxas does not coalesce across the jump table) cost more than the handlers themselves.
+ */
+
+template <int P, int K> __device__ __forceinline__ void pool_declare()
+{
+    asm volatile(".reg .b64 %%gs<%0>;" ::"n"(2 * P * K));
+}
+
+template <int I> __device__ __forceinline__ void r_get(float &x, float &y)
+{
+    asm volatile("mov.b64 {%0, %1}, %%gs%2;" : "=f"(x), "=f"(y) : "n"(I));
+}
+template <int I> __device__ __forceinline__ void r_set(float x, float y)
+{
+    asm volatile("mov.b64 %%gs%2, {%0, %1};" ::"f"(x), "f"(y), "n"(I));
+}
+template <int I> __device__ __forceinline__ void r_set64(u64 v)
+{
+    asm volatile("mov.b64 %%gs%1, %0;" ::"l"(v), "n"(I));
+}
+template <int D, int A> __device__ __forceinline__ void r_mov()
+{
+    if constexpr (D != A) asm volatile("mov.b64 %%gs%0, %%gs%1;" ::"n"(D), "n"(A));
+}
+template <int A, int B> __device__ __forceinline__ void r_swap()
+{
+    asm volatile("{ .reg .b64 t; mov.b64 t, %%gs%0; mov.b64 %%gs%0, %%gs%1; mov.b64 %%gs%1, t; }" ::"n"(A), "n"(B));
+}
+template <int D, int A, int B> __device__ __forceinline__ void r_add2()
+{
+    asm volatile("add.rn.f32x2 %%gs%0, %%gs%1, %%gs%2;" ::"n"(D), "n"(A), "n"(B));
+}
+template <int D, int A, int B> __device__ __forceinline__ void r_sub2()
+{
+    asm volatile("sub.rn.f32x2 %%gs%0, %%gs%1, %%gs%2;" ::"n"(D), "n"(A), "n"(B));
+}
+template <int D, int A, int B> __device__ __forceinline__ void r_mul2()
+{
+    asm volatile("mul.rn.f32x2 %%gs%0, %%gs%1, %%gs%2;" ::"n"(D), "n"(A), "n"(B));
+}
+template <int D, int A, int B, int C> __device__ __forceinline__ void r_fma2()
+{
+    asm volatile("fma.rn.f32x2 %%gs%0, %%gs%1, %%gs%2, %%gs%3;" ::"n"(D), "n"(A), "n"(B), "n"(C));
+}
+template <int D> __device__ __forceinline__ void r_add2_imm(u64 imm)
+{
+    asm volatile("add.rn.f32x2 %%gs%0, %%gs%0, %1;" ::"n"(D), "l"(imm));
+}
+template <int D> __device__ __forceinline__ void r_mul2_imm(u64 imm)
+{
+    asm volatile("mul.rn.f32x2 %%gs%0, %%gs%0, %1;" ::"n"(D), "l"(imm));
+}
+template <int D> __device__ __forceinline__ void r_fma2_imm(u64 m, u64 c)
+{
+    asm volatile("fma.rn.f32x2 %%gs%0, %%gs%0, %1, %2;" ::"n"(D), "l"(m), "l"(c));
+}
+template <int D> __device__ __forceinline__ void r_neg2()
+{
+    asm volatile("xor.b64 %%gs%0, %%gs%0, 0x8000000080000000;" ::"n"(D));
+}
+
+/* index of the low (h = 0) / high (h = 1) pair of slot `slot`, tile `k` */
+template <int K> __host__ __device__ constexpr int gs(int slot, int k, int h) { return (slot * K + k) * 2 + h; }
+
+template <int K, int SLOT, int KI> __device__ __forceinline__ void slot_read(float (&v)[4])
+{
+    r_get<gs<K>(SLOT, KI, 0)>(v[0], v[1]);
+    r_get<gs<K>(SLOT, KI, 1)>(v[2], v[3]);
+}
+template <int K, int SLOT, int KI> __device__ __forceinline__ void slot_write(const float (&v)[4])
+{
+    r_set<gs<K>(SLOT, KI, 0)>(v[0], v[1]);
+    r_set<gs<K>(SLOT, KI, 1)>(v[2], v[3]);
+}
+template <int K, int D, int A, int KI> __device__ __forceinline__ void slot_mov()
+{
+    r_mov<gs<K>(D, KI, 0), gs<K>(A, KI, 0)>();
+    r_mov<gs<K>(D, KI, 1), gs<K>(A, KI, 1)>();
+}
+template <int K, int A, int B, int KI> __device__ __forceinline__ void slot_swap()
+{
+    r_swap<gs<K>(A, KI, 0), gs<K>(B, KI, 0)>();
+    r_swap<gs<K>(A, KI, 1), gs<K>(B, KI, 1)>();
+}
+
+/* ------------------------------------------------------------------------------------------------ */
+/* one instruction at one stack depth, for one of the warp's K tiles                                 */
 
 struct Ctx {
     TileInfo *tiles;  // this warp's K tile descriptors (shared memory)
@@ -364,8 +471,9 @@ GINT_OPCODE_LIST(GINT_X_INFO)
 template <int OP, int SP, int P> __host__ __device__ constexpr bool op_valid()
 {
     constexpr int limit = P < GINT_MAX_STACK ? P : GINT_MAX_STACK;
-    if (SP < OpInfo<OP>::min_depth) return false;
+    if (SP > limit || SP < OpInfo<OP>::min_depth) return false;
     if (SP + OpInfo<OP>::net_effect > limit) return false;
+    if (OP == OP_DupX2 && SP + 1 > limit) return false;
     if (OP >= OP_FLoadReg0 && OP <= OP_FLoadReg7 && (P - 1 - (OP - OP_FLoadReg0)) < 0) return false;
     if (OP >= OP_FStoreReg0 && OP <= OP_FStoreReg7 && (P - 1 - (OP - OP_FStoreReg0)) < 0) return false;
     return true;
@@ -380,257 +488,293 @@ __device__ __forceinline__ float sel4(const float (&v)[4], uint32_t i)
     return (i & 2u) ? hi : lo;
 }
 
-template <int LAYOUT, int DT, int SP, int P, int K>
-__device__ __forceinline__ void op_load(Slot (&S)[P][K], uint32_t operand, const Ctx &cx)
+template <int OP> __host__ __device__ constexpr bool is_scalar_binary()
 {
-#pragma unroll
-    for (int k = 0; k < K; k++) {
-        float v[4];
-        tile_rw<LAYOUT, DT, false>(cx.tiles + k, operand, cx.lane, v);
-        S[SP][k] = make_slot(v[0], v[1], v[2], v[3]);
-    }
+    return OP == OP_FDiv || OP == OP_FRDiv || OP == OP_FRem || (OP >= OP_FGt && OP <= OP_FApprox) || OP == OP_FArcTan2 ||
+           OP == OP_FPow || (OP >= OP_IAdd && OP <= OP_IXor);
 }
-template <int LAYOUT, int DT, int SP, int P, int K>
-__device__ __forceinline__ void op_store(Slot (&S)[P][K], uint32_t operand, const Ctx &cx)
+template <int OP> __host__ __device__ constexpr bool is_scalar_unary()
 {
+    return OP == OP_FSqrt || OP == OP_FSin || OP == OP_FCos || OP == OP_FTan || OP == OP_FArcSin || OP == OP_FArcCos ||
+           OP == OP_FArcTan || OP == OP_FExp || OP == OP_FExp2 || OP == OP_FLog || OP == OP_FLog2 || OP == OP_FRSqrt ||
+           OP == OP_FErf || OP == OP_FRcp;
+}
+template <int OP> struct MemOp { static constexpr bool is = false; };
+#define GINT_MEMOP(name, lay, dt, st) \
+    template <> struct MemOp<OP_##name> { static constexpr bool is = true; static constexpr int layout = lay; static constexpr int dtype = dt; static constexpr bool store = st; };
+GINT_MEMOP(LoadGlobal1DF32, LAY_1D, DT_F32, false) GINT_MEMOP(StoreGlobal1DF32, LAY_1D, DT_F32, true)
+GINT_MEMOP(LoadGlobal1DF16, LAY_1D, DT_F16, false) GINT_MEMOP(StoreGlobal1DF16, LAY_1D, DT_F16, true)
+GINT_MEMOP(LoadGlobal1DBF16, LAY_1D, DT_BF16, false) GINT_MEMOP(StoreGlobal1DBF16, LAY_1D, DT_BF16, true)
+GINT_MEMOP(LoadGlobal1DU8, LAY_1D, DT_U8, false)
+GINT_MEMOP(LoadGlobal2DTF32, LAY_2DT, DT_F32, false) GINT_MEMOP(StoreGlobal2DTF32, LAY_2DT, DT_F32, true)
+GINT_MEMOP(LoadGlobal2DTF16, LAY_2DT, DT_F16, false) GINT_MEMOP(StoreGlobal2DTF16, LAY_2DT, DT_F16, true)
+GINT_MEMOP(LoadGlobal2DTBF16, LAY_2DT, DT_BF16, false) GINT_MEMOP(StoreGlobal2DTBF16, LAY_2DT, DT_BF16, true)
+GINT_MEMOP(LoadGlobal2DTU8, LAY_2DT, DT_U8, false)
+GINT_MEMOP(LoadGlobal2DWF32, LAY_2DW, DT_F32, false) GINT_MEMOP(StoreGlobal2DWF32, LAY_2DW, DT_F32, true)
+GINT_MEMOP(LoadGlobal2DWF16, LAY_2DW, DT_F16, false) GINT_MEMOP(StoreGlobal2DWF16, LAY_2DW, DT_F16, true)
+GINT_MEMOP(LoadGlobal2DWBF16, LAY_2DW, DT_BF16, false) GINT_MEMOP(StoreGlobal2DWBF16, LAY_2DW, DT_BF16, true)
+GINT_MEMOP(LoadGlobal2DWU8, LAY_2DW, DT_U8, false)
+#undef GINT_MEMOP
+
+template <int OP, int SP, int P, int K, int KI>
+__device__ __forceinline__ void exec_tile(const uint32_t operand, const Ctx &cx)
+{
+    constexpr int T = SP - 1;  // top of stack; T-1 = second ("S"), T-2 = third ("U")
+#define LO(slot) gs<K>((slot), KI, 0)
+#define HI(slot) gs<K>((slot), KI, 1)
+    /* ---- float ALU (arith.py:15-66): binary handlers compute fn(T, S) ---- */
+    if constexpr (OP == OP_Nop || OP == OP_Pop || OP == OP_Pop2) {
+    } else if constexpr (OP == OP_FAdd) {
+        r_add2<LO(T - 1), LO(T), LO(T - 1)>();
+        r_add2<HI(T - 1), HI(T), HI(T - 1)>();
+    } else if constexpr (OP == OP_FMul) {
+        r_mul2<LO(T - 1), LO(T), LO(T - 1)>();
+        r_mul2<HI(T - 1), HI(T), HI(T - 1)>();
+    } else if constexpr (OP == OP_FSub) {
+        r_sub2<LO(T - 1), LO(T), LO(T - 1)>();
+        r_sub2<HI(T - 1), HI(T), HI(T - 1)>();
+    } else if constexpr (OP == OP_FRSub) {
+        r_sub2<LO(T - 1), LO(T - 1), LO(T)>();
+        r_sub2<HI(T - 1), HI(T - 1), HI(T)>();
+    } else if constexpr (OP == OP_FMA) {  // fma(T, S, U)
+        r_fma2<LO(T - 2), LO(T), LO(T - 1), LO(T - 2)>();
+        r_fma2<HI(T - 2), HI(T), HI(T - 1), HI(T - 2)>();
+    } else if constexpr (OP == OP_FNeg) {
+        r_neg2<LO(T)>();
+        r_neg2<HI(T)>();
+    } else if constexpr (is_scalar_binary<OP>()) {
+        float t[4], s[4];
+        slot_read<K, T, KI>(t);
+        slot_read<K, T - 1, KI>(s);
 #pragma unroll
-    for (int k = 0; k < K; k++) {
-        float v[4];
-        slot_get(S[SP - 1][k], v);
-        tile_rw<LAYOUT, DT, true>(cx.tiles + k, operand, cx.lane, v);
+        for (int w = 0; w < 4; w++) s[w] = scalar_binary<OP>(t[w], s[w], operand);
+        slot_write<K, T - 1, KI>(s);
+    } else if constexpr (is_scalar_unary<OP>()) {
+        float t[4];
+        slot_read<K, T, KI>(t);
+#pragma unroll
+        for (int w = 0; w < 4; w++) t[w] = scalar_unary<OP>(t[w]);
+        slot_write<K, T, KI>(t);
     }
+    /* ---- immediates (immediate.py:7-61) ---- */
+    else if constexpr (OP == OP_LoadImm) {
+        const u64 v = pack2(__uint_as_float(operand), __uint_as_float(operand));
+        r_set64<LO(SP)>(v);
+        r_set64<HI(SP)>(v);
+    } else if constexpr (OP == OP_FAddImm) {
+        const u64 imm = pack2(__uint_as_float(operand), __uint_as_float(operand));
+        r_add2_imm<LO(T)>(imm);
+        r_add2_imm<HI(T)>(imm);
+    } else if constexpr (OP == OP_FMulImm) {
+        const u64 imm = pack2(__uint_as_float(operand), __uint_as_float(operand));
+        r_mul2_imm<LO(T)>(imm);
+        r_mul2_imm<HI(T)>(imm);
+    } else if constexpr (OP == OP_FMAImm) {  // f16x2: low half = multiplier, high half = addend
+        const float m = __half2float(__ushort_as_half((unsigned short)(operand & 0xFFFFu)));
+        const float c = __half2float(__ushort_as_half((unsigned short)(operand >> 16)));
+        const u64 m2 = pack2(m, m), c2 = pack2(c, c);
+        r_fma2_imm<LO(T)>(m2, c2);
+        r_fma2_imm<HI(T)>(m2, c2);
+    } else if constexpr (OP == OP_LoadImm4F) {
+        r_set<LO(SP)>((float)(signed char)(operand), (float)(signed char)(operand >> 8));
+        r_set<HI(SP)>((float)(signed char)(operand >> 16), (float)(signed char)(operand >> 24));
+    } else if constexpr (OP == OP_LoadImm4I) {
+        r_set<LO(SP)>(__int_as_float((int)(signed char)(operand)), __int_as_float((int)(signed char)(operand >> 8)));
+        r_set<HI(SP)>(__int_as_float((int)(signed char)(operand >> 16)), __int_as_float((int)(signed char)(operand >> 24)));
+    }
+    /* ---- stack moves (move.py:7-55), rightmost = top ---- */
+    else if constexpr (OP == OP_Dup) {
+        slot_mov<K, SP, T, KI>();
+    } else if constexpr (OP == OP_DupX1) {  // [a, b] -> [b, a, b]
+        slot_mov<K, SP, T, KI>();
+        slot_swap<K, T, T - 1, KI>();
+    } else if constexpr (OP == OP_DupX2) {  // [a, b, c] -> [c, a, b, c]
+        slot_mov<K, SP, T, KI>();
+        slot_mov<K, T, T - 1, KI>();
+        slot_mov<K, T - 1, T - 2, KI>();
+        slot_mov<K, T - 2, SP, KI>();
+    } else if constexpr (OP == OP_Dup2) {  // [a, b] -> [a, b, a, b]
+        slot_mov<K, SP, T - 1, KI>();
+        slot_mov<K, SP + 1, T, KI>();
+    } else if constexpr (OP == OP_Swap) {
+        slot_swap<K, T, T - 1, KI>();
+    } else if constexpr (OP == OP_Select) {  // T > 0 ? S : U (predication.py:64-73)
+        float c[4], x[4], y[4];
+        slot_read<K, T, KI>(c);
+        slot_read<K, T - 1, KI>(x);
+        slot_read<K, T - 2, KI>(y);
+#pragma unroll
+        for (int w = 0; w < 4; w++) y[w] = c[w] > 0.0f ? x[w] : y[w];
+        slot_write<K, T - 2, KI>(y);
+    }
+    /* ---- width-lane moves (move.py:69-135); operand indices pre-clamped to 0..3 ---- */
+    else if constexpr (OP == OP_DupBroadcastW) {
+        float t[4];
+        slot_read<K, T, KI>(t);
+        const float x = sel4(t, operand);
+        r_set<LO(SP)>(x, x);
+        r_set<HI(SP)>(x, x);
+    } else if constexpr (OP == OP_FPermW) {
+        float t[4];
+        slot_read<K, T, KI>(t);
+        const float o[4] = {sel4(t, operand), sel4(t, operand >> 8), sel4(t, operand >> 16), sel4(t, operand >> 24)};
+        slot_write<K, T, KI>(o);
+    } else if constexpr (OP == OP_FShuf2) {  // vec2 = T, vec1 = S -> (vec1[x], vec1[y], vec2[z], vec2[w])
+        float v2[4], v1[4];
+        slot_read<K, T, KI>(v2);
+        slot_read<K, T - 1, KI>(v1);
+        const float o[4] = {sel4(v1, operand), sel4(v1, operand >> 8), sel4(v2, operand >> 16), sel4(v2, operand >> 24)};
+        slot_write<K, T - 1, KI>(o);
+    }
+    /* ---- virtual registers: reg n = pool[P-1-n] (state.py:38-41, reg.py:7-59) ---- */
+    else if constexpr (OP >= OP_FLoadReg0 && OP <= OP_FLoadReg7) {
+        slot_mov<K, SP, P - 1 - (OP - OP_FLoadReg0), KI>();
+    } else if constexpr (OP >= OP_FStoreReg0 && OP <= OP_FStoreReg7) {
+        slot_mov<K, P - 1 - (OP - OP_FStoreReg0), T, KI>();
+    }
+    /* ---- warp all-reduce (reduction.py:7-30, nvptx.py:89-104): butterfly 16, 8, 4, 2, 1 per width lane ---- */
+    else if constexpr (OP >= OP_WarpAllReduceSum && OP <= OP_WarpAllReduceProd) {
+        float t[4];
+        slot_read<K, T, KI>(t);
+#pragma unroll
+        for (int mask = 16; mask >= 1; mask >>= 1) {
+#pragma unroll
+            for (int w = 0; w < 4; w++) {
+                const float o = __shfl_xor_sync(0xffffffffu, t[w], mask);
+                if constexpr (OP == OP_WarpAllReduceSum) t[w] = __fadd_rn(t[w], o);
+                else if constexpr (OP == OP_WarpAllReduceMax) t[w] = max_nan(t[w], o);
+                else if constexpr (OP == OP_WarpAllReduceMin) t[w] = min_nan(t[w], o);
+                else t[w] = __fmul_rn(t[w], o);
+            }
+        }
+        slot_write<K, T, KI>(t);
+    }
+    /* ---- global memory (load_store.py) ---- */
+    else if constexpr (MemOp<OP>::is) {
+        float v[4];
+        if constexpr (MemOp<OP>::store) {
+            slot_read<K, T, KI>(v);
+            tile_rw<MemOp<OP>::layout, MemOp<OP>::dtype, true>(cx.tiles + KI, operand, cx.lane, v);
+        } else {
+            tile_rw<MemOp<OP>::layout, MemOp<OP>::dtype, false>(cx.tiles + KI, operand, cx.lane, v);
+            slot_write<K, SP, KI>(v);
+        }
+    } else if constexpr (OP == OP_LoadGlobal1DF32Indirect) {  // pops indices, pushes values
+        float idx[4], v[4];
+        slot_read<K, T, KI>(idx);
+        tile_indirect<false>(cx.tiles + KI, operand, idx, v);
+        slot_write<K, T, KI>(v);
+    } else if constexpr (OP == OP_StoreGlobal1DF32Indirect) {  // indices on top, values below
+        float idx[4], v[4];
+        slot_read<K, T, KI>(idx);
+        slot_read<K, T - 1, KI>(v);
+        tile_indirect<true>(cx.tiles + KI, operand, idx, v);
+    } else if constexpr (OP == OP_AdvanceBlock2D || OP == OP_AdvanceBase) {  // load_store.py:291-321, operand >> 4 is arithmetic
+        if (cx.lane == 0) {
+            const int arg = operand & 15;
+            const int delta = ((int)operand) >> 4;
+            if constexpr (OP == OP_AdvanceBlock2D) cx.tiles[KI].adv[arg] += delta;
+            else cx.tiles[KI].ptr[arg] += (u64)(long long)delta;  // bytes
+        }
+    }
+#undef LO
+#undef HI
 }
 
-template <int OP, int SP, int P, int K>
-__device__ __forceinline__ void exec(Slot (&S)[P][K], const uint32_t operand, const Ctx &cx)
+template <int OP, int SP, int P, int K, int... KI>
+__device__ __forceinline__ void exec_all(const uint32_t operand, const Ctx &cx, std::integer_sequence<int, KI...>)
 {
-    if constexpr (!op_valid<OP, SP, P>()) {
-        return;
-    } else {
-        constexpr int T = SP - 1;  // top of stack
-#define GINT_FOR_K _Pragma("unroll") for (int k = 0; k < K; k++)
-        /* ---- float ALU (arith.py:15-66): binary handlers compute fn(T, S) ---- */
-        if constexpr (OP == OP_Nop) {
-        } else if constexpr (OP == OP_FAdd) {
-            GINT_FOR_K { S[T - 1][k].a = add2(S[T][k].a, S[T - 1][k].a); S[T - 1][k].b = add2(S[T][k].b, S[T - 1][k].b); }
-        } else if constexpr (OP == OP_FMul) {
-            GINT_FOR_K { S[T - 1][k].a = mul2(S[T][k].a, S[T - 1][k].a); S[T - 1][k].b = mul2(S[T][k].b, S[T - 1][k].b); }
-        } else if constexpr (OP == OP_FSub) {
-            GINT_FOR_K { S[T - 1][k].a = sub2(S[T][k].a, S[T - 1][k].a); S[T - 1][k].b = sub2(S[T][k].b, S[T - 1][k].b); }
-        } else if constexpr (OP == OP_FRSub) {
-            GINT_FOR_K { S[T - 1][k].a = sub2(S[T - 1][k].a, S[T][k].a); S[T - 1][k].b = sub2(S[T - 1][k].b, S[T][k].b); }
-        } else if constexpr (OP == OP_FMA) {
-            GINT_FOR_K {
-                S[T - 2][k].a = fma2(S[T][k].a, S[T - 1][k].a, S[T - 2][k].a);
-                S[T - 2][k].b = fma2(S[T][k].b, S[T - 1][k].b, S[T - 2][k].b);
-            }
-        } else if constexpr (OP == OP_FNeg) {
-            GINT_FOR_K { S[T][k].a ^= 0x8000000080000000ull; S[T][k].b ^= 0x8000000080000000ull; }
-        } else if constexpr (OP == OP_FDiv || OP == OP_FRDiv || OP == OP_FRem || (OP >= OP_FGt && OP <= OP_FApprox) ||
-                             OP == OP_FArcTan2 || OP == OP_FPow || (OP >= OP_IAdd && OP <= OP_IXor)) {
-            GINT_FOR_K {
-                float t[4], s[4];
-                slot_get(S[T][k], t);
-                slot_get(S[T - 1][k], s);
-#pragma unroll
-                for (int w = 0; w < 4; w++) s[w] = scalar_binary<OP>(t[w], s[w], operand);
-                S[T - 1][k] = make_slot(s[0], s[1], s[2], s[3]);
-            }
-        } else if constexpr (OP == OP_FSqrt || OP == OP_FSin || OP == OP_FCos || OP == OP_FTan || OP == OP_FArcSin ||
-                             OP == OP_FArcCos || OP == OP_FArcTan || OP == OP_FExp || OP == OP_FExp2 || OP == OP_FLog ||
-                             OP == OP_FLog2 || OP == OP_FRSqrt || OP == OP_FErf || OP == OP_FRcp) {
-            GINT_FOR_K {
-                float t[4];
-                slot_get(S[T][k], t);
-#pragma unroll
-                for (int w = 0; w < 4; w++) t[w] = scalar_unary<OP>(t[w]);
-                S[T][k] = make_slot(t[0], t[1], t[2], t[3]);
-            }
-        }
-        /* ---- immediates (immediate.py:7-61) ---- */
-        else if constexpr (OP == OP_LoadImm) {
-            const Slot v = splat(__uint_as_float(operand));
-            GINT_FOR_K S[SP][k] = v;
-        } else if constexpr (OP == OP_FAddImm) {
-            const u64 imm = pack2(__uint_as_float(operand), __uint_as_float(operand));
-            GINT_FOR_K { S[T][k].a = add2(S[T][k].a, imm); S[T][k].b = add2(S[T][k].b, imm); }
-        } else if constexpr (OP == OP_FMulImm) {
-            const u64 imm = pack2(__uint_as_float(operand), __uint_as_float(operand));
-            GINT_FOR_K { S[T][k].a = mul2(S[T][k].a, imm); S[T][k].b = mul2(S[T][k].b, imm); }
-        } else if constexpr (OP == OP_FMAImm) {  // f16x2: low half = multiplier, high half = addend
-            const float m = __half2float(__ushort_as_half((unsigned short)(operand & 0xFFFFu)));
-            const float c = __half2float(__ushort_as_half((unsigned short)(operand >> 16)));
-            const u64 m2 = pack2(m, m), c2 = pack2(c, c);
-            GINT_FOR_K { S[T][k].a = fma2(S[T][k].a, m2, c2); S[T][k].b = fma2(S[T][k].b, m2, c2); }
-        } else if constexpr (OP == OP_LoadImm4F) {
-            const Slot v = make_slot((float)(signed char)(operand), (float)(signed char)(operand >> 8),
-                                     (float)(signed char)(operand >> 16), (float)(signed char)(operand >> 24));
-            GINT_FOR_K S[SP][k] = v;
-        } else if constexpr (OP == OP_LoadImm4I) {
-            const Slot v = make_slot(__int_as_float((int)(signed char)(operand)), __int_as_float((int)(signed char)(operand >> 8)),
-                                     __int_as_float((int)(signed char)(operand >> 16)), __int_as_float((int)(signed char)(operand >> 24)));
-            GINT_FOR_K S[SP][k] = v;
-        }
-        /* ---- stack moves (move.py:7-55), rightmost = top ---- */
-        else if constexpr (OP == OP_Pop || OP == OP_Pop2) {
-        } else if constexpr (OP == OP_Dup) {
-            GINT_FOR_K S[SP][k] = S[T][k];
-        } else if constexpr (OP == OP_DupX1) {  // [a, b] -> [b, a, b]
-            GINT_FOR_K { const Slot b = S[T][k], a = S[T - 1][k]; S[T - 1][k] = b; S[T][k] = a; S[SP][k] = b; }
-        } else if constexpr (OP == OP_DupX2) {  // [a, b, c] -> [c, a, b, c]
-            GINT_FOR_K {
-                const Slot c = S[T][k], b = S[T - 1][k], a = S[T - 2][k];
-                S[T - 2][k] = c; S[T - 1][k] = a; S[T][k] = b; S[SP][k] = c;
-            }
-        } else if constexpr (OP == OP_Dup2) {  // [a, b] -> [a, b, a, b]
-            GINT_FOR_K { S[SP][k] = S[T - 1][k]; S[SP + 1][k] = S[T][k]; }
-        } else if constexpr (OP == OP_Swap) {
-            GINT_FOR_K { const Slot b = S[T][k]; S[T][k] = S[T - 1][k]; S[T - 1][k] = b; }
-        } else if constexpr (OP == OP_Select) {  // T > 0 ? S : U (predication.py:64-73)
-            GINT_FOR_K {
-                float c[4], x[4], y[4];
-                slot_get(S[T][k], c);
-                slot_get(S[T - 1][k], x);
-                slot_get(S[T - 2][k], y);
-#pragma unroll
-                for (int w = 0; w < 4; w++) y[w] = c[w] > 0.0f ? x[w] : y[w];
-                S[T - 2][k] = make_slot(y[0], y[1], y[2], y[3]);
-            }
-        }
-        /* ---- width-lane moves (move.py:69-135); operand indices pre-clamped to 0..3 ---- */
-        else if constexpr (OP == OP_DupBroadcastW) {
-            GINT_FOR_K {
-                float t[4];
-                slot_get(S[T][k], t);
-                S[SP][k] = splat(sel4(t, operand));
-            }
-        } else if constexpr (OP == OP_FPermW) {
-            GINT_FOR_K {
-                float t[4];
-                slot_get(S[T][k], t);
-                S[T][k] = make_slot(sel4(t, operand), sel4(t, operand >> 8), sel4(t, operand >> 16), sel4(t, operand >> 24));
-            }
-        } else if constexpr (OP == OP_FShuf2) {  // vec2 = T, vec1 = S -> (vec1[x], vec1[y], vec2[z], vec2[w])
-            GINT_FOR_K {
-                float v2[4], v1[4];
-                slot_get(S[T][k], v2);
-                slot_get(S[T - 1][k], v1);
-                S[T - 1][k] = make_slot(sel4(v1, operand), sel4(v1, operand >> 8), sel4(v2, operand >> 16), sel4(v2, operand >> 24));
-            }
-        }
-        /* ---- virtual registers: reg n = pool[P-1-n] (state.py:38-41, reg.py:7-59) ---- */
-        else if constexpr (OP >= OP_FLoadReg0 && OP <= OP_FLoadReg7) {
-            GINT_FOR_K S[SP][k] = S[P - 1 - (OP - OP_FLoadReg0)][k];
-        } else if constexpr (OP >= OP_FStoreReg0 && OP <= OP_FStoreReg7) {
-            GINT_FOR_K S[P - 1 - (OP - OP_FStoreReg0)][k] = S[T][k];
-        }
-        /* ---- warp all-reduce (reduction.py:7-30, nvptx.py:89-104): butterfly 16, 8, 4, 2, 1 per width lane ---- */
-        else if constexpr (OP >= OP_WarpAllReduceSum && OP <= OP_WarpAllReduceProd) {
-            GINT_FOR_K {
-                float t[4];
-                slot_get(S[T][k], t);
-#pragma unroll
-                for (int mask = 16; mask >= 1; mask >>= 1) {
-#pragma unroll
-                    for (int w = 0; w < 4; w++) {
-                        const float o = __shfl_xor_sync(0xffffffffu, t[w], mask);
-                        if constexpr (OP == OP_WarpAllReduceSum) t[w] = __fadd_rn(t[w], o);
-                        else if constexpr (OP == OP_WarpAllReduceMax) t[w] = max_nan(t[w], o);
-                        else if constexpr (OP == OP_WarpAllReduceMin) t[w] = min_nan(t[w], o);
-                        else t[w] = __fmul_rn(t[w], o);
-                    }
-                }
-                S[T][k] = make_slot(t[0], t[1], t[2], t[3]);
-            }
-        }
-        /* ---- global memory (load_store.py) ---- */
-        else if constexpr (OP == OP_LoadGlobal1DF32) op_load<LAY_1D, DT_F32, SP>(S, operand, cx);
-        else if constexpr (OP == OP_StoreGlobal1DF32) op_store<LAY_1D, DT_F32, SP>(S, operand, cx);
-        else if constexpr (OP == OP_LoadGlobal1DF16) op_load<LAY_1D, DT_F16, SP>(S, operand, cx);
-        else if constexpr (OP == OP_StoreGlobal1DF16) op_store<LAY_1D, DT_F16, SP>(S, operand, cx);
-        else if constexpr (OP == OP_LoadGlobal1DBF16) op_load<LAY_1D, DT_BF16, SP>(S, operand, cx);
-        else if constexpr (OP == OP_StoreGlobal1DBF16) op_store<LAY_1D, DT_BF16, SP>(S, operand, cx);
-        else if constexpr (OP == OP_LoadGlobal1DU8) op_load<LAY_1D, DT_U8, SP>(S, operand, cx);
-        else if constexpr (OP == OP_LoadGlobal2DTF32) op_load<LAY_2DT, DT_F32, SP>(S, operand, cx);
-        else if constexpr (OP == OP_StoreGlobal2DTF32) op_store<LAY_2DT, DT_F32, SP>(S, operand, cx);
-        else if constexpr (OP == OP_LoadGlobal2DTF16) op_load<LAY_2DT, DT_F16, SP>(S, operand, cx);
-        else if constexpr (OP == OP_StoreGlobal2DTF16) op_store<LAY_2DT, DT_F16, SP>(S, operand, cx);
-        else if constexpr (OP == OP_LoadGlobal2DTBF16) op_load<LAY_2DT, DT_BF16, SP>(S, operand, cx);
-        else if constexpr (OP == OP_StoreGlobal2DTBF16) op_store<LAY_2DT, DT_BF16, SP>(S, operand, cx);
-        else if constexpr (OP == OP_LoadGlobal2DTU8) op_load<LAY_2DT, DT_U8, SP>(S, operand, cx);
-        else if constexpr (OP == OP_LoadGlobal2DWF32) op_load<LAY_2DW, DT_F32, SP>(S, operand, cx);
-        else if constexpr (OP == OP_StoreGlobal2DWF32) op_store<LAY_2DW, DT_F32, SP>(S, operand, cx);
-        else if constexpr (OP == OP_LoadGlobal2DWF16) op_load<LAY_2DW, DT_F16, SP>(S, operand, cx);
-        else if constexpr (OP == OP_StoreGlobal2DWF16) op_store<LAY_2DW, DT_F16, SP>(S, operand, cx);
-        else if constexpr (OP == OP_LoadGlobal2DWBF16) op_load<LAY_2DW, DT_BF16, SP>(S, operand, cx);
-        else if constexpr (OP == OP_StoreGlobal2DWBF16) op_store<LAY_2DW, DT_BF16, SP>(S, operand, cx);
-        else if constexpr (OP == OP_LoadGlobal2DWU8) op_load<LAY_2DW, DT_U8, SP>(S, operand, cx);
-        else if constexpr (OP == OP_LoadGlobal1DF32Indirect) {  // pops indices, pushes values
-            GINT_FOR_K {
-                float idx[4], v[4];
-                slot_get(S[T][k], idx);
-                tile_indirect<false>(cx.tiles + k, operand, idx, v);
-                S[T][k] = make_slot(v[0], v[1], v[2], v[3]);
-            }
-        } else if constexpr (OP == OP_StoreGlobal1DF32Indirect) {  // indices on top, values below
-            GINT_FOR_K {
-                float idx[4], v[4];
-                slot_get(S[T][k], idx);
-                slot_get(S[T - 1][k], v);
-                tile_indirect<true>(cx.tiles + k, operand, idx, v);
-            }
-        } else if constexpr (OP == OP_AdvanceBlock2D || OP == OP_AdvanceBase) {  // load_store.py:291-321, operand >> 4 is arithmetic
-            __syncwarp();
-            if (cx.lane == 0) {
-                const int arg = operand & 15;
-                const int delta = ((int)operand) >> 4;
-                GINT_FOR_K {
-                    if constexpr (OP == OP_AdvanceBlock2D) cx.tiles[k].adv[arg] += delta;
-                    else cx.tiles[k].ptr[arg] += (u64)(long long)delta;  // bytes
-                }
-            }
-            __syncwarp();
-        }
-#undef GINT_FOR_K
-    }
+    if constexpr (OP == OP_AdvanceBlock2D || OP == OP_AdvanceBase) __syncwarp();
+    (exec_tile<OP, SP, P, K, KI>(operand, cx), ...);
+    if constexpr (OP == OP_AdvanceBlock2D || OP == OP_AdvanceBase) __syncwarp();
 }
 
 /* ------------------------------------------------------------------------------------------------ */
 /* fetch / dispatch loop for one group of K logical programs                                          */
 
-template <bool SMEM> __device__ __forceinline__ uint2 fetch(const uint2 *p)
+template <int N> __device__ __forceinline__ void pool_clear()
 {
-    if constexpr (SMEM) {
-        uint2 r;
-        const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
-        asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(r.x), "=r"(r.y) : "r"(a));
-        return r;
-    } else {
-        return __ldg(p);
+    if constexpr (N > 0) {
+        pool_clear<N - 1>();
+        r_set64<N - 1>(0ull);
     }
 }
 
-template <int P, int K, bool SMEM_CODE>
-__device__ __forceinline__ void interpret(const uint2 *code, const Ctx &cx)
+/*
+ * Interpreter state that is carried from one handler to the next lives, like the pool, in named PTX registers:
+ *   %gc          address of the next stream entry to fetch (shared-memory address, or a global pointer in indirect mode)
+ *   %ge0, %ge1   the current stream entry {operand of this instruction, opcode of the next one}
+ *   %gkey        dispatch key for the C++ fallback switch (dead once the jump tables are in place)
+ *   %gbudget     instructions left before the interpreter gives up (only with GINT_GUARD, a debugging aid)
+ * so no C++ value is live from handler to handler and a handler's basic block can be entered from any other handler.
+ */
+template <bool SMEM> __device__ __forceinline__ void state_declare()
 {
-    Slot S[P][K];
-#pragma unroll
-    for (int i = 0; i < P; i++)
-#pragma unroll
-        for (int k = 0; k < K; k++) { S[i][k].a = 0ull; S[i][k].b = 0ull; }
+    // (the unused "n" operand makes nvcc treat the string as a template, so that %% means %)
+    if constexpr (SMEM) asm volatile(".reg .b32 %%gc; .reg .b32 %%ge<2>; .reg .b32 %%gkey; .reg .b32 %%gbudget; // %0" ::"n"(0));
+    else asm volatile(".reg .b64 %%gc; .reg .b32 %%ge<2>; .reg .b32 %%gkey; .reg .b32 %%gbudget; // %0" ::"n"(0));
+}
 
-    uint2 next = fetch<SMEM_CODE>(code);
-    ++code;
+/* read the current entry, then start loading the following one */
+template <bool SMEM> __device__ __forceinline__ void state_advance(uint32_t &operand, uint32_t &next_opcode)
+{
+    asm volatile("mov.b32 %0, %%ge0; mov.b32 %1, %%ge1;" : "=r"(operand), "=r"(next_opcode));
+    if constexpr (SMEM) asm volatile("ld.shared.v2.u32 {%%ge0, %%ge1}, [%%gc]; add.u32 %%gc, %%gc, 8; // %0" ::"n"(0) : "memory");
+    else asm volatile("ld.global.nc.v2.u32 {%%ge0, %%ge1}, [%%gc]; add.u64 %%gc, %%gc, 8; // %0" ::"n"(0) : "memory");
+}
+
+/*
+ * Threaded dispatch. The pre-decoded stream is skewed: entry 0 = {-, opcode of insn 0}, entry i+1 = {operand of insn i,
+ * opcode of insn i+1}. On entry to the handler of insn i, (%ge0, %ge1) hold entry i+1 -- everything this handler needs
+ * (its own operand) and everything the NEXT dispatch needs (the next opcode; the next stack depth is a compile-time
+ * property of the handler) -- and the handler's first act is to start the load of entry i+2. Each handler ends in its own
+ * dispatch, so there is one indirect branch per interpreted instruction and the jump-table lookup for the next handler can
+ * be issued before the current handler's payload.
+ *
+ * The marker comments survive into the PTX. nvcc lowers a C++ switch to a compare tree (about ten dependent branches for
+ * this many cases) and never emits an indirect branch; the build step gint_b200/ptx_dispatch.py ends every handler with
+ * one `brx.idx` jump-table branch, indexed by the opcode into the table of that handler's next stack depth and targeting
+ * the blocks that carry TARGET markers. Without that step the code below is still a correct (slower) interpreter: every
+ * handler loops back to the switch. With THREADED = false only the loop-top dispatch becomes a jump table (over all
+ * (depth, opcode) keys) and handlers branch back to it: one more branch per instruction, but a control-flow graph that
+ * ptxas digests in seconds whatever surrounds the interpreter.
+ */
+template <int P, int K, bool SMEM_CODE, bool THREADED>
+__device__ __forceinline__ void interpret(const uint2 *code, uint32_t n_entries, const Ctx &cx)
+{
+    pool_clear<2 * P * K>();
+    if constexpr (SMEM_CODE) {
+        const uint32_t a = (uint32_t)__cvta_generic_to_shared(code);
+        asm volatile("ld.shared.u32 %%gkey, [%0+4]; ld.shared.v2.u32 {%%ge0, %%ge1}, [%0+8]; add.u32 %%gc, %0, 16; mov.u32 %%gbudget, %1;"
+                     ::"r"(a), "r"(n_entries) : "memory");
+    } else {
+        asm volatile("ld.global.nc.u32 %%gkey, [%0+4]; ld.global.nc.v2.u32 {%%ge0, %%ge1}, [%0+8]; add.u64 %%gc, %0, 16; mov.u32 %%gbudget, %1;"
+                     ::"l"(code), "r"(n_entries) : "memory");
+    }
     for (;;) {
-        const uint2 cur = next;
-        next = fetch<SMEM_CODE>(code);  // the stream is padded with Halt, so reading one ahead is in bounds
-        ++code;
-        switch (cur.x) {
-#define GINT_CASE_SP(num, spv)                                  \
-    case (spv) * GINT_N_OPCODES + (num):                        \
-        if constexpr ((num) == OP_Halt) return;                 \
-        else exec<num, spv, P, K>(S, cur.y, cx);                \
-        break;
+        uint32_t key;
+        asm volatile("mov.b32 %0, %%gkey;" : "=r"(key));
+        if constexpr (THREADED) asm volatile("// GINT_DISPATCH %0 site entry depth 0;" ::"r"(key));
+        else asm volatile("// GINT_DISPATCH %0 site entry depth all;" ::"r"(key));
+        switch (key) {
+#define GINT_CASE_SP(num, spv)                                                                          \
+    case (spv) * GINT_N_OPCODES + (num):                                                                \
+        if constexpr (op_valid<num, spv, P>()) {                                                        \
+            asm volatile("// GINT_TARGET %0;" ::"n"((spv) * GINT_N_OPCODES + (num)));                   \
+            if constexpr ((num) == OP_Halt) return;                                                     \
+            else {                                                                                      \
+                constexpr int next_depth = (spv) + OpInfo<num>::net_effect;                             \
+                uint32_t operand, opc;                                                                  \
+                state_advance<SMEM_CODE>(operand, opc);                                                 \
+                GINT_GUARD_STEP                                                                         \
+                exec_all<num, spv, P, K>(operand, cx, std::make_integer_sequence<int, K>());            \
+                asm volatile("add.u32 %%gkey, %0, %1;" ::"r"(opc), "n"(next_depth * GINT_N_OPCODES));   \
+                if constexpr (THREADED)                                                                 \
+                    asm volatile("// GINT_DISPATCH %0 site %1 depth %2;" ::"r"(opc),                     \
+                                 "n"((spv) * GINT_N_OPCODES + (num)), "n"(next_depth));                 \
+            }                                                                                           \
+        }                                                                                               \
+        continue;
 #define GINT_X_CASES(name, num, md, net)                                                                           \
     GINT_CASE_SP(num, 0) GINT_CASE_SP(num, 1) GINT_CASE_SP(num, 2) GINT_CASE_SP(num, 3) GINT_CASE_SP(num, 4)       \
     GINT_CASE_SP(num, 5) GINT_CASE_SP(num, 6) GINT_CASE_SP(num, 7) GINT_CASE_SP(num, 8)
@@ -638,6 +782,7 @@ __device__ __forceinline__ void interpret(const uint2 *code, const Ctx &cx)
 #undef GINT_X_CASES
 #undef GINT_CASE_SP
         default:
+            asm volatile("// GINT_TARGET default;");
             return;
         }
     }
@@ -646,12 +791,25 @@ __device__ __forceinline__ void interpret(const uint2 *code, const Ctx &cx)
 /* ------------------------------------------------------------------------------------------------ */
 /* kernels                                                                                           */
 
+/* Indirect mode: copy one program and its descriptor block from global memory into the warp's shared-memory slice. */
+static __device__ __noinline__ void stage_for_warp(uint2 *code_s, const uint2 *code_g, uint32_t n_slots, gint_tensor_info *ti_s,
+                                                   const gint_tensor_info *ti_g, int lane)
+{
+    for (uint32_t i = lane; i < n_slots; i += 32) code_s[i] = __ldg(code_g + i);
+    const int *src = reinterpret_cast<const int *>(ti_g);
+    int *dst = reinterpret_cast<int *>(ti_s);
+    for (uint32_t i = lane; i < sizeof(gint_tensor_info) / 4; i += 32) dst[i] = __ldg(src + i);
+    __syncwarp();
+}
+
 /* Direct mode: every logical program runs the same bytecode. Persistent blocks of kWarpsPerBlock warps;
  * shared memory = [program | descriptor block | kWarpsPerBlock x K TileInfo]. */
 template <int P, int K>
-__global__ void __launch_bounds__(kThreadsPerBlock, GINT_MIN_BLOCKS(P, K)) geval_direct(const __grid_constant__ LaunchArgs a)
+__device__ __forceinline__ void geval_direct_body(const LaunchArgs &a)
 {
     extern __shared__ __align__(16) unsigned char smem[];
+    pool_declare<P, K>();
+    state_declare<true>();
     uint2 *code_s = reinterpret_cast<uint2 *>(smem);
     gint_tensor_info *ti_s = reinterpret_cast<gint_tensor_info *>(smem + a.code_smem_bytes);
     TileInfo *tiles_s = reinterpret_cast<TileInfo *>(smem + a.code_smem_bytes + kTensorInfoSmemBytes);
@@ -673,27 +831,47 @@ __global__ void __launch_bounds__(kThreadsPerBlock, GINT_MIN_BLOCKS(P, K)) geval
     for (uint32_t g = blockIdx.x * kWarpsPerBlock + warp; g < n_groups; g += gridDim.x * kWarpsPerBlock) {
         __syncwarp();  // every lane is done with the previous group's tile descriptors
         decode_tiles<K>(ti_s, (int)a.n_tensors, a.first + g * (uint32_t)K, a.end, cx.tiles, lane);
-        interpret<P, K, true>(code_s, cx);
+        interpret<P, K, true, true>(code_s, a.n_slots, cx);
     }
 }
 
-/* Indirect mode (main.py:179-194, flag > 0): logical program i has its own bytecode and descriptors, read
- * through a per-program table; the bytecode is fetched from global memory through the read-only path. */
+/* Indirect mode (main.py:179-194, flag > 0): logical program i has its own bytecode and descriptors, listed in a
+ * per-program table. Each warp copies them into its own slice of shared memory ([TileInfo | descriptor block | program],
+ * `code_smem_bytes` for the program) and interprets from there. */
 template <int P>
-__global__ void __launch_bounds__(kThreadsPerBlock) geval_indirect(const __grid_constant__ IndirectArgs a)
+__device__ __forceinline__ void geval_indirect_body(const IndirectArgs &a)
 {
     extern __shared__ __align__(16) unsigned char smem[];
-    TileInfo *tiles_s = reinterpret_cast<TileInfo *>(smem);
+    pool_declare<P, 1>();
+    state_declare<true>();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    unsigned char *mine = smem + (size_t)warp * (sizeof(TileInfo) + kTensorInfoSmemBytes + a.code_smem_bytes);
+    gint_tensor_info *ti_s = reinterpret_cast<gint_tensor_info *>(mine + sizeof(TileInfo));
+    uint2 *code_s = reinterpret_cast<uint2 *>(mine + sizeof(TileInfo) + kTensorInfoSmemBytes);
     Ctx cx;
-    cx.tiles = tiles_s + warp;
+    cx.tiles = reinterpret_cast<TileInfo *>(mine);
     cx.lane = lane;
     for (uint32_t g = blockIdx.x * kWarpsPerBlock + warp; g < a.grid_dim; g += gridDim.x * kWarpsPerBlock) {
         const IndirectEntry e = a.table[g];
-        __syncwarp();
-        decode_tiles<1>(e.ti, (int)a.n_tensors, g, a.grid_dim, cx.tiles, lane);
-        interpret<P, 1, false>(e.code, cx);
+        __syncwarp();  // every lane is done with the previous program's code and descriptors
+        stage_for_warp(code_s, e.code, e.n_slots, ti_s, e.ti, lane);
+        decode_tiles<1>(ti_s, (int)a.n_tensors, g, a.grid_dim, cx.tiles, lane);
+        interpret<P, 1, true, false>(code_s, e.n_slots, cx);
     }
 }
 
 }  // namespace gint
+
+/* Entry points have C names so the host can look them up in the loaded cubin by name. */
+#define GINT_DEFINE_INDIRECT_KERNEL(P)                                                                          \
+    extern "C" __global__ void __launch_bounds__(gint::kThreadsPerBlock, GINT_MIN_BLOCKS(P, 1))                  \
+        gint_geval_indirect_##P(const __grid_constant__ gint::IndirectArgs a)                                   \
+    {                                                                                                           \
+        gint::geval_indirect_body<P>(a);                                                                        \
+    }
+#define GINT_DEFINE_DIRECT_KERNEL(P, K)                                                                         \
+    extern "C" __global__ void __launch_bounds__(gint::kThreadsPerBlock, GINT_MIN_BLOCKS(P, K))                  \
+        gint_geval_direct_##P##_##K(const __grid_constant__ gint::LaunchArgs a)                                  \
+    {                                                                                                           \
+        gint::geval_direct_body<P, K>(a);                                                                       \
+    }

@@ -49,12 +49,17 @@ struct LaunchArgs {
 struct IndirectEntry {
     const uint2 *code;              // pre-decoded program of this logical program
     const gint_tensor_info *ti;     // its descriptor block in device memory
+    uint32_t n_slots;               // entries in `code`
+    uint32_t reserved;
 };
+
 
 struct IndirectArgs {
     const IndirectEntry *table;
     uint32_t n_tensors;       // maximum over the batch (executor_impl.py:192)
     uint32_t grid_dim;
+    uint32_t code_smem_bytes; // shared-memory bytes reserved per warp for its program
+    uint32_t reserved;
 };
 
 }  // namespace gint

@@ -1,9 +1,9 @@
 /*
- * gint_variants.h -- the kernel instantiations compiled into libgint_b200.so.
+ * gint_variants.h -- the interpreter kernels shipped inside libgint_b200.so.
  *
- * Each (pool size P, tiles per warp K) pair is compiled in its own translation unit so the build runs in
- * parallel; the host side only needs the kernel's address (for cudaLaunchKernel, cudaFuncGetAttributes and the
- * occupancy query).
+ * Each (pool size P, tiles per warp K) pair is compiled separately (gint_b200/csrc/kernels/), its dispatch switch is
+ * turned into a jump table at the PTX level (gint_b200/ptx_dispatch.py), and the resulting sm_100a cubin is embedded in
+ * the library as a byte array. The host loads the arrays with cudaLibraryLoadData and looks the kernels up by name.
  */
 #ifndef GINT_VARIANTS_H
 #define GINT_VARIANTS_H
@@ -15,10 +15,14 @@ extern "C" {
 #define GINT_DIRECT_VARIANTS(X) X(4, 1) X(4, 2) X(4, 4) X(7, 1) X(7, 2) X(12, 1) X(12, 2)
 #define GINT_INDIRECT_VARIANTS(X) X(12)
 
-#define GINT_X_DECL(P, K) const void *gint_kernel_direct_##P##_##K(void);
+#define GINT_X_DECL(P, K)                                        \
+    extern const unsigned char gint_cubin_direct_##P##_##K[];     \
+    extern const unsigned char gint_cubin_direct_##P##_##K##_end[];
 GINT_DIRECT_VARIANTS(GINT_X_DECL)
 #undef GINT_X_DECL
-#define GINT_X_DECL(P) const void *gint_kernel_indirect_##P(void);
+#define GINT_X_DECL(P)                                     \
+    extern const unsigned char gint_cubin_indirect_##P[];   \
+    extern const unsigned char gint_cubin_indirect_##P##_end[];
 GINT_INDIRECT_VARIANTS(GINT_X_DECL)
 #undef GINT_X_DECL
 

@@ -1,0 +1,3 @@
+// Interpreter kernel for a pool of 4 slots, 1 logical program(s) per warp (see gint_interp.cuh).
+#include "../gint_interp.cuh"
+GINT_DEFINE_DIRECT_KERNEL(4, 1)
