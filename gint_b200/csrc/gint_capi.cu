@@ -182,7 +182,43 @@ struct Program {
     int n_tensors = 0;
     gint_tensor_info ti;
     gint_bytecode_stats st;
+    uint32_t prefetch_mask = 0;
+    gint::Footprint fp[GINT_MAX_TENSORS];
 };
+
+/* Which bytes of each tensor one logical program reads: the union of its tile loads along the contiguous dimension.
+ * Tensors that are only written, are reached through gather/scatter or AdvanceBlock2D/AdvanceBase, use the 2DT layout or a
+ * non-f32 element type get no footprint (they are simply not prefetched). */
+void compute_footprints(const int32_t *code, int n_insns, const gint_tensor_info &ti, int n_tensors, Program *p)
+{
+    bool dynamic[GINT_MAX_TENSORS] = {};
+    for (int t = 0; t < GINT_MAX_TENSORS; t++) p->fp[t] = gint::Footprint{gint::FP_NONE, INT32_MAX, INT32_MIN, 0};
+    for (int i = 0; i < n_insns; i++) {
+        const int op = code[2 * i];
+        const uint32_t operand = (uint32_t)code[2 * i + 1];
+        if (!is_tensor_op(op)) continue;
+        const int t = (int)(operand & 15u);
+        if (t >= n_tensors) continue;
+        const int off = (int)(operand >> 4);
+        int kind = gint::FP_NONE, width = 0;
+        if (op == OP_LoadGlobal1DF32) { kind = gint::FP_1D; width = 128; }
+        else if (op == OP_LoadGlobal2DWF32) { kind = gint::FP_ROWS; width = 4; }
+        else if (op == OP_StoreGlobal1DF32 || op == OP_StoreGlobal2DWF32 || op == OP_StoreGlobal2DTF32) continue;  // writes need no prefetch
+        else { dynamic[t] = true; continue; }
+        gint::Footprint &f = p->fp[t];
+        if (f.kind != gint::FP_NONE && f.kind != kind) { dynamic[t] = true; continue; }
+        f.kind = kind;
+        if (off < f.lo) f.lo = off;
+        if (off + width > f.hi) f.hi = off + width;
+    }
+    p->prefetch_mask = 0;
+    for (int t = 0; t < n_tensors; t++) {
+        gint::Footprint &f = p->fp[t];
+        const bool unit = f.kind == gint::FP_1D ? ti.block_shape_stride_1[t][1] == 1 : ti.block_shape_stride_2[t][1] == 1;
+        if (f.kind == gint::FP_NONE || dynamic[t] || !unit || ti.elm_size[t] != 4) { f.kind = gint::FP_NONE; f.lo = f.hi = 0; continue; }
+        p->prefetch_mask |= 1u << t;
+    }
+}
 
 }  // namespace
 
@@ -197,6 +233,7 @@ struct gint_ctx {
     std::string last_error;
     int opt_tiles_per_warp = 0;
     int opt_max_blocks = 0;
+    int opt_prefetch = 1;
     /* scratch for indirect launches */
     void *ind_dev = nullptr;
     void *ind_host = nullptr;
@@ -318,7 +355,8 @@ int launch_direct(gint_ctx *ctx, uint64_t handle, const uint64_t *base_ptrs, int
     a.first = first;
     a.end = first + count;
     a.code_smem_bytes = g.code_smem;
-    a.reserved = 0;
+    a.prefetch_mask = ctx->opt_prefetch ? p->prefetch_mask : 0u;
+    for (int t = 0; t < GINT_MAX_TENSORS; t++) a.fp[t] = p->fp[t];
     a.ti = p->ti;
     for (int i = 0; i < n_tensors; i++) a.ti.base_ptr[i] = (int64_t)base_ptrs[i];
     void *args[1] = {&a};
@@ -454,6 +492,7 @@ int gint_program_create(gint_ctx *ctx, const int32_t *code, int n_words, const g
     memset(&p->ti, 0, sizeof(p->ti));
     if (ti) p->ti = *ti;
     for (int t = 0; t < GINT_MAX_TENSORS; t++) p->ti.base_ptr[t] = 0;
+    compute_footprints(code, p->st.num_instructions, p->ti, n_tensors, p);
     {
         DeviceGuard guard(ctx->device);
         cudaError_t e = cudaMalloc(&p->code_dev, pre.size() * sizeof(uint2));
@@ -607,6 +646,10 @@ int gint_set_option(gint_ctx *ctx, const char *name, int value)
     if (strcmp(name, "tiles_per_warp") == 0) {
         if (value != 0 && value != 1 && value != 2 && value != 4) return fail(ctx, GINT_ERR_INVALID_ARGUMENT, "tiles_per_warp must be 0, 1, 2 or 4");
         ctx->opt_tiles_per_warp = value;
+        return GINT_OK;
+    }
+    if (strcmp(name, "prefetch") == 0) {
+        ctx->opt_prefetch = value != 0;
         return GINT_OK;
     }
     if (strcmp(name, "max_blocks") == 0) {

@@ -791,6 +791,42 @@ __device__ __forceinline__ void interpret(const uint2 *code, uint32_t n_entries,
 /* ------------------------------------------------------------------------------------------------ */
 /* kernels                                                                                           */
 
+/*
+ * The interpreter consumes every load right away (the value is needed by the next bytecode instruction), so by itself it
+ * keeps only one tile per warp in flight and is bound by memory latency. The bytecode is straight-line, though, so what
+ * each logical program will read is known before it starts: right after the descriptors of a group are decoded, the warp
+ * asks for those bytes to be brought into L2 (prefetch.global.L2, one 128-byte line per lane and step). The loads that
+ * follow then hit L2 while the DRAM transfers of the rest of the footprint overlap with interpretation.
+ */
+template <int K>
+__device__ __forceinline__ void prefetch_footprints(const LaunchArgs &a, const TileInfo *tiles, int lane)
+{
+    for (uint32_t m = a.prefetch_mask; m; m &= m - 1) {
+        const int t = __ffs(m) - 1;
+        const Footprint f = a.fp[t];
+#pragma unroll
+        for (int k = 0; k < K; k++) {
+            const TileInfo *ti = tiles + k;
+            const char *base = reinterpret_cast<const char *>(ti->ptr[t]);
+            const int2 s1 = ti->s1[t];
+            if (f.kind == FP_1D) {
+                if (s1.y != 1) continue;
+                const int hi = min(f.hi, s1.x);
+                const char *p = base + (long long)f.lo * 4;
+                const char *end = base + (long long)hi * 4;
+                for (p += lane * 128; p < end; p += 32 * 128) asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
+            } else {
+                const int2 s2 = ti->s2[t];
+                if (s2.y != 1 || lane >= s1.x) continue;
+                const int hi = min(f.hi, s2.x);
+                const char *p = base + ((long long)lane * s1.y + f.lo) * 4;
+                const char *end = base + ((long long)lane * s1.y + hi) * 4;
+                for (; p < end; p += 128) asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
+            }
+        }
+    }
+}
+
 /* Indirect mode: copy one program and its descriptor block from global memory into the warp's shared-memory slice. */
 static __device__ __noinline__ void stage_for_warp(uint2 *code_s, const uint2 *code_g, uint32_t n_slots, gint_tensor_info *ti_s,
                                                    const gint_tensor_info *ti_g, int lane)
@@ -831,6 +867,7 @@ __device__ __forceinline__ void geval_direct_body(const LaunchArgs &a)
     for (uint32_t g = blockIdx.x * kWarpsPerBlock + warp; g < n_groups; g += gridDim.x * kWarpsPerBlock) {
         __syncwarp();  // every lane is done with the previous group's tile descriptors
         decode_tiles<K>(ti_s, (int)a.n_tensors, a.first + g * (uint32_t)K, a.end, cx.tiles, lane);
+        if (a.prefetch_mask) prefetch_footprints<K>(a, cx.tiles, lane);
         interpret<P, K, true, true>(code_s, a.n_slots, cx);
     }
 }

@@ -35,6 +35,15 @@ struct __align__(16) TileInfo {
 };
 constexpr int kVecRows = 1;
 
+/* What a program reads from one tensor, per logical program, found by a static walk over its (straight-line) bytecode:
+ * the element range [lo, hi) relative to the tile origin along the contiguous dimension. */
+enum { FP_NONE = 0, FP_1D = 1, FP_ROWS = 2 };
+struct Footprint {
+    int32_t kind;  // FP_1D: 1-D tiles, elements [lo, hi) of the block; FP_ROWS: 2DW tiles, columns [lo, hi) of each of the 32 rows
+    int32_t lo, hi;
+    int32_t reserved;
+};
+
 struct LaunchArgs {
     const uint2 *code;        // pre-decoded {key, operand}; n_slots entries, padded with Halt
     uint32_t n_slots;         // entries staged into shared memory (even, so the copy is a 16-byte multiple)
@@ -42,7 +51,8 @@ struct LaunchArgs {
     uint32_t first;           // first logical program of this launch
     uint32_t end;             // one past the last logical program
     uint32_t code_smem_bytes; // shared-memory bytes reserved for the program
-    uint32_t reserved;
+    uint32_t prefetch_mask;   // bit t set: prefetch tensor t's footprint into L2 when a tile's descriptors are decoded
+    Footprint fp[GINT_MAX_TENSORS];
     gint_tensor_info ti;      // descriptor block, base pointers patched per call: travels as a kernel parameter
 };
 
