@@ -233,7 +233,7 @@ struct gint_ctx {
     std::string last_error;
     int opt_tiles_per_warp = 0;
     int opt_max_blocks = 0;
-    int opt_prefetch = 1;
+    int opt_prefetch = 0;
     /* scratch for indirect launches */
     void *ind_dev = nullptr;
     void *ind_host = nullptr;
@@ -304,7 +304,9 @@ int plan_direct(gint_ctx *ctx, const Program *p, uint32_t count, Geometry *g)
     Geometry best{};
     bool have = false;
     for (int K : ks) {
-        if (ctx->opt_tiles_per_warp && K > ctx->opt_tiles_per_warp) continue;  // option = upper bound on K
+        /* upper bound on K: the option if set, else 2 (measured: 4 tiles per warp lose more to the lower occupancy of
+         * the 96-register kernels than they gain from amortised dispatch) */
+        if (K > (ctx->opt_tiles_per_warp ? ctx->opt_tiles_per_warp : 2)) continue;
         Variant *v = find_variant(ctx, P, K);
         if (!v) continue;
         Geometry c{};
