@@ -8,6 +8,7 @@
  * with no allocation and no copy and every captured launch in a CUDA graph is self-contained.
  */
 #include <cuda_runtime.h>
+#include <stddef.h>
 #include <stdint.h>
 #include <stdio.h>
 #include <string.h>
@@ -369,6 +370,57 @@ int launch_direct(gint_ctx *ctx, uint64_t handle, const uint64_t *base_ptrs, int
 
 }  // namespace
 
+/* ------------------------------------------------------------------------------------------------ */
+/* Allocation-free indirect launches: the per-launch tables live in a fixed device array instead of context-owned
+ * scratch that is grown with cudaMalloc.                                                                          */
+
+#define GINT_STATIC_MAX_PROGRAMS 64
+#define GINT_STATIC_MAX_GRID 4096
+
+struct StaticScratch {
+    gint_tensor_info ti[GINT_STATIC_MAX_PROGRAMS];        // per-program descriptor blocks, base pointers filled in
+    gint::IndirectEntry table[GINT_STATIC_MAX_GRID];       // per-logical-program {code, descriptors, length}
+};
+
+/* 136 KiB that every GPU which loads this library holds until the process exits. In host code this name is only a
+ * stand-in for the device object: it must never be handed to a kernel; the device address comes from
+ * cudaGetSymbolAddress (static_scratch_for_device below). */
+static __device__ __align__(256) unsigned char g_static_scratch[sizeof(StaticScratch)];
+
+/* Zeroes the array once per device at set-up, so its contents are defined before the first table lands in it. */
+static __global__ void static_scratch_clear()
+{
+    uint32_t *w = reinterpret_cast<uint32_t *>(g_static_scratch);
+    for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < sizeof(StaticScratch) / 4; i += gridDim.x * blockDim.x) w[i] = 0u;
+}
+
+namespace {
+
+constexpr int kMaxDevices = 64;
+void *g_static_scratch_dev[kMaxDevices];          // device address of g_static_scratch, per device; nullptr = not set up
+unsigned char g_static_host[sizeof(StaticScratch)];  // host image of the tables for the call in progress
+std::mutex g_static_mu;                            // one allocation-free launch at a time builds its tables here
+
+/* Once per device, with that device current: resolve the device address of the scratch array and clear it. */
+int static_scratch_for_device(gint_ctx *ctx, void **out)
+{
+    if (ctx->device < 0 || ctx->device >= kMaxDevices) return fail(ctx, GINT_ERR_INVALID_ARGUMENT, "device ordinal out of range");
+    if (!g_static_scratch_dev[ctx->device]) {
+        void *ptr = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&ptr, g_static_scratch);
+        if (e != cudaSuccess || !ptr) return fail(ctx, GINT_ERR_CUDA, "cudaGetSymbolAddress(static scratch)", e);
+        static_scratch_clear<<<8, 256>>>();
+        e = cudaGetLastError();
+        if (e == cudaSuccess) e = cudaDeviceSynchronize();
+        if (e != cudaSuccess) return fail(ctx, GINT_ERR_CUDA, "clearing the static scratch", e);
+        g_static_scratch_dev[ctx->device] = ptr;
+    }
+    *out = g_static_scratch_dev[ctx->device];
+    return GINT_OK;
+}
+
+}  // namespace
+
 /* ================================================================================================ */
 
 extern "C" {
@@ -639,6 +691,82 @@ int gint_execute_indirect(gint_ctx *ctx, const uint64_t *handles, int n_programs
     void *args[1] = {&a};
     e = cudaLaunchKernel(ctx->indirect.fn, dim3((unsigned)blocks), dim3(gint::kThreadsPerBlock), args, smem, stream);
     if (e != cudaSuccess) return fail(ctx, GINT_ERR_CUDA, "cudaLaunchKernel(indirect)", e);
+    return GINT_OK;
+}
+
+int gint_execute_indirect_static(gint_ctx *ctx, const uint64_t *handles, int n_programs, const uint64_t *base_ptrs,
+                                 const int32_t *indices, uint32_t grid_dim, void *cuda_stream)
+{
+    if (!ctx || !handles || !base_ptrs || !indices || n_programs <= 0) return fail(ctx, GINT_ERR_INVALID_ARGUMENT, "null argument");
+    if (n_programs > GINT_STATIC_MAX_PROGRAMS)
+        return fail(ctx, GINT_ERR_TOO_LARGE, "gint_execute_indirect_static: more than 64 programs in one launch");
+    if (grid_dim > GINT_STATIC_MAX_GRID)
+        return fail(ctx, GINT_ERR_TOO_LARGE, "gint_execute_indirect_static: more than 4096 logical programs in one launch");
+    if (grid_dim == 0) return GINT_OK;
+    if (!ctx->indirect.ok) return fail(ctx, GINT_ERR_NO_DEVICE, "indirect kernel image not usable on this device");
+    Program *progs[GINT_STATIC_MAX_PROGRAMS];
+    int max_tensors = 0;
+    uint32_t max_slots = 0;
+    for (int i = 0; i < n_programs; i++) {
+        progs[i] = lookup(ctx, handles[i]);
+        if (!progs[i]) return fail(ctx, GINT_ERR_BAD_HANDLE, "unknown program handle");
+        if (progs[i]->n_tensors > max_tensors) max_tensors = progs[i]->n_tensors;
+        if (progs[i]->n_slots > max_slots) max_slots = progs[i]->n_slots;
+    }
+    for (uint32_t i = 0; i < grid_dim; i++)
+        if (indices[i] < 0 || indices[i] >= n_programs) return fail(ctx, GINT_ERR_INVALID_ARGUMENT, "program index out of range");
+    const uint32_t code_smem = (max_slots * 8u + 127u) & ~127u;
+    const uint32_t smem = (uint32_t)gint::kWarpsPerBlock * ((uint32_t)sizeof(gint::TileInfo) + (uint32_t)gint::kTensorInfoSmemBytes + code_smem);
+    if ((int)smem > ctx->max_smem_optin) return fail(ctx, GINT_ERR_TOO_LARGE, "a program of this batch is too long for indirect mode (shared memory)");
+
+    DeviceGuard guard(ctx->device);
+    void *scratch = nullptr;
+    int rc = static_scratch_for_device(ctx, &scratch);  // first call on a device: set-up (synchronises the device)
+    if (rc != GINT_OK) return rc;
+    cudaStream_t stream = (cudaStream_t)cuda_stream;
+    const StaticScratch *d = reinterpret_cast<const StaticScratch *>(scratch);
+    cudaError_t e;
+    {
+        std::lock_guard<std::mutex> lk(g_static_mu);
+        StaticScratch *h = reinterpret_cast<StaticScratch *>(g_static_host);
+        for (int i = 0; i < n_programs; i++) {
+            h->ti[i] = progs[i]->ti;
+            for (int t = 0; t < progs[i]->n_tensors; t++) h->ti[i].base_ptr[t] = (int64_t)base_ptrs[(size_t)i * GINT_MAX_TENSORS + (size_t)t];
+        }
+        for (uint32_t i = 0; i < grid_dim; i++) {
+            h->table[i].code = progs[indices[i]]->code_dev;
+            h->table[i].ti = d->ti + indices[i];
+            h->table[i].n_slots = progs[indices[i]]->n_slots;
+            h->table[i].reserved = 0;
+        }
+        /* Two copies of exactly the used parts. The source is ordinary (pageable) host memory: the runtime stages it and
+         * returns once the host image may be reused, which is why the lock can be dropped after these calls. */
+        e = cudaMemcpyAsync(scratch, h, (size_t)n_programs * sizeof(gint_tensor_info), cudaMemcpyHostToDevice, stream);
+        if (e == cudaSuccess)
+            e = cudaMemcpyAsync((char *)scratch + offsetof(StaticScratch, table), h->table, (size_t)grid_dim * sizeof(IndirectEntry),
+                                cudaMemcpyHostToDevice, stream);
+    }
+    if (e != cudaSuccess) return fail(ctx, GINT_ERR_CUDA, "cudaMemcpyAsync(static indirect tables)", e);
+
+    IndirectArgs a;
+    a.table = d->table;
+    a.n_tensors = (uint32_t)max_tensors;
+    a.grid_dim = grid_dim;
+    a.code_smem_bytes = code_smem;
+    a.reserved = 0;
+    if (smem > 48u * 1024u) {
+        e = cudaFuncSetAttribute(ctx->indirect.fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return fail(ctx, GINT_ERR_CUDA, "cudaFuncSetAttribute(indirect)", e);
+    }
+    int bps = 0;
+    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&bps, ctx->indirect.fn, gint::kThreadsPerBlock, smem);
+    if (e != cudaSuccess || bps < 1) return fail(ctx, GINT_ERR_CUDA, "occupancy query (indirect)", e);
+    uint64_t blocks = ((uint64_t)grid_dim + gint::kWarpsPerBlock - 1) / gint::kWarpsPerBlock;
+    const uint64_t resident = (uint64_t)bps * (uint64_t)ctx->num_sms;
+    if (blocks > resident) blocks = resident;
+    void *args[1] = {&a};
+    e = cudaLaunchKernel(ctx->indirect.fn, dim3((unsigned)blocks), dim3(gint::kThreadsPerBlock), args, smem, stream);
+    if (e != cudaSuccess) return fail(ctx, GINT_ERR_CUDA, "cudaLaunchKernel(indirect, static tables)", e);
     return GINT_OK;
 }
 

@@ -76,6 +76,7 @@ SIGNATURES = {
     "gint_execute": (c_int, [c_void_p, c_uint64, POINTER(c_uint64), c_int, c_uint32, c_void_p]),
     "gint_execute_range": (c_int, [c_void_p, c_uint64, POINTER(c_uint64), c_int, c_uint32, c_uint32, c_void_p]),
     "gint_execute_indirect": (c_int, [c_void_p, POINTER(c_uint64), c_int, POINTER(c_uint64), POINTER(c_int32), c_uint32, c_void_p]),
+    "gint_execute_indirect_static": (c_int, [c_void_p, POINTER(c_uint64), c_int, POINTER(c_uint64), POINTER(c_int32), c_uint32, c_void_p]),
     "gint_set_option": (c_int, [c_void_p, c_char_p, c_int]),
 }
 

@@ -281,9 +281,14 @@ class B200Executor(BaseExecutor):
         self.launches += 1
 
     def execute_indirect(self, programs: Sequence[BaseExecutableProgram], args_list: Sequence[Sequence], indices: Sequence[int],
-                         cuda_stream: int = 0):
+                         cuda_stream: int = 0, static_tables: bool = False):
         """One launch; logical program ``i`` runs ``programs[indices[i]]`` on ``args_list[indices[i]]``
-        (``gint/host/cuda/executor_impl.py:135-201``)."""
+        (``gint/host/cuda/executor_impl.py:135-201``).
+
+        ``static_tables=True`` routes the launch through ``gint_execute_indirect_static``: the same kernel and results, but
+        the per-launch tables go into a fixed array inside the library instead of scratch memory that may be (re)allocated,
+        for callers that must not allocate device memory at launch time. At most 64 programs and 4096 logical programs;
+        the first such call on a device does a one-time set-up that synchronises the device."""
         if len(programs) != len(args_list):
             raise AssertionError("programs and args_list must have the same length")
         n = len(programs)
@@ -298,9 +303,10 @@ class B200Executor(BaseExecutor):
             for i, a in enumerate(line.indices):
                 ptrs[p * MAX_N_TENSORS + i] = conv[a].base_ptr
         idx = (ctypes.c_int32 * grid_dim)(*[int(i) for i in indices])
-        rc = self._lib.gint_execute_indirect(ctx, handles, n, ptrs, idx, grid_dim, cuda_stream)
+        fn = self._lib.gint_execute_indirect_static if static_tables else self._lib.gint_execute_indirect
+        rc = fn(ctx, handles, n, ptrs, idx, grid_dim, cuda_stream)
         if rc != 0:
-            self._check(ctx, rc, "gint_execute_indirect")
+            self._check(ctx, rc, "gint_execute_indirect_static" if static_tables else "gint_execute_indirect")
         self.launches += 1
 
     # ------------------------------------------------------------------ introspection / tuning

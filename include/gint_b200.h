@@ -147,6 +147,27 @@ int gint_execute_range(gint_ctx *ctx, uint64_t handle, const uint64_t *base_ptrs
 int gint_execute_indirect(gint_ctx *ctx, const uint64_t *handles, int n_programs, const uint64_t *base_ptrs,
                           const int32_t *indices, uint32_t grid_dim, void *cuda_stream);
 
+/* Indirect launch that allocates nothing. No counterpart in the reference (whose execute_indirect allocates and frees
+ * on every call). Same arguments and same results as gint_execute_indirect, but the per-launch tables (one descriptor
+ * block per program, one {program, descriptors} entry per logical program) are written into a fixed 136 KiB array that
+ * lives in the library's device image, not into context scratch that grows with cudaMalloc. It exists for callers that
+ * are not allowed to allocate device memory when they launch: processes whose whole device-memory budget has been handed
+ * to another allocator (a framework's caching pool, a partitioned inference server), control loops with a hard deadline
+ * that cannot absorb the device-wide stall an allocation may cause, and deployments where the set of permitted driver
+ * calls is audited and cudaMalloc / cudaFree are not on the list. This call performs no cudaMalloc, cudaFree, cudaMallocHost
+ * or any other allocating routine, on the device or in a library.
+ *   Limits: n_programs <= 64 and grid_dim <= 4096; anything larger is refused with GINT_ERR_TOO_LARGE (and a message in
+ *     gint_last_error) before any work is queued. Use gint_execute_indirect for larger batches.
+ *   Set-up: the first call on a device resolves the array's device address and clears the array once; that first call
+ *     synchronises the device, so make it before any stream capture begins and outside latency-critical sections.
+ *   Sharing: every call on a device, from any context or thread, uses the same array, and the array keeps the previous
+ *     call's tables until they are overwritten. Each call rewrites every entry it is going to read (nothing has to start
+ *     at zero), but two of these launches that can overlap on the GPU -- different streams without an ordering between
+ *     them -- race on the tables: the second upload may replace entries the first kernel has not read yet. Issue them
+ *     on one stream, or order the streams with events. */
+int gint_execute_indirect_static(gint_ctx *ctx, const uint64_t *handles, int n_programs, const uint64_t *base_ptrs,
+                                 const int32_t *indices, uint32_t grid_dim, void *cuda_stream);
+
 /* ---- tuning knobs (benchmarks / tests) ---------------------------------------------------------- */
 
 /* Force tiles-per-warp (0 = automatic) and row staging (-1 = automatic, 0 = off, 1 = on) for later launches. */
