@@ -512,9 +512,20 @@ static void *job_main(void *arg)
     return NULL;
 }
 
+int gint_oracle_execute_range(const int32_t *code, int n_words, const oracle_tensor_info *ti, int n_tensors,
+                              uint32_t first, uint32_t count, int pool_size, int n_threads);
+
 int gint_oracle_execute(const int32_t *code, int n_words, const oracle_tensor_info *ti, int n_tensors,
                         uint32_t grid_dim, int pool_size, int n_threads)
 {
+    return gint_oracle_execute_range(code, n_words, ti, n_tensors, 0u, grid_dim, pool_size, n_threads);
+}
+
+/* Logical programs [first, first + count) only: what one rank of a sharded launch executes. */
+int gint_oracle_execute_range(const int32_t *code, int n_words, const oracle_tensor_info *ti, int n_tensors,
+                              uint32_t first, uint32_t count, int pool_size, int n_threads)
+{
+    const uint32_t grid_dim = count;
     oracle_stats st;
     int rc = gint_oracle_analyze(code, n_words, &st);
     if (rc != ORACLE_OK) return rc;
@@ -531,7 +542,7 @@ int gint_oracle_execute(const int32_t *code, int n_words, const oracle_tensor_in
         uint32_t lo = (uint32_t)t * chunk, hi = lo + chunk;
         if (lo > grid_dim) lo = grid_dim;
         if (hi > grid_dim) hi = grid_dim;
-        jobs[t] = (job_t){code, n_words, ti, n_tensors, lo, hi, P, ORACLE_OK};
+        jobs[t] = (job_t){code, n_words, ti, n_tensors, first + lo, first + hi, P, ORACLE_OK};
     }
     if (n_threads == 1) {
         job_main(&jobs[0]);

@@ -57,6 +57,9 @@ def lib() -> ctypes.CDLL:
         L.gint_oracle_execute.restype = ctypes.c_int
         L.gint_oracle_execute.argtypes = [ctypes.POINTER(ctypes.c_int32), ctypes.c_int, ctypes.POINTER(OracleTensorInfo),
                                           ctypes.c_int, ctypes.c_uint32, ctypes.c_int, ctypes.c_int]
+        L.gint_oracle_execute_range.restype = ctypes.c_int
+        L.gint_oracle_execute_range.argtypes = [ctypes.POINTER(ctypes.c_int32), ctypes.c_int, ctypes.POINTER(OracleTensorInfo),
+                                                ctypes.c_int, ctypes.c_uint32, ctypes.c_uint32, ctypes.c_int, ctypes.c_int]
         L.gint_oracle_execute_indirect.restype = ctypes.c_int
         L.gint_oracle_execute_indirect.argtypes = [ctypes.POINTER(ctypes.POINTER(ctypes.c_int32)), ctypes.POINTER(ctypes.c_int32),
                                                    ctypes.POINTER(ctypes.POINTER(OracleTensorInfo)), ctypes.c_int,
@@ -114,6 +117,17 @@ def execute(program, infos, tensors, grid_dim: int, input_indices=None, pool_siz
     _fill(ti, infos, [_host_ptr(tensors[i]) for i in idx])
     rc = lib().gint_oracle_execute(code.ctypes.data_as(ctypes.POINTER(ctypes.c_int32)), int(code.size), ctypes.byref(ti),
                                    len(infos), int(grid_dim), int(pool_size), int(threads))
+    if rc != 0:
+        raise RuntimeError(f"oracle: status {rc}")
+
+
+def execute_range(program, infos, ptrs, first: int, count: int, pool_size: int = 0, threads: int = 1) -> None:
+    """Run logical programs [first, first + count) with explicit base addresses (ints), e.g. biased shard pointers."""
+    code = _code(program)
+    ti = OracleTensorInfo()
+    _fill(ti, infos, ptrs)
+    rc = lib().gint_oracle_execute_range(code.ctypes.data_as(ctypes.POINTER(ctypes.c_int32)), int(code.size), ctypes.byref(ti),
+                                         len(infos), int(first), int(count), int(pool_size), int(threads))
     if rc != 0:
         raise RuntimeError(f"oracle: status {rc}")
 
