@@ -29,7 +29,8 @@ CSRC = os.path.join(PKG_DIR, "csrc")
 KERNELS = os.path.join(CSRC, "kernels")
 OBJ_DIR = os.path.join(CSRC, "build")
 LIB_PATH = os.path.join(PKG_DIR, "libgint_b200.so")
-N_KEYS = 9 * 106   # (GINT_MAX_STACK + 1) * GINT_N_OPCODES
+N_OPS = 126          # GINT_N_DISPATCH: the 106 opcodes of the format + 20 internal ones
+N_KEYS = 9 * N_OPS   # (GINT_MAX_STACK + 1) * GINT_N_DISPATCH
 
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 COMMON = ["-lineinfo", "-O3", "-std=c++17",
@@ -66,7 +67,7 @@ def _build_kernel(src: str, extra: list[str], jump_table: bool) -> tuple[str, st
     _run([_nvcc(), "-arch=compute_100a", "-ptx"] + COMMON + extra + [src, "-o", ptx], f"nvcc -ptx {stem}")
     log = ""
     if jump_table:
-        text, stats = ptx_dispatch.rewrite(open(ptx).read(), N_KEYS)
+        text, stats = ptx_dispatch.rewrite(open(ptx).read(), N_KEYS, N_OPS)
         with open(ptx, "w") as f:
             f.write(text)
         log += f"jump table: {stats['cases']} cases over {stats['keys']} keys\n"

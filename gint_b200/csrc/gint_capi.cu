@@ -87,23 +87,20 @@ uint32_t clamp_lane_bytes(uint32_t operand)
     return r;
 }
 
-/* Pre-decoded stream, skewed for threaded dispatch: entry 0 = {0, opcode of insn 0}; entry i+1 = {operand of insn i,
- * opcode of insn i+1}; the opcode after the final Halt is Halt again. The stack depth before every instruction is static
- * (straight-line code) and is baked into the handlers, not the stream. Width-lane
- * selectors are clamped to 0..3, which is what the reference's compare tree computes for any operand
- * (gint/kernel/interpreter/instructions/move.py:58-66). */
-int predecode(const int32_t *code, int n_words, int n_tensors, std::vector<uint2> *out, std::vector<int> *depth_out = nullptr)
+/* One instruction of the normalised program: opcode (format or internal), operand as the kernel wants it. */
+struct Insn { int op; uint32_t operand; };
+
+/* Validate and normalise: width-lane selectors are clamped to 0..3, which is what the reference's compare tree computes for
+ * any operand (gint/kernel/interpreter/instructions/move.py:58-66). The list ends with the Halt. */
+int normalise(const int32_t *code, int n_words, int n_tensors, std::vector<Insn> *out)
 {
     gint_bytecode_stats st;
     int rc = analyze(code, n_words, &st);
     if (rc != GINT_OK) return rc;
-    const int n = st.num_instructions + 1;  // including the Halt
-    std::vector<uint32_t> keys((size_t)n + 1), operands((size_t)n);
-    std::vector<int> depths((size_t)n + 1, 0);
-    int depth = 0;
-    for (int i = 0; i < n; i++) {
-        const int op = i < st.num_instructions ? code[2 * i] : OP_Halt;
-        uint32_t operand = i < st.num_instructions ? (uint32_t)code[2 * i + 1] : 0u;
+    out->clear();
+    for (int i = 0; i < st.num_instructions; i++) {
+        const int op = code[2 * i];
+        uint32_t operand = (uint32_t)code[2 * i + 1];
         if (is_tensor_op(op) && (int)(operand & 15u) >= n_tensors) return GINT_ERR_INVALID_ARGUMENT;
         if (op == OP_DupBroadcastW) {
             const int32_t s = (int32_t)operand;
@@ -111,20 +108,137 @@ int predecode(const int32_t *code, int n_words, int n_tensors, std::vector<uint2
         } else if (op == OP_FPermW || op == OP_FShuf2) {
             operand = clamp_lane_bytes(operand);
         }
-        keys[(size_t)i] = (uint32_t)op;
-        depths[(size_t)i] = depth;
-        operands[(size_t)i] = operand;
-        depth += kEffects[op].net;
+        out->push_back(Insn{op, operand});
     }
-    keys[(size_t)n] = OP_Halt;
+    out->push_back(Insn{OP_Halt, 0u});
+    return GINT_OK;
+}
+
+int net_effect(int op)
+{
+    if (op < GINT_N_OPCODES) return kEffects[op].net;
+    const int kind = (op - OP_PfTake0) >> 2;   // 0 take, 1/2 issue, 3/4 take+issue
+    return (kind == 1 || kind == 2) ? 0 : 1;
+}
+
+/* Stream layout, skewed for threaded dispatch: entry 0 = {0, opcode of insn 0}; entry i+1 = {operand of insn i, opcode of
+ * insn i+1}; the opcode after the final Halt is Halt again. The stack depth before every instruction is static
+ * (straight-line code) and is baked into the handlers, not the stream. */
+void emit_stream(const std::vector<Insn> &prog, std::vector<uint2> *out, std::vector<int> *depth_out = nullptr)
+{
+    const size_t n = prog.size();
     out->clear();
-    out->reserve((size_t)n + 4);
-    out->push_back(make_uint2(0u, keys[0]));
-    for (int i = 0; i < n; i++) out->push_back(make_uint2(operands[(size_t)i], keys[(size_t)i + 1]));
+    out->reserve(n + 4);
+    out->push_back(make_uint2(0u, (uint32_t)prog[0].op));
+    for (size_t i = 0; i < n; i++) out->push_back(make_uint2(prog[i].operand, i + 1 < n ? (uint32_t)prog[i + 1].op : (uint32_t)OP_Halt));
     out->push_back(make_uint2(0u, OP_Halt));  // handlers fetch one entry ahead
     if (out->size() & 1) out->push_back(make_uint2(0u, OP_Halt));
-    if (depth_out) *depth_out = depths;
+    if (depth_out) {
+        depth_out->assign(n, 0);
+        int depth = 0;
+        for (size_t i = 0; i < n; i++) { (*depth_out)[i] = depth; depth += net_effect(prog[i].op); }
+    }
+}
+
+int predecode(const int32_t *code, int n_words, int n_tensors, std::vector<uint2> *out, std::vector<int> *depth_out = nullptr)
+{
+    std::vector<Insn> prog;
+    int rc = normalise(code, n_words, n_tensors, &prog);
+    if (rc != GINT_OK) return rc;
+    emit_stream(prog, out, depth_out);
     return GINT_OK;
+}
+
+bool writes_tensor(int op)
+{
+    return op == OP_StoreGlobal1DF32 || op == OP_StoreGlobal1DF16 || op == OP_StoreGlobal1DBF16 || op == OP_StoreGlobal1DF32Indirect ||
+           op == OP_StoreGlobal2DTF32 || op == OP_StoreGlobal2DTF16 || op == OP_StoreGlobal2DTBF16 || op == OP_StoreGlobal2DWF32 ||
+           op == OP_StoreGlobal2DWF16 || op == OP_StoreGlobal2DWBF16;
+}
+
+/*
+ * Early-issue transformation. The interpreter consumes every loaded value in the next instruction or two, so as written
+ * a program keeps one tile load per logical program in flight and waits out the full memory latency each time. The
+ * bytecode is straight-line, though: which tiles it will load, and in which order, is known here. Eligible loads
+ * (f32, 1-D or 2DW layout) are numbered 0, 1, 2, ... in program order; load n is STARTED where load n-D is consumed (the
+ * first D in a prologue) into hidden register slot n mod D, and at its original place only a register move remains
+ * (PfTake / PfTakeIssue, gint_opcodes.h). A load keeps its place when starting it early could change what it reads:
+ *   - a store or scatter to the SAME tensor slot, or an AdvanceBlock2D / AdvanceBase on it, lies in between (checked here);
+ *   - a store to ANOTHER slot lies in between and the two tensors overlap in memory: that depends on the base pointers
+ *     of the launch, so the pairs (loaded slot, stored slot) are recorded and checked against address ranges at launch
+ *     time (launch_direct); on any overlap the untransformed stream runs instead.
+ * Also folded here: a load that immediately repeats the previous instruction's load becomes Dup.
+ */
+struct EarlyIssue {
+    std::vector<Insn> prog;
+    uint8_t alias_slots[GINT_MAX_TENSORS] = {};   // bit b of [a]: loads of slot a were moved across stores to slot b
+    int n_early = 0;
+};
+
+void early_issue_transform(const std::vector<Insn> &in, int D, EarlyIssue *out)
+{
+    std::vector<Insn> prog = in;
+    for (size_t i = 1; i < prog.size(); i++) {
+        const int op = prog[i].op;
+        const bool is_load = (op >= OP_LoadGlobal1DF32 && op <= OP_LoadGlobal1DU8 && !writes_tensor(op)) ||
+                             (op >= OP_LoadGlobal2DTF32 && op <= OP_LoadGlobal2DWU8 && !writes_tensor(op));
+        if (is_load && prog[i - 1].op == op && prog[i - 1].operand == prog[i].operand) prog[i] = Insn{OP_Dup, 0u};
+    }
+    struct Member { size_t site; int layout; uint32_t operand; };
+    std::vector<Member> ring;
+    for (size_t i = 0; i < prog.size(); i++) {
+        const int op = prog[i].op;
+        if (op != OP_LoadGlobal1DF32 && op != OP_LoadGlobal2DWF32) continue;
+        const int slot = (int)(prog[i].operand & 15u);
+        const size_t n = ring.size();
+        const size_t from = n >= (size_t)D ? ring[n - (size_t)D].site + 1 : 0;   // first instruction the load would move across
+        bool hazard = false;
+        for (size_t j = from; j < i && !hazard; j++) {
+            const int oj = prog[j].op;
+            const int sj = (int)(prog[j].operand & 15u);
+            if ((writes_tensor(oj) || oj == OP_AdvanceBlock2D || oj == OP_AdvanceBase) && sj == slot) hazard = true;
+        }
+        if (hazard) continue;
+        for (size_t j = from; j < i; j++)
+            if (writes_tensor(prog[j].op)) out->alias_slots[slot] |= (uint8_t)(1u << (prog[j].operand & 7u));
+        ring.push_back(Member{i, op == OP_LoadGlobal1DF32 ? 1 : 2, prog[i].operand});
+    }
+    out->n_early = (int)ring.size();
+    out->prog.clear();
+    if (ring.empty()) { out->prog = prog; return; }
+    const size_t R = ring.size();
+    for (size_t n = 0; n < R && n < (size_t)D; n++)
+        out->prog.push_back(Insn{(ring[n].layout == 1 ? OP_PfIssue1D0 : OP_PfIssue2DW0) + (int)(n % (size_t)D), ring[n].operand});
+    size_t next = 0;
+    for (size_t i = 0; i < prog.size(); i++) {
+        if (next < R && ring[next].site == i) {
+            const int h = (int)(next % (size_t)D);
+            if (next + (size_t)D < R) {
+                const Member &f = ring[next + (size_t)D];
+                out->prog.push_back(Insn{(f.layout == 1 ? OP_PfTakeIssue1D0 : OP_PfTakeIssue2DW0) + h, f.operand});
+            } else {
+                out->prog.push_back(Insn{OP_PfTake0 + h, 0u});
+            }
+            next++;
+        } else {
+            out->prog.push_back(prog[i]);
+        }
+    }
+}
+
+/* Conservative byte extent a program can touch from a tensor's base pointer; 0 = unknown (negative strides). */
+uint64_t tensor_extent_bytes(const gint_tensor_info &ti, int t)
+{
+    int64_t elems = 1;
+    const int32_t dims[6][2] = {{ti.block_shape_stride_1[t][0], ti.block_shape_stride_1[t][1]},
+                                {ti.block_shape_stride_2[t][0], ti.block_shape_stride_2[t][1]},
+                                {ti.batch_shape[t][0], ti.batch_strides[t][0]}, {ti.batch_shape[t][1], ti.batch_strides[t][1]},
+                                {ti.batch_shape[t][2], ti.batch_strides[t][2]}, {ti.batch_shape[t][3], ti.batch_strides[t][3]}};
+    for (auto &d : dims) {
+        if (d[1] < 0) return 0;
+        if (d[0] > 1) elems += (int64_t)(d[0] - 1) * (int64_t)d[1];
+    }
+    return (uint64_t)elems * (uint64_t)(ti.elm_size[t] > 4 ? ti.elm_size[t] : 4);
 }
 
 struct Variant {
@@ -185,6 +299,12 @@ struct Program {
     gint_bytecode_stats st;
     uint32_t prefetch_mask = 0;
     gint::Footprint fp[GINT_MAX_TENSORS];
+    /* early-issue stream (nullptr if the program has no eligible load) and what must hold at launch for it to be used */
+    uint2 *early_dev = nullptr;
+    uint32_t early_slots = 0;
+    int n_early = 0;
+    uint8_t alias_slots[GINT_MAX_TENSORS] = {};
+    uint64_t extent[GINT_MAX_TENSORS] = {};
 };
 
 /* Which bytes of each tensor one logical program reads: the union of its tile loads along the contiguous dimension.
@@ -235,6 +355,7 @@ struct gint_ctx {
     int opt_tiles_per_warp = 0;
     int opt_max_blocks = 0;
     int opt_prefetch = 0;
+    int opt_early_issue = 1;
     /* scratch for indirect launches */
     void *ind_dev = nullptr;
     void *ind_host = nullptr;
@@ -295,7 +416,8 @@ uint32_t direct_smem(const Program *p, int K, uint32_t *code_smem)
 {
     const uint32_t cs = (p->n_slots * 8u + 127u) & ~127u;
     *code_smem = cs;
-    return cs + gint::kTensorInfoSmemBytes + (uint32_t)(gint::kWarpsPerBlock * K) * (uint32_t)sizeof(gint::TileInfo);
+    return cs + gint::kTensorInfoSmemBytes + (uint32_t)(gint::kWarpsPerBlock * K) * (uint32_t)sizeof(gint::TileInfo) +
+           (uint32_t)(gint::kWarpsPerBlock * K * gint::hidden_slots(p->st.pool_size) * 512);
 }
 
 int plan_direct(gint_ctx *ctx, const Program *p, uint32_t count, Geometry *g)
@@ -348,12 +470,24 @@ int launch_direct(gint_ctx *ctx, uint64_t handle, const uint64_t *base_ptrs, int
     if (count == 0) return GINT_OK;
     if ((uint64_t)first + (uint64_t)count > 0xFFFFFFFFull) return fail(ctx, GINT_ERR_TOO_LARGE, "logical program range overflows 32 bits");
     DeviceGuard guard(ctx->device);
+    /* The early-issue stream is used unless a tensor whose loads were moved across stores overlaps, at this launch's
+     * addresses, one of the tensors those stores write. */
+    bool early = ctx->opt_early_issue && p->early_dev != nullptr;
+    for (int t = 0; early && t < n_tensors; t++) {
+        for (int b = 0; early && b < n_tensors; b++) {
+            if (!((p->alias_slots[t] >> b) & 1u)) continue;
+            const uint64_t a0 = base_ptrs[t], a1 = a0 + p->extent[t], b0 = base_ptrs[b], b1 = b0 + p->extent[b];
+            if (a0 < b1 && b0 < a1) early = false;
+        }
+    }
+    Program view = *p;   // geometry depends on the stream length
+    if (early) view.n_slots = p->early_slots;
     Geometry g;
-    int rc = plan_direct(ctx, p, count, &g);
+    int rc = plan_direct(ctx, &view, count, &g);
     if (rc != GINT_OK) return rc;
     LaunchArgs a;
-    a.code = p->code_dev;
-    a.n_slots = p->n_slots;
+    a.code = early ? p->early_dev : p->code_dev;
+    a.n_slots = view.n_slots;
     a.n_tensors = (uint32_t)p->n_tensors;
     a.first = first;
     a.end = first + count;
@@ -519,6 +653,7 @@ void gint_destroy(gint_ctx *ctx)
         for (Program *p : ctx->programs) {
             if (p) {
                 if (p->code_dev) cudaFree(p->code_dev);
+                if (p->early_dev) cudaFree(p->early_dev);
                 delete p;
             }
         }
@@ -547,12 +682,39 @@ int gint_program_create(gint_ctx *ctx, const int32_t *code, int n_words, const g
     if (ti) p->ti = *ti;
     for (int t = 0; t < GINT_MAX_TENSORS; t++) p->ti.base_ptr[t] = 0;
     compute_footprints(code, p->st.num_instructions, p->ti, n_tensors, p);
+    std::vector<uint2> early;
+    {
+        std::vector<Insn> prog;
+        normalise(code, n_words, n_tensors, &prog);
+        EarlyIssue ei;
+        early_issue_transform(prog, gint::hidden_slots(p->st.pool_size), &ei);
+        bool usable = ei.n_early > 0;
+        for (int t = 0; t < n_tensors; t++) {
+            p->extent[t] = tensor_extent_bytes(p->ti, t);
+            p->alias_slots[t] = ei.alias_slots[t];
+            if (ei.alias_slots[t] && p->extent[t] == 0) usable = false;
+            for (int b = 0; b < n_tensors; b++)
+                if ((ei.alias_slots[t] >> b) & 1u) { if (tensor_extent_bytes(p->ti, b) == 0) usable = false; }
+        }
+        if (usable) { emit_stream(ei.prog, &early); p->n_early = ei.n_early; }
+    }
     {
         DeviceGuard guard(ctx->device);
         cudaError_t e = cudaMalloc(&p->code_dev, pre.size() * sizeof(uint2));
         if (e != cudaSuccess) { delete p; return fail(ctx, GINT_ERR_OUT_OF_MEMORY, "cudaMalloc(program)", e); }
         e = cudaMemcpy(p->code_dev, pre.data(), pre.size() * sizeof(uint2), cudaMemcpyHostToDevice);
         if (e != cudaSuccess) { cudaFree(p->code_dev); delete p; return fail(ctx, GINT_ERR_CUDA, "cudaMemcpy(program)", e); }
+        if (!early.empty()) {
+            e = cudaMalloc(&p->early_dev, early.size() * sizeof(uint2));
+            if (e == cudaSuccess) e = cudaMemcpy(p->early_dev, early.data(), early.size() * sizeof(uint2), cudaMemcpyHostToDevice);
+            if (e != cudaSuccess) {
+                if (p->early_dev) cudaFree(p->early_dev);
+                cudaFree(p->code_dev);
+                delete p;
+                return fail(ctx, GINT_ERR_OUT_OF_MEMORY, "cudaMalloc/cudaMemcpy(early-issue program)", e);
+            }
+            p->early_slots = (uint32_t)early.size();
+        }
     }
     p->live = true;
     std::lock_guard<std::mutex> lk(ctx->mu);
@@ -574,6 +736,7 @@ int gint_program_destroy(gint_ctx *ctx, uint64_t handle)
     DeviceGuard guard(ctx->device);
     /* the program may still be running on some stream: cudaFree waits for the device */
     if (p->code_dev) cudaFree(p->code_dev);
+    if (p->early_dev) cudaFree(p->early_dev);
     delete p;
     return GINT_OK;
 }
@@ -596,6 +759,7 @@ int gint_program_launch_info(gint_ctx *ctx, uint64_t handle, uint32_t grid_dim, 
     out->regs_per_thread = g.v->regs;
     out->blocks_per_sm = g.blocks_per_sm;
     out->num_sms = ctx->num_sms;
+    out->staged_row_tensors = p->n_early;   // number of tile loads per logical program that are issued early
     return GINT_OK;
 }
 
@@ -776,6 +940,10 @@ int gint_set_option(gint_ctx *ctx, const char *name, int value)
     if (strcmp(name, "tiles_per_warp") == 0) {
         if (value != 0 && value != 1 && value != 2 && value != 4) return fail(ctx, GINT_ERR_INVALID_ARGUMENT, "tiles_per_warp must be 0, 1, 2 or 4");
         ctx->opt_tiles_per_warp = value;
+        return GINT_OK;
+    }
+    if (strcmp(name, "early_issue") == 0) {
+        ctx->opt_early_issue = value != 0;
         return GINT_OK;
     }
     if (strcmp(name, "prefetch") == 0) {

@@ -372,7 +372,7 @@ __device__ __forceinline__ void decode_tiles(const gint_tensor_info *__restrict_
  * every path (which ptxas does not coalesce across the jump table) cost more than the handlers themselves.
  */
 
-template <int P, int K> __device__ __forceinline__ void pool_declare()
+template <int P, int K, int D> __device__ __forceinline__ void pool_declare()
 {
     asm volatile(".reg .b64 %%gs<%0>;" ::"n"(2 * P * K));
 }
@@ -458,14 +458,16 @@ template <int K, int A, int B, int KI> __device__ __forceinline__ void slot_swap
 /* one instruction at one stack depth, for one of the warp's K tiles                                 */
 
 struct Ctx {
-    TileInfo *tiles;  // this warp's K tile descriptors (shared memory)
+    TileInfo *tiles;   // this warp's K tile descriptors (shared memory)
     int lane;
+    uint32_t hidden;   // shared-memory address of this lane's 16 bytes in slot 0, tile 0 of the warp's load staging area
 };
 
 template <int OP> struct OpInfo;
 #define GINT_X_INFO(name, num, md, net) \
     template <> struct OpInfo<num> { static constexpr int min_depth = md; static constexpr int net_effect = net; };
 GINT_OPCODE_LIST(GINT_X_INFO)
+GINT_INTERNAL_OPCODE_LIST(GINT_X_INFO)
 #undef GINT_X_INFO
 
 template <int OP, int SP, int P> __host__ __device__ constexpr bool op_valid()
@@ -476,6 +478,7 @@ template <int OP, int SP, int P> __host__ __device__ constexpr bool op_valid()
     if (OP == OP_DupX2 && SP + 1 > limit) return false;
     if (OP >= OP_FLoadReg0 && OP <= OP_FLoadReg7 && (P - 1 - (OP - OP_FLoadReg0)) < 0) return false;
     if (OP >= OP_FStoreReg0 && OP <= OP_FStoreReg7 && (P - 1 - (OP - OP_FStoreReg0)) < 0) return false;
+    if (OP >= OP_PfTake0 && ((OP - OP_PfTake0) & 3) >= hidden_slots(P)) return false;
     return true;
 }
 
@@ -516,14 +519,87 @@ GINT_MEMOP(LoadGlobal2DWBF16, LAY_2DW, DT_BF16, false) GINT_MEMOP(StoreGlobal2DW
 GINT_MEMOP(LoadGlobal2DWU8, LAY_2DW, DT_U8, false)
 #undef GINT_MEMOP
 
+/*
+ * Start a tile load whose values are not needed yet. Each lane copies the (up to) four elements it will consume with
+ * cp.async into its own 16 bytes of a per-warp staging area in shared memory -- slot h, tile k, lane l at
+ * ((h*K + k)*32 + l)*16 -- and commits them as one group; masked elements are zero-filled by the copy itself (source size
+ * 0). Nothing here waits for memory. PfTake later waits for exactly this group (cp.async groups complete in order, and at
+ * that point D-1 newer groups are in flight) and reads the 16 bytes back with one shared-memory load. Completion is tracked
+ * by the copy engine per thread, so a lane only ever reads what it wrote itself and no warp synchronisation is needed.
+ * Same addressing and masking rules as tile_rw.
+ */
+__device__ __forceinline__ void cp_async_f32(uint32_t dst, const void *src, bool ok)
+{
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(dst), "l"(src), "r"(ok ? 4 : 0) : "memory");
+}
+template <int LAYOUT, int K, int H, int KI>
+__device__ __forceinline__ void tile_issue(const TileInfo *ti, uint32_t operand, const Ctx &cx)
+{
+    const int arg = operand & 15;
+    const int off = (int)(operand >> 4);
+    const int lane = cx.lane;
+    char *base = reinterpret_cast<char *>(ti->ptr[arg]);
+    const int2 s1 = ti->s1[arg];
+    const uint32_t dst = cx.hidden + (uint32_t)((H * K + KI) * 512);   // cx.hidden already includes lane*16
+    if constexpr (LAYOUT == LAY_1D) {
+        const int e = lane + off;
+        if (s1.y == 1 && off + 128 <= s1.x) {  // full unit-stride tile: four unmasked copies at fixed offsets
+            const char *p = base + (long long)e * 4;
+            asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n\t"
+                         "cp.async.ca.shared.global [%0+4], [%1+128], 4;\n\t"
+                         "cp.async.ca.shared.global [%0+8], [%1+256], 4;\n\t"
+                         "cp.async.ca.shared.global [%0+12], [%1+384], 4;" ::"r"(dst), "l"(p) : "memory");
+            return;
+        }
+        const char *p = base + (long long)(e * s1.y) * 4;
+        const long long pstep = (long long)(s1.y * 32) * 4;
+#pragma unroll
+        for (int w = 0; w < 4; w++) {
+            const bool ok = e + 32 * w < s1.x;
+            cp_async_f32(dst + 4 * w, ok ? p + w * pstep : base, ok);
+        }
+    } else {  // LAY_2DW
+        const int2 s2 = ti->s2[arg];
+        const int adv = ti->adv[arg];
+        const int t = lane + adv;
+        const int j0 = off;
+        const bool tok = t < s1.x;
+        if ((ti->flags[arg] & kVecRows) && (j0 & 3) == 0 && j0 + 4 <= s2.x) {
+            const char *p = base + (long long)(t * s1.y + j0) * 4;
+            asm volatile("cp.async.ca.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(tok ? p : base), "r"(tok ? 16 : 0) : "memory");
+        } else {
+            const char *p = base + (long long)(t * s1.y + j0 * s2.y) * 4;
+            const long long pstep = (long long)s2.y * 4;
+#pragma unroll
+            for (int w = 0; w < 4; w++) {
+                const bool ok = tok && (j0 + w < s2.x);
+                cp_async_f32(dst + 4 * w, ok ? p + w * pstep : base, ok);
+            }
+        }
+    }
+}
+template <int K, int SLOT, int H, int KI> __device__ __forceinline__ void take_hidden(const Ctx &cx)
+{
+    const uint32_t src = cx.hidden + (uint32_t)((H * K + KI) * 512);
+    asm volatile("ld.shared.v2.b64 {%%gs%0, %%gs%1}, [%2];" ::"n"(gs<K>(SLOT, KI, 0)), "n"(gs<K>(SLOT, KI, 1)), "r"(src) : "memory");
+}
+
 template <int OP, int SP, int P, int K, int KI>
 __device__ __forceinline__ void exec_tile(const uint32_t operand, const Ctx &cx)
 {
     constexpr int T = SP - 1;  // top of stack; T-1 = second ("S"), T-2 = third ("U")
 #define LO(slot) gs<K>((slot), KI, 0)
 #define HI(slot) gs<K>((slot), KI, 1)
+    /* ---- early-issued loads (internal opcodes) ---- */
+    if constexpr (OP >= OP_PfTake0) {
+        constexpr int H = (OP - OP_PfTake0) & 3;
+        constexpr int kind = (OP - OP_PfTake0) >> 2;  // 0 take, 1 issue 1D, 2 issue 2DW, 3 take+issue 1D, 4 take+issue 2DW
+        if constexpr (kind == 0 || kind >= 3) take_hidden<K, SP, H, KI>(cx);
+        if constexpr (kind == 1 || kind == 3) tile_issue<LAY_1D, K, H, KI>(cx.tiles + KI, operand, cx);
+        if constexpr (kind == 2 || kind == 4) tile_issue<LAY_2DW, K, H, KI>(cx.tiles + KI, operand, cx);
+    }
     /* ---- float ALU (arith.py:15-66): binary handlers compute fn(T, S) ---- */
-    if constexpr (OP == OP_Nop || OP == OP_Pop || OP == OP_Pop2) {
+    else if constexpr (OP == OP_Nop || OP == OP_Pop || OP == OP_Pop2) {
     } else if constexpr (OP == OP_FAdd) {
         r_add2<LO(T - 1), LO(T), LO(T - 1)>();
         r_add2<HI(T - 1), HI(T), HI(T - 1)>();
@@ -685,7 +761,16 @@ template <int OP, int SP, int P, int K, int... KI>
 __device__ __forceinline__ void exec_all(const uint32_t operand, const Ctx &cx, std::integer_sequence<int, KI...>)
 {
     if constexpr (OP == OP_AdvanceBlock2D || OP == OP_AdvanceBase) __syncwarp();
+    if constexpr (OP >= OP_PfTake0) {
+        constexpr int kind = (OP - OP_PfTake0) >> 2;
+        /* One cp.async group per early-issued load (all K tiles together). When load n is taken, the D-1 loads after it
+         * are in flight, so "all but the newest D-1 groups" is exactly "load n has landed"; a plain PfTake belongs to the
+         * tail of the program, where fewer are in flight, and simply waits for everything. */
+        if constexpr (kind >= 3) asm volatile("cp.async.wait_group %0;" ::"n"(hidden_slots(P) - 1) : "memory");
+        else if constexpr (kind == 0) asm volatile("cp.async.wait_group 0;" ::: "memory");
+    }
     (exec_tile<OP, SP, P, K, KI>(operand, cx), ...);
+    if constexpr (OP >= OP_PfIssue1D0) asm volatile("cp.async.commit_group;" ::: "memory");
     if constexpr (OP == OP_AdvanceBlock2D || OP == OP_AdvanceBase) __syncwarp();
 }
 
@@ -758,9 +843,9 @@ __device__ __forceinline__ void interpret(const uint2 *code, uint32_t n_entries,
         else asm volatile("// GINT_DISPATCH %0 site entry depth all;" ::"r"(key));
         switch (key) {
 #define GINT_CASE_SP(num, spv)                                                                          \
-    case (spv) * GINT_N_OPCODES + (num):                                                                \
+    case (spv) * GINT_N_DISPATCH + (num):                                                                \
         if constexpr (op_valid<num, spv, P>()) {                                                        \
-            asm volatile("// GINT_TARGET %0;" ::"n"((spv) * GINT_N_OPCODES + (num)));                   \
+            asm volatile("// GINT_TARGET %0;" ::"n"((spv) * GINT_N_DISPATCH + (num)));                   \
             if constexpr ((num) == OP_Halt) return;                                                     \
             else {                                                                                      \
                 constexpr int next_depth = (spv) + OpInfo<num>::net_effect;                             \
@@ -768,10 +853,10 @@ __device__ __forceinline__ void interpret(const uint2 *code, uint32_t n_entries,
                 state_advance<SMEM_CODE>(operand, opc);                                                 \
                 GINT_GUARD_STEP                                                                         \
                 exec_all<num, spv, P, K>(operand, cx, std::make_integer_sequence<int, K>());            \
-                asm volatile("add.u32 %%gkey, %0, %1;" ::"r"(opc), "n"(next_depth * GINT_N_OPCODES));   \
+                asm volatile("add.u32 %%gkey, %0, %1;" ::"r"(opc), "n"(next_depth * GINT_N_DISPATCH));   \
                 if constexpr (THREADED)                                                                 \
                     asm volatile("// GINT_DISPATCH %0 site %1 depth %2;" ::"r"(opc),                     \
-                                 "n"((spv) * GINT_N_OPCODES + (num)), "n"(next_depth));                 \
+                                 "n"((spv) * GINT_N_DISPATCH + (num)), "n"(next_depth));                 \
             }                                                                                           \
         }                                                                                               \
         continue;
@@ -779,6 +864,7 @@ __device__ __forceinline__ void interpret(const uint2 *code, uint32_t n_entries,
     GINT_CASE_SP(num, 0) GINT_CASE_SP(num, 1) GINT_CASE_SP(num, 2) GINT_CASE_SP(num, 3) GINT_CASE_SP(num, 4)       \
     GINT_CASE_SP(num, 5) GINT_CASE_SP(num, 6) GINT_CASE_SP(num, 7) GINT_CASE_SP(num, 8)
             GINT_OPCODE_LIST(GINT_X_CASES)
+            GINT_INTERNAL_OPCODE_LIST(GINT_X_CASES)
 #undef GINT_X_CASES
 #undef GINT_CASE_SP
         default:
@@ -839,12 +925,12 @@ static __device__ __noinline__ void stage_for_warp(uint2 *code_s, const uint2 *c
 }
 
 /* Direct mode: every logical program runs the same bytecode. Persistent blocks of kWarpsPerBlock warps;
- * shared memory = [program | descriptor block | kWarpsPerBlock x K TileInfo]. */
+ * shared memory = [program | descriptor block | kWarpsPerBlock x K TileInfo | kWarpsPerBlock x load staging]. */
 template <int P, int K>
 __device__ __forceinline__ void geval_direct_body(const LaunchArgs &a)
 {
     extern __shared__ __align__(16) unsigned char smem[];
-    pool_declare<P, K>();
+    pool_declare<P, K, hidden_slots(P)>();
     state_declare<true>();
     uint2 *code_s = reinterpret_cast<uint2 *>(smem);
     gint_tensor_info *ti_s = reinterpret_cast<gint_tensor_info *>(smem + a.code_smem_bytes);
@@ -862,6 +948,11 @@ __device__ __forceinline__ void geval_direct_body(const LaunchArgs &a)
     Ctx cx;
     cx.tiles = tiles_s + warp * K;
     cx.lane = lane;
+    {   // load staging area: after the tile descriptors, hidden_slots(P) * K * 512 bytes per warp
+        unsigned char *stage = reinterpret_cast<unsigned char *>(tiles_s + kWarpsPerBlock * K) +
+                               (size_t)warp * (hidden_slots(P) * K * 512) + lane * 16;
+        cx.hidden = (uint32_t)__cvta_generic_to_shared(stage);
+    }
 
     const uint32_t n_groups = (a.end - a.first + (uint32_t)K - 1u) / (uint32_t)K;
     for (uint32_t g = blockIdx.x * kWarpsPerBlock + warp; g < n_groups; g += gridDim.x * kWarpsPerBlock) {
@@ -879,7 +970,7 @@ template <int P>
 __device__ __forceinline__ void geval_indirect_body(const IndirectArgs &a)
 {
     extern __shared__ __align__(16) unsigned char smem[];
-    pool_declare<P, 1>();
+    pool_declare<P, 1, hidden_slots(P)>();
     state_declare<true>();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     unsigned char *mine = smem + (size_t)warp * (sizeof(TileInfo) + kTensorInfoSmemBytes + a.code_smem_bytes);
@@ -888,6 +979,7 @@ __device__ __forceinline__ void geval_indirect_body(const IndirectArgs &a)
     Ctx cx;
     cx.tiles = reinterpret_cast<TileInfo *>(mine);
     cx.lane = lane;
+    cx.hidden = 0;   // indirect mode runs programs as written (no early-issued loads)
     for (uint32_t g = blockIdx.x * kWarpsPerBlock + warp; g < a.grid_dim; g += gridDim.x * kWarpsPerBlock) {
         const IndirectEntry e = a.table[g];
         __syncwarp();  // every lane is done with the previous program's code and descriptors

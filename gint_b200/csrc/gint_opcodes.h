@@ -120,9 +120,26 @@
     X(FPermW, 104, 1, 0) \
     X(FShuf2, 105, 2, -1)
 
+/*
+ * Internal opcodes. They never appear in a gint bytecode stream; the host pre-decoder (gint_capi.cu) introduces them when
+ * it turns tile loads into "issue early, take later" pairs (see interpret / exec_tile in gint_interp.cuh):
+ *   PfTake<h>            push the four values waiting in hidden slot h
+ *   PfIssue1D<h>/2DW<h>  start the tile load described by the operand into hidden slot h (no stack effect)
+ *   PfTakeIssue..<h>     PfTake<h>, then start the load described by the operand into the slot just emptied
+ */
+#define GINT_MAX_HIDDEN 4
+#define GINT_INTERNAL_OPCODE_LIST(X) \
+    X(PfTake0, 106, 0, 1) X(PfTake1, 107, 0, 1) X(PfTake2, 108, 0, 1) X(PfTake3, 109, 0, 1) \
+    X(PfIssue1D0, 110, 0, 0) X(PfIssue1D1, 111, 0, 0) X(PfIssue1D2, 112, 0, 0) X(PfIssue1D3, 113, 0, 0) \
+    X(PfIssue2DW0, 114, 0, 0) X(PfIssue2DW1, 115, 0, 0) X(PfIssue2DW2, 116, 0, 0) X(PfIssue2DW3, 117, 0, 0) \
+    X(PfTakeIssue1D0, 118, 0, 1) X(PfTakeIssue1D1, 119, 0, 1) X(PfTakeIssue1D2, 120, 0, 1) X(PfTakeIssue1D3, 121, 0, 1) \
+    X(PfTakeIssue2DW0, 122, 0, 1) X(PfTakeIssue2DW1, 123, 0, 1) X(PfTakeIssue2DW2, 124, 0, 1) X(PfTakeIssue2DW3, 125, 0, 1)
+#define GINT_N_DISPATCH 126   /* opcodes the kernels dispatch on: the 106 of the format + 20 internal ones */
+
 enum gint_opcode {
 #define GINT_X_ENUM(name, num, md, net) OP_##name = num,
     GINT_OPCODE_LIST(GINT_X_ENUM)
+    GINT_INTERNAL_OPCODE_LIST(GINT_X_ENUM)
 #undef GINT_X_ENUM
 };
 

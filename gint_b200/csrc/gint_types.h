@@ -16,12 +16,15 @@ typedef unsigned long long u64;
 constexpr int kWarpsPerBlock = 4;
 constexpr int kThreadsPerBlock = kWarpsPerBlock * 32;
 constexpr int kTensorInfoSmemBytes = 640;  // 608-byte descriptor block, padded to a 128-byte multiple
-constexpr int kNumKeys = (GINT_MAX_STACK + 1) * GINT_N_OPCODES;
+constexpr int kNumKeys = (GINT_MAX_STACK + 1) * GINT_N_DISPATCH;
 
-/* Minimum resident blocks per SM requested from the compiler (caps registers per thread): the pool itself
- * takes 4*P*K registers. */
+/* Hidden load slots per kernel geometry: how many tile loads per logical program may be in flight ahead of their use. */
+__host__ __device__ constexpr int hidden_slots(int P) { return P <= 4 ? 4 : 2; }
+
+/* Minimum resident blocks per SM requested from the compiler (caps registers per thread): the pool itself takes 4*P*K
+ * registers; addresses and interpreter state take about 40 more. */
 #ifndef GINT_MIN_BLOCKS
-#define GINT_MIN_BLOCKS(P, K) ((P) * (K) <= 7 ? 8 : (P) * (K) <= 16 ? 5 : 4)
+#define GINT_MIN_BLOCKS(P, K) ((P) * (K) <= 7 ? 8 : (P) * (K) <= 8 ? 7 : (P) * (K) <= 16 ? 5 : 4)
 #endif
 
 /* Per logical program, decoded once into shared memory (the reference's BlockTensorInfo,

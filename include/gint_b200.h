@@ -75,7 +75,7 @@ typedef struct gint_launch_info {
     int32_t regs_per_thread;
     int32_t blocks_per_sm;
     int32_t num_sms;
-    int32_t staged_row_tensors; /* bit t set = tensor slot t is staged into shared memory */
+    int32_t staged_row_tensors; /* tile loads per logical program that are started ahead of their use (early issue) */
     int32_t reserved[7];
 } gint_launch_info;
 
@@ -170,7 +170,9 @@ int gint_execute_indirect_static(gint_ctx *ctx, const uint64_t *handles, int n_p
 
 /* ---- tuning knobs (benchmarks / tests) ---------------------------------------------------------- */
 
-/* Force tiles-per-warp (0 = automatic) and row staging (-1 = automatic, 0 = off, 1 = on) for later launches. */
+/* Knobs for later launches: "tiles_per_warp" (0 = automatic, else upper bound 1/2/4), "early_issue" (1 = start tile
+ * loads ahead of their use when safe, default; 0 = run programs exactly as written), "prefetch" (L2 footprint prefetch,
+ * default 0), "max_blocks" (cap on the persistent grid, 0 = none). */
 int gint_set_option(gint_ctx *ctx, const char *name, int value);
 
 #ifdef __cplusplus
