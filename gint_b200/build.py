@@ -29,7 +29,7 @@ CSRC = os.path.join(PKG_DIR, "csrc")
 KERNELS = os.path.join(CSRC, "kernels")
 OBJ_DIR = os.path.join(CSRC, "build")
 LIB_PATH = os.path.join(PKG_DIR, "libgint_b200.so")
-N_OPS = 126          # GINT_N_DISPATCH: the 106 opcodes of the format + 20 internal ones
+N_OPS = 141          # GINT_N_DISPATCH: the 106 opcodes of the format + the internal ones
 N_KEYS = 9 * N_OPS   # (GINT_MAX_STACK + 1) * GINT_N_DISPATCH
 
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
@@ -72,7 +72,8 @@ def _build_kernel(src: str, extra: list[str], jump_table: bool) -> tuple[str, st
             f.write(text)
         log += f"jump table: {stats['cases']} cases over {stats['keys']} keys\n"
     t1 = time.time()
-    log += _run([_nvcc(), "-arch=sm_100a", "-cubin", "-lineinfo", "-Xptxas", "-v", ptx, "-o", cubin], f"ptxas {stem}")
+    # -fmad=false again: ptxas would otherwise contract the adjacent mul.rn.f32x2 / add.rn.f32x2 of a fused handler into an fma
+    log += _run([_nvcc(), "-arch=sm_100a", "-cubin", "-lineinfo", "-fmad=false", "-Xptxas", "-v", ptx, "-o", cubin], f"ptxas {stem}")
     log += f"build time: nvcc -ptx {t1 - t0:.0f} s, ptxas {time.time() - t1:.0f} s\n"
     asm = os.path.join(OBJ_DIR, stem + ".S")
     with open(asm, "w") as f:

@@ -18,8 +18,9 @@
 #include <vector>
 
 #include "../../include/gint_b200.h"
-#include "gint_types.h"
+#include "gint_fused.h"
 #include "gint_opcodes.h"
+#include "gint_types.h"
 #include "gint_variants.h"
 
 using gint::IndirectArgs;
@@ -114,11 +115,46 @@ int normalise(const int32_t *code, int n_words, int n_tensors, std::vector<Insn>
     return GINT_OK;
 }
 
+struct FusedDef { int num, len; int ops[GINT_MAX_FUSED_LEN]; };
+const FusedDef kFused[GINT_N_FUSED] = {
+#define GINT_X_FDEF(num, len, ...) {num, len, {__VA_ARGS__}},
+    GINT_FUSED_LIST(GINT_X_FDEF)
+#undef GINT_X_FDEF
+};
+constexpr int OP_CARRIER = -1;   // an instruction absorbed into the fused handler before it: only its operand is used
+
 int net_effect(int op)
 {
+    if (op == OP_CARRIER) return 0;
     if (op < GINT_N_OPCODES) return kEffects[op].net;
-    const int kind = (op - OP_PfTake0) >> 2;   // 0 take, 1/2 issue, 3/4 take+issue
-    return (kind == 1 || kind == 2) ? 0 : 1;
+    if (op >= GINT_FUSED_FIRST) {
+        int net = 0;
+        const FusedDef &f = kFused[op - GINT_FUSED_FIRST];
+        for (int j = 0; j < f.len; j++) net += net_effect(f.ops[j]);
+        return net;
+    }
+    return (op == OP_PfTake || op == OP_PfTakeIssue1D || op == OP_PfTakeIssue2DW) ? 1 : 0;
+}
+
+/* Replace known instruction sequences by fused handlers (gint_fused.h): greedy, longest match first. The absorbed
+ * instructions stay in the stream as operand carriers. */
+void fuse_sequences(std::vector<Insn> *prog)
+{
+    std::vector<Insn> &p = *prog;
+    for (size_t i = 0; i < p.size();) {
+        int best = -1;
+        for (int k = 0; k < GINT_N_FUSED; k++) {
+            const FusedDef &f = kFused[k];
+            if (i + (size_t)f.len > p.size() || (best >= 0 && f.len <= kFused[best].len)) continue;
+            bool match = true;
+            for (int j = 0; j < f.len && match; j++) match = p[i + (size_t)j].op == f.ops[j];
+            if (match) best = k;
+        }
+        if (best < 0) { i++; continue; }
+        p[i].op = kFused[best].num;
+        for (int j = 1; j < kFused[best].len; j++) p[i + (size_t)j].op = OP_CARRIER;
+        i += (size_t)kFused[best].len;
+    }
 }
 
 /* Stream layout, skewed for threaded dispatch: entry 0 = {0, opcode of insn 0}; entry i+1 = {operand of insn i, opcode of
@@ -130,7 +166,10 @@ void emit_stream(const std::vector<Insn> &prog, std::vector<uint2> *out, std::ve
     out->clear();
     out->reserve(n + 4);
     out->push_back(make_uint2(0u, (uint32_t)prog[0].op));
-    for (size_t i = 0; i < n; i++) out->push_back(make_uint2(prog[i].operand, i + 1 < n ? (uint32_t)prog[i + 1].op : (uint32_t)OP_Halt));
+    for (size_t i = 0; i < n; i++) {
+        const int next = i + 1 < n ? prog[i + 1].op : OP_Halt;
+        out->push_back(make_uint2(prog[i].operand, next == OP_CARRIER ? (uint32_t)OP_Halt : (uint32_t)next));
+    }
     out->push_back(make_uint2(0u, OP_Halt));  // handlers fetch one entry ahead
     if (out->size() & 1) out->push_back(make_uint2(0u, OP_Halt));
     if (depth_out) {
@@ -188,7 +227,9 @@ void early_issue_transform(const std::vector<Insn> &in, int D, EarlyIssue *out)
     std::vector<Member> ring;
     for (size_t i = 0; i < prog.size(); i++) {
         const int op = prog[i].op;
-        if (op != OP_LoadGlobal1DF32 && op != OP_LoadGlobal2DWF32) continue;
+        /* 1-D tile loads only: for 2DW rows (one 16-byte access per thread, mostly L1 hits) the staging round trip costs
+         * more than it hides (measured on the batched 4x4 programs) */
+        if (op != OP_LoadGlobal1DF32) continue;
         const int slot = (int)(prog[i].operand & 15u);
         const size_t n = ring.size();
         const size_t from = n >= (size_t)D ? ring[n - (size_t)D].site + 1 : 0;   // first instruction the load would move across
@@ -207,17 +248,18 @@ void early_issue_transform(const std::vector<Insn> &in, int D, EarlyIssue *out)
     out->prog.clear();
     if (ring.empty()) { out->prog = prog; return; }
     const size_t R = ring.size();
-    for (size_t n = 0; n < R && n < (size_t)D; n++)
-        out->prog.push_back(Insn{(ring[n].layout == 1 ? OP_PfIssue1D0 : OP_PfIssue2DW0) + (int)(n % (size_t)D), ring[n].operand});
+    for (size_t n = 0; n < (size_t)D; n++) {   // prologue: fill the ring (padded so that it wraps back to slot 0)
+        if (n < R) out->prog.push_back(Insn{ring[n].layout == 1 ? OP_PfIssue1D : OP_PfIssue2DW, ring[n].operand});
+        else out->prog.push_back(Insn{OP_PfSkip, 0u});
+    }
     size_t next = 0;
     for (size_t i = 0; i < prog.size(); i++) {
         if (next < R && ring[next].site == i) {
-            const int h = (int)(next % (size_t)D);
             if (next + (size_t)D < R) {
                 const Member &f = ring[next + (size_t)D];
-                out->prog.push_back(Insn{(f.layout == 1 ? OP_PfTakeIssue1D0 : OP_PfTakeIssue2DW0) + h, f.operand});
+                out->prog.push_back(Insn{f.layout == 1 ? OP_PfTakeIssue1D : OP_PfTakeIssue2DW, f.operand});
             } else {
-                out->prog.push_back(Insn{OP_PfTake0 + h, 0u});
+                out->prog.push_back(Insn{OP_PfTake, 0u});
             }
             next++;
         } else {
@@ -356,6 +398,7 @@ struct gint_ctx {
     int opt_max_blocks = 0;
     int opt_prefetch = 0;
     int opt_early_issue = 1;
+    int opt_fuse = 1;           // applies to programs created afterwards
     /* scratch for indirect launches */
     void *ind_dev = nullptr;
     void *ind_host = nullptr;
@@ -493,6 +536,8 @@ int launch_direct(gint_ctx *ctx, uint64_t handle, const uint64_t *base_ptrs, int
     a.end = first + count;
     a.code_smem_bytes = g.code_smem;
     a.prefetch_mask = ctx->opt_prefetch ? p->prefetch_mask : 0u;
+    a.zero = 0;
+    a.reserved = 0;
     for (int t = 0; t < GINT_MAX_TENSORS; t++) a.fp[t] = p->fp[t];
     a.ti = p->ti;
     for (int i = 0; i < n_tensors; i++) a.ti.base_ptr[i] = (int64_t)base_ptrs[i];
@@ -672,8 +717,13 @@ int gint_program_create(gint_ctx *ctx, const int32_t *code, int n_words, const g
     if (!ctx || !code || !out_handle || (!ti && n_tensors > 0)) return fail(ctx, GINT_ERR_INVALID_ARGUMENT, "null argument");
     if (n_tensors < 0 || n_tensors > GINT_MAX_TENSORS) return fail(ctx, GINT_ERR_INVALID_ARGUMENT, "at most 8 tensors");
     std::vector<uint2> pre;
-    int rc = predecode(code, n_words, n_tensors, &pre);
-    if (rc != GINT_OK) return fail(ctx, rc, gint_status_string(rc));
+    {
+        std::vector<Insn> plain;
+        int rc = normalise(code, n_words, n_tensors, &plain);
+        if (rc != GINT_OK) return fail(ctx, rc, gint_status_string(rc));
+        if (ctx->opt_fuse) fuse_sequences(&plain);
+        emit_stream(plain, &pre);
+    }
     Program *p = new Program();
     analyze(code, n_words, &p->st);
     p->n_tensors = n_tensors;
@@ -696,7 +746,11 @@ int gint_program_create(gint_ctx *ctx, const int32_t *code, int n_words, const g
             for (int b = 0; b < n_tensors; b++)
                 if ((ei.alias_slots[t] >> b) & 1u) { if (tensor_extent_bytes(p->ti, b) == 0) usable = false; }
         }
-        if (usable) { emit_stream(ei.prog, &early); p->n_early = ei.n_early; }
+        if (usable) {
+            if (ctx->opt_fuse) fuse_sequences(&ei.prog);
+            emit_stream(ei.prog, &early);
+            p->n_early = ei.n_early;
+        }
     }
     {
         DeviceGuard guard(ctx->device);
@@ -934,12 +988,51 @@ int gint_execute_indirect_static(gint_ctx *ctx, const uint64_t *handles, int n_p
     return GINT_OK;
 }
 
+int gint_debug_transform(const int32_t *code, int n_words, const gint_tensor_info *ti, int n_tensors, int early_issue, int fuse,
+                         int32_t *out_ops, uint32_t *out_operands, int max_insns)
+{
+    std::vector<Insn> prog;
+    int rc = normalise(code, n_words, n_tensors, &prog);
+    if (rc != GINT_OK) return rc;
+    if (early_issue) {
+        gint_bytecode_stats st;
+        analyze(code, n_words, &st);
+        EarlyIssue ei;
+        early_issue_transform(prog, gint::hidden_slots(st.pool_size), &ei);
+        prog = ei.prog;
+    }
+    if (fuse) fuse_sequences(&prog);
+    (void)ti;
+    if ((int)prog.size() > max_insns) return GINT_ERR_INVALID_ARGUMENT;
+    for (size_t i = 0; i < prog.size(); i++) {
+        if (out_ops) out_ops[i] = prog[i].op;
+        if (out_operands) out_operands[i] = prog[i].operand;
+    }
+    return (int)prog.size();
+}
+
+int gint_debug_fused_table(int32_t *out, int max_entries)
+{
+    if (!out || max_entries < GINT_N_FUSED) return GINT_ERR_INVALID_ARGUMENT;
+    for (int k = 0; k < GINT_N_FUSED; k++) {
+        int32_t *row = out + (size_t)k * (2 + GINT_MAX_FUSED_LEN);
+        row[0] = kFused[k].num;
+        row[1] = kFused[k].len;
+        for (int j = 0; j < GINT_MAX_FUSED_LEN; j++) row[2 + j] = j < kFused[k].len ? kFused[k].ops[j] : -1;
+    }
+    return GINT_N_FUSED;
+}
+
 int gint_set_option(gint_ctx *ctx, const char *name, int value)
 {
     if (!ctx || !name) return GINT_ERR_INVALID_ARGUMENT;
     if (strcmp(name, "tiles_per_warp") == 0) {
         if (value != 0 && value != 1 && value != 2 && value != 4) return fail(ctx, GINT_ERR_INVALID_ARGUMENT, "tiles_per_warp must be 0, 1, 2 or 4");
         ctx->opt_tiles_per_warp = value;
+        return GINT_OK;
+    }
+    if (strcmp(name, "fuse") == 0) {
+        ctx->opt_fuse = value != 0;
         return GINT_OK;
     }
     if (strcmp(name, "early_issue") == 0) {

@@ -32,6 +32,7 @@
 #include <utility>
 
 #include "../../include/gint_b200.h"
+#include "gint_fused.h"
 #include "gint_opcodes.h"
 #include "gint_types.h"
 
@@ -470,16 +471,53 @@ GINT_OPCODE_LIST(GINT_X_INFO)
 GINT_INTERNAL_OPCODE_LIST(GINT_X_INFO)
 #undef GINT_X_INFO
 
+template <int OP, int SP, int P> __host__ __device__ constexpr bool op_valid();
+
+/* Fused handlers (gint_fused.h): a sequence's stack effect and validity follow from its members. */
+template <int... OPS> struct Seq { static constexpr int n = sizeof...(OPS); };
+template <int NUM> struct FusedSeq;
+#define GINT_X_FSEQ(num, len, ...) template <> struct FusedSeq<num> { using type = Seq<__VA_ARGS__>; static_assert(Seq<__VA_ARGS__>::n == len, "length"); };
+GINT_FUSED_LIST(GINT_X_FSEQ)
+#undef GINT_X_FSEQ
+static_assert(GINT_FUSED_FIRST + GINT_N_FUSED == GINT_N_DISPATCH, "gint_fused.h and gint_opcodes.h disagree");
+
+template <typename S> struct SeqInfo;
+template <> struct SeqInfo<Seq<>> {
+    static constexpr int net = 0, min_depth = 0;
+    template <int SP, int P> static constexpr bool valid() { return true; }
+};
+template <int OP0, int... REST> struct SeqInfo<Seq<OP0, REST...>> {
+    using Tail = SeqInfo<Seq<REST...>>;
+    static constexpr int net = OpInfo<OP0>::net_effect + Tail::net;
+    static constexpr int tail_need = Tail::min_depth - OpInfo<OP0>::net_effect;
+    static constexpr int min_depth = OpInfo<OP0>::min_depth > tail_need ? OpInfo<OP0>::min_depth : tail_need;
+    template <int SP, int P> static constexpr bool valid()
+    {
+        if constexpr (!op_valid<OP0, SP, P>()) return false;
+        else return Tail::template valid<SP + OpInfo<OP0>::net_effect, P>();
+    }
+};
+#define GINT_X_FINFO(num, len, ...)                                                                        \
+    template <> struct OpInfo<num> {                                                                       \
+        static constexpr int min_depth = SeqInfo<Seq<__VA_ARGS__>>::min_depth;                             \
+        static constexpr int net_effect = SeqInfo<Seq<__VA_ARGS__>>::net;                                  \
+    };
+GINT_FUSED_LIST(GINT_X_FINFO)
+#undef GINT_X_FINFO
+
 template <int OP, int SP, int P> __host__ __device__ constexpr bool op_valid()
 {
-    constexpr int limit = P < GINT_MAX_STACK ? P : GINT_MAX_STACK;
-    if (SP > limit || SP < OpInfo<OP>::min_depth) return false;
-    if (SP + OpInfo<OP>::net_effect > limit) return false;
-    if (OP == OP_DupX2 && SP + 1 > limit) return false;
-    if (OP >= OP_FLoadReg0 && OP <= OP_FLoadReg7 && (P - 1 - (OP - OP_FLoadReg0)) < 0) return false;
-    if (OP >= OP_FStoreReg0 && OP <= OP_FStoreReg7 && (P - 1 - (OP - OP_FStoreReg0)) < 0) return false;
-    if (OP >= OP_PfTake0 && ((OP - OP_PfTake0) & 3) >= hidden_slots(P)) return false;
-    return true;
+    if constexpr (OP >= GINT_FUSED_FIRST) {
+        return SP >= 0 && SeqInfo<typename FusedSeq<OP>::type>::template valid<SP, P>();
+    } else {
+        constexpr int limit = P < GINT_MAX_STACK ? P : GINT_MAX_STACK;
+        if (SP > limit || SP < OpInfo<OP>::min_depth) return false;
+        if (SP + OpInfo<OP>::net_effect > limit) return false;
+        if (OP == OP_DupX2 && SP + 1 > limit) return false;
+        if (OP >= OP_FLoadReg0 && OP <= OP_FLoadReg7 && (P - 1 - (OP - OP_FLoadReg0)) < 0) return false;
+        if (OP >= OP_FStoreReg0 && OP <= OP_FStoreReg7 && (P - 1 - (OP - OP_FStoreReg0)) < 0) return false;
+        return true;
+    }
 }
 
 /* 4-way select by a 2-bit index; indices are clamped to 0..3 by the host pre-decoder, which makes this equal to
@@ -521,8 +559,8 @@ GINT_MEMOP(LoadGlobal2DWU8, LAY_2DW, DT_U8, false)
 
 /*
  * Start a tile load whose values are not needed yet. Each lane copies the (up to) four elements it will consume with
- * cp.async into its own 16 bytes of a per-warp staging area in shared memory -- slot h, tile k, lane l at
- * ((h*K + k)*32 + l)*16 -- and commits them as one group; masked elements are zero-filled by the copy itself (source size
+ * cp.async into its own 16 bytes of a per-warp ring of staging slots in shared memory -- slot h, tile k, lane l at
+ * ((h*K + k)*32 + l)*16, the current slot being tracked in the named register %gring -- and commits them as one group; masked elements are zero-filled by the copy itself (source size
  * 0). Nothing here waits for memory. PfTake later waits for exactly this group (cp.async groups complete in order, and at
  * that point D-1 newer groups are in flight) and reads the 16 bytes back with one shared-memory load. Completion is tracked
  * by the copy engine per thread, so a lane only ever reads what it wrote itself and no warp synchronisation is needed.
@@ -532,15 +570,15 @@ __device__ __forceinline__ void cp_async_f32(uint32_t dst, const void *src, bool
 {
     asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(dst), "l"(src), "r"(ok ? 4 : 0) : "memory");
 }
-template <int LAYOUT, int K, int H, int KI>
-__device__ __forceinline__ void tile_issue(const TileInfo *ti, uint32_t operand, const Ctx &cx)
+template <int LAYOUT, int K, int KI>
+__device__ __forceinline__ void tile_issue(const TileInfo *ti, uint32_t operand, const Ctx &cx, uint32_t slot)
 {
     const int arg = operand & 15;
     const int off = (int)(operand >> 4);
     const int lane = cx.lane;
     char *base = reinterpret_cast<char *>(ti->ptr[arg]);
     const int2 s1 = ti->s1[arg];
-    const uint32_t dst = cx.hidden + (uint32_t)((H * K + KI) * 512);   // cx.hidden already includes lane*16
+    const uint32_t dst = slot + (uint32_t)(KI * 512);   // `slot` already includes this lane's 16-byte offset
     if constexpr (LAYOUT == LAY_1D) {
         const int e = lane + off;
         if (s1.y == 1 && off + 128 <= s1.x) {  // full unit-stride tile: four unmasked copies at fixed offsets
@@ -578,9 +616,9 @@ __device__ __forceinline__ void tile_issue(const TileInfo *ti, uint32_t operand,
         }
     }
 }
-template <int K, int SLOT, int H, int KI> __device__ __forceinline__ void take_hidden(const Ctx &cx)
+template <int K, int SLOT, int KI> __device__ __forceinline__ void take_hidden(uint32_t slot)
 {
-    const uint32_t src = cx.hidden + (uint32_t)((H * K + KI) * 512);
+    const uint32_t src = slot + (uint32_t)(KI * 512);
     asm volatile("ld.shared.v2.b64 {%%gs%0, %%gs%1}, [%2];" ::"n"(gs<K>(SLOT, KI, 0)), "n"(gs<K>(SLOT, KI, 1)), "r"(src) : "memory");
 }
 
@@ -590,16 +628,8 @@ __device__ __forceinline__ void exec_tile(const uint32_t operand, const Ctx &cx)
     constexpr int T = SP - 1;  // top of stack; T-1 = second ("S"), T-2 = third ("U")
 #define LO(slot) gs<K>((slot), KI, 0)
 #define HI(slot) gs<K>((slot), KI, 1)
-    /* ---- early-issued loads (internal opcodes) ---- */
-    if constexpr (OP >= OP_PfTake0) {
-        constexpr int H = (OP - OP_PfTake0) & 3;
-        constexpr int kind = (OP - OP_PfTake0) >> 2;  // 0 take, 1 issue 1D, 2 issue 2DW, 3 take+issue 1D, 4 take+issue 2DW
-        if constexpr (kind == 0 || kind >= 3) take_hidden<K, SP, H, KI>(cx);
-        if constexpr (kind == 1 || kind == 3) tile_issue<LAY_1D, K, H, KI>(cx.tiles + KI, operand, cx);
-        if constexpr (kind == 2 || kind == 4) tile_issue<LAY_2DW, K, H, KI>(cx.tiles + KI, operand, cx);
-    }
     /* ---- float ALU (arith.py:15-66): binary handlers compute fn(T, S) ---- */
-    else if constexpr (OP == OP_Nop || OP == OP_Pop || OP == OP_Pop2) {
+    if constexpr (OP == OP_Nop || OP == OP_Pop || OP == OP_Pop2) {
     } else if constexpr (OP == OP_FAdd) {
         r_add2<LO(T - 1), LO(T), LO(T - 1)>();
         r_add2<HI(T - 1), HI(T), HI(T - 1)>();
@@ -760,19 +790,75 @@ __device__ __forceinline__ void exec_tile(const uint32_t operand, const Ctx &cx)
 template <int OP, int SP, int P, int K, int... KI>
 __device__ __forceinline__ void exec_all(const uint32_t operand, const Ctx &cx, std::integer_sequence<int, KI...>)
 {
-    if constexpr (OP == OP_AdvanceBlock2D || OP == OP_AdvanceBase) __syncwarp();
-    if constexpr (OP >= OP_PfTake0) {
-        constexpr int kind = (OP - OP_PfTake0) >> 2;
-        /* One cp.async group per early-issued load (all K tiles together). When load n is taken, the D-1 loads after it
-         * are in flight, so "all but the newest D-1 groups" is exactly "load n has landed"; a plain PfTake belongs to the
-         * tail of the program, where fewer are in flight, and simply waits for everything. */
-        if constexpr (kind >= 3) asm volatile("cp.async.wait_group %0;" ::"n"(hidden_slots(P) - 1) : "memory");
-        else if constexpr (kind == 0) asm volatile("cp.async.wait_group 0;" ::: "memory");
+    if constexpr (OP >= OP_PfTake) {
+        /* Early-issued loads. One cp.async group per load (all K tiles together). When load n is taken, the D-1 loads
+         * after it are in flight, so "all but the newest D-1 groups have landed" is exactly "load n has landed"; a plain
+         * PfTake belongs to the tail of the program, where fewer are in flight, and simply waits for everything. */
+        constexpr int D = hidden_slots(P);
+        constexpr bool take = OP == OP_PfTake || OP == OP_PfTakeIssue1D || OP == OP_PfTakeIssue2DW;
+        uint32_t ring;
+        asm volatile("mov.b32 %0, %%gring;" : "=r"(ring));
+        const uint32_t slot = cx.hidden + ring;
+        if constexpr (OP == OP_PfTake) asm volatile("cp.async.wait_group 0;" ::: "memory");
+        else if constexpr (take) asm volatile("cp.async.wait_group %0;" ::"n"(D - 1) : "memory");
+        if constexpr (take) (take_hidden<K, SP, KI>(slot), ...);
+        if constexpr (OP == OP_PfIssue1D || OP == OP_PfTakeIssue1D) (tile_issue<LAY_1D, K, KI>(cx.tiles + KI, operand, cx, slot), ...);
+        if constexpr (OP == OP_PfIssue2DW || OP == OP_PfTakeIssue2DW) (tile_issue<LAY_2DW, K, KI>(cx.tiles + KI, operand, cx, slot), ...);
+        if constexpr (OP != OP_PfTake && OP != OP_PfSkip) asm volatile("cp.async.commit_group;" ::: "memory");
+        asm volatile("add.u32 %%gring, %%gring, %0;\n\tand.b32 %%gring, %%gring, %1;" ::"n"(K * 512), "n"(D * K * 512 - 1));
+    } else {
+        if constexpr (OP == OP_AdvanceBlock2D || OP == OP_AdvanceBase) __syncwarp();
+        (exec_tile<OP, SP, P, K, KI>(operand, cx), ...);
+        if constexpr (OP == OP_AdvanceBlock2D || OP == OP_AdvanceBase) __syncwarp();
     }
-    (exec_tile<OP, SP, P, K, KI>(operand, cx), ...);
-    if constexpr (OP >= OP_PfIssue1D0) asm volatile("cp.async.commit_group;" ::: "memory");
-    if constexpr (OP == OP_AdvanceBlock2D || OP == OP_AdvanceBase) __syncwarp();
 }
+
+template <typename S> struct SeqFirst;
+template <int OP0, int... REST> struct SeqFirst<Seq<OP0, REST...>> { static constexpr int value = OP0; };
+template <typename S> __host__ __device__ constexpr int seq_first() { return SeqFirst<S>::value; }
+
+template <int A, int B> __device__ __forceinline__ void fma_barrier_one()
+{
+    asm volatile("xor.b64 %%gs%0, %%gs%0, %%gzero;\n\txor.b64 %%gs%1, %%gs%1, %%gzero;" ::"n"(A), "n"(B));
+}
+template <int K, int SLOT, int... KI> __device__ __forceinline__ void fma_barrier(std::integer_sequence<int, KI...>)
+{
+    (fma_barrier_one<gs<K>(SLOT, KI, 0), gs<K>(SLOT, KI, 1)>(), ...);
+}
+
+/* Run the members of a fused sequence back to back; member J takes its operand from ops[J] if it uses one. */
+template <typename S, int SP, int P, int K, int J> struct SeqRun;
+template <int SP, int P, int K, int J> struct SeqRun<Seq<>, SP, P, K, J> {
+    static __device__ __forceinline__ void run(const Ctx &, const uint32_t *) {}
+};
+template <int OP0, int... REST, int SP, int P, int K, int J> struct SeqRun<Seq<OP0, REST...>, SP, P, K, J> {
+    static __device__ __forceinline__ void run(const Ctx &cx, const uint32_t *ops)
+    {
+        exec_all<OP0, SP, P, K>(GINT_OP_USES_OPERAND(OP0) ? ops[J] : 0u, cx, std::make_integer_sequence<int, K>());
+        if constexpr (sizeof...(REST) > 0 && (OP0 == OP_FMul || OP0 == OP_FMulImm)) {
+            /* A product that the next member adds to or subtracts from: inside one handler ptxas contracts the packed
+             * multiply and add into a fused multiply-add (observed, even with --fmad=false and explicit .rn), which would
+             * change the rounding the bytecode asks for. XOR-ing the product with a zero that the assembler cannot see
+             * through keeps the two operations apart. */
+            constexpr int next = seq_first<Seq<REST...>>();
+            if constexpr (next == OP_FAdd || next == OP_FSub || next == OP_FRSub || next == OP_FAddImm)
+                fma_barrier<K, SP + OpInfo<OP0>::net_effect - 1>(std::make_integer_sequence<int, K>());
+        }
+        SeqRun<Seq<REST...>, SP + OpInfo<OP0>::net_effect, P, K, J + 1>::run(cx, ops);
+    }
+};
+template <typename S, int J> struct SeqFetch;
+template <int J> struct SeqFetch<Seq<>, J> {
+    static __device__ __forceinline__ void run(uint32_t, uint32_t *) {}
+};
+template <int OP0, int... REST, int J> struct SeqFetch<Seq<OP0, REST...>, J> {
+    static __device__ __forceinline__ void run(uint32_t base, uint32_t *ops)
+    {
+        /* member J >= 1 has its operand in stream entry (first entry of the sequence) + J, i.e. at [base + 8*(J-1)] */
+        if constexpr (J >= 1 && GINT_OP_USES_OPERAND(OP0)) asm volatile("ld.shared.u32 %0, [%1+%2];" : "=r"(ops[J]) : "r"(base), "n"(8 * (J - 1)));
+        SeqFetch<Seq<REST...>, J + 1>::run(base, ops);
+    }
+};
 
 /* ------------------------------------------------------------------------------------------------ */
 /* fetch / dispatch loop for one group of K logical programs                                          */
@@ -791,13 +877,15 @@ template <int N> __device__ __forceinline__ void pool_clear()
  *   %ge0, %ge1   the current stream entry {operand of this instruction, opcode of the next one}
  *   %gkey        dispatch key for the C++ fallback switch (dead once the jump tables are in place)
  *   %gbudget     instructions left before the interpreter gives up (only with GINT_GUARD, a debugging aid)
+ *   %gring       byte offset of the current slot in the warp's ring of early-issued loads
+ *   %gzero       64 bits of zero that reach the kernel as a launch parameter (see fma_barrier)
  * so no C++ value is live from handler to handler and a handler's basic block can be entered from any other handler.
  */
 template <bool SMEM> __device__ __forceinline__ void state_declare()
 {
     // (the unused "n" operand makes nvcc treat the string as a template, so that %% means %)
-    if constexpr (SMEM) asm volatile(".reg .b32 %%gc; .reg .b32 %%ge<2>; .reg .b32 %%gkey; .reg .b32 %%gbudget; // %0" ::"n"(0));
-    else asm volatile(".reg .b64 %%gc; .reg .b32 %%ge<2>; .reg .b32 %%gkey; .reg .b32 %%gbudget; // %0" ::"n"(0));
+    if constexpr (SMEM) asm volatile(".reg .b32 %%gc; .reg .b32 %%ge<2>; .reg .b32 %%gkey; .reg .b32 %%gbudget; .reg .b32 %%gring; .reg .b64 %%gzero; // %0" ::"n"(0));
+    else asm volatile(".reg .b64 %%gc; .reg .b32 %%ge<2>; .reg .b32 %%gkey; .reg .b32 %%gbudget; .reg .b32 %%gring; .reg .b64 %%gzero; // %0" ::"n"(0));
 }
 
 /* read the current entry, then start loading the following one */
@@ -824,16 +912,40 @@ template <bool SMEM> __device__ __forceinline__ void state_advance(uint32_t &ope
  * (depth, opcode) keys) and handlers branch back to it: one more branch per instruction, but a control-flow graph that
  * ptxas digests in seconds whatever surrounds the interpreter.
  */
+/* A fused handler covers n consecutive instructions i .. i+n-1. On entry %ge holds stream entry i+1 = {operand_i, -} and
+ * %gc points at entry i+2; the opcode to dispatch on afterwards sits in entry i+n and the entry the next handler expects
+ * in %ge is entry i+n+1. (Direct mode only: the stream is in shared memory.) */
+template <int NUM, int SP, int P, int K>
+__device__ __forceinline__ void run_fused(const Ctx &cx, uint32_t &next_opcode)
+{
+    using S = typename FusedSeq<NUM>::type;
+    constexpr int n = S::n;
+    uint32_t ops[GINT_MAX_FUSED_LEN];
+    uint32_t base;
+    asm volatile("mov.b32 %0, %%ge0; mov.b32 %1, %%gc;" : "=r"(ops[0]), "=r"(base));
+    asm volatile("ld.shared.u32 %0, [%1+%2];" : "=r"(next_opcode) : "r"(base), "n"(8 * (n - 2) + 4));
+    asm volatile("ld.shared.v2.u32 {%%ge0, %%ge1}, [%%gc+%0]; add.u32 %%gc, %%gc, %1;" ::"n"(8 * (n - 1)), "n"(8 * n) : "memory");
+    SeqFetch<S, 0>::run(base, ops);
+#ifdef GINT_GUARD
+    {
+        uint32_t left;
+        asm volatile("sub.u32 %%gbudget, %%gbudget, %1; mov.u32 %0, %%gbudget;" : "=r"(left) : "n"(n));
+        if ((int)left < 0) return;
+    }
+#endif
+    SeqRun<S, SP, P, K, 0>::run(cx, ops);
+}
+
 template <int P, int K, bool SMEM_CODE, bool THREADED>
 __device__ __forceinline__ void interpret(const uint2 *code, uint32_t n_entries, const Ctx &cx)
 {
     pool_clear<2 * P * K>();
     if constexpr (SMEM_CODE) {
         const uint32_t a = (uint32_t)__cvta_generic_to_shared(code);
-        asm volatile("ld.shared.u32 %%gkey, [%0+4]; ld.shared.v2.u32 {%%ge0, %%ge1}, [%0+8]; add.u32 %%gc, %0, 16; mov.u32 %%gbudget, %1;"
+        asm volatile("ld.shared.u32 %%gkey, [%0+4]; ld.shared.v2.u32 {%%ge0, %%ge1}, [%0+8]; add.u32 %%gc, %0, 16; mov.u32 %%gbudget, %1; mov.u32 %%gring, 0;"
                      ::"r"(a), "r"(n_entries) : "memory");
     } else {
-        asm volatile("ld.global.nc.u32 %%gkey, [%0+4]; ld.global.nc.v2.u32 {%%ge0, %%ge1}, [%0+8]; add.u64 %%gc, %0, 16; mov.u32 %%gbudget, %1;"
+        asm volatile("ld.global.nc.u32 %%gkey, [%0+4]; ld.global.nc.v2.u32 {%%ge0, %%ge1}, [%0+8]; add.u64 %%gc, %0, 16; mov.u32 %%gbudget, %1; mov.u32 %%gring, 0;"
                      ::"l"(code), "r"(n_entries) : "memory");
     }
     for (;;) {
@@ -850,9 +962,13 @@ __device__ __forceinline__ void interpret(const uint2 *code, uint32_t n_entries,
             else {                                                                                      \
                 constexpr int next_depth = (spv) + OpInfo<num>::net_effect;                             \
                 uint32_t operand, opc;                                                                  \
-                state_advance<SMEM_CODE>(operand, opc);                                                 \
-                GINT_GUARD_STEP                                                                         \
-                exec_all<num, spv, P, K>(operand, cx, std::make_integer_sequence<int, K>());            \
+                if constexpr ((num) >= GINT_FUSED_FIRST) {                                              \
+                    run_fused<num, spv, P, K>(cx, opc);                                                 \
+                } else {                                                                                \
+                    state_advance<SMEM_CODE>(operand, opc);                                             \
+                    GINT_GUARD_STEP                                                                     \
+                    exec_all<num, spv, P, K>(operand, cx, std::make_integer_sequence<int, K>());        \
+                }                                                                                       \
                 asm volatile("add.u32 %%gkey, %0, %1;" ::"r"(opc), "n"(next_depth * GINT_N_DISPATCH));   \
                 if constexpr (THREADED)                                                                 \
                     asm volatile("// GINT_DISPATCH %0 site %1 depth %2;" ::"r"(opc),                     \
@@ -865,6 +981,9 @@ __device__ __forceinline__ void interpret(const uint2 *code, uint32_t n_entries,
     GINT_CASE_SP(num, 5) GINT_CASE_SP(num, 6) GINT_CASE_SP(num, 7) GINT_CASE_SP(num, 8)
             GINT_OPCODE_LIST(GINT_X_CASES)
             GINT_INTERNAL_OPCODE_LIST(GINT_X_CASES)
+#define GINT_X_FCASES(num, len, ...) GINT_X_CASES(fused, num, 0, 0)
+            GINT_FUSED_LIST(GINT_X_FCASES)
+#undef GINT_X_FCASES
 #undef GINT_X_CASES
 #undef GINT_CASE_SP
         default:
@@ -932,6 +1051,7 @@ __device__ __forceinline__ void geval_direct_body(const LaunchArgs &a)
     extern __shared__ __align__(16) unsigned char smem[];
     pool_declare<P, K, hidden_slots(P)>();
     state_declare<true>();
+    asm volatile("mov.b64 %%gzero, %0;" ::"l"((u64)a.zero));
     uint2 *code_s = reinterpret_cast<uint2 *>(smem);
     gint_tensor_info *ti_s = reinterpret_cast<gint_tensor_info *>(smem + a.code_smem_bytes);
     TileInfo *tiles_s = reinterpret_cast<TileInfo *>(smem + a.code_smem_bytes + kTensorInfoSmemBytes);
@@ -972,6 +1092,7 @@ __device__ __forceinline__ void geval_indirect_body(const IndirectArgs &a)
     extern __shared__ __align__(16) unsigned char smem[];
     pool_declare<P, 1, hidden_slots(P)>();
     state_declare<true>();
+    asm volatile("mov.b64 %%gzero, %0;" ::"l"((u64)a.reserved));
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     unsigned char *mine = smem + (size_t)warp * (sizeof(TileInfo) + kTensorInfoSmemBytes + a.code_smem_bytes);
     gint_tensor_info *ti_s = reinterpret_cast<gint_tensor_info *>(mine + sizeof(TileInfo));

@@ -122,19 +122,18 @@
 
 /*
  * Internal opcodes. They never appear in a gint bytecode stream; the host pre-decoder (gint_capi.cu) introduces them when
- * it turns tile loads into "issue early, take later" pairs (see interpret / exec_tile in gint_interp.cuh):
- *   PfTake<h>            push the four values waiting in hidden slot h
- *   PfIssue1D<h>/2DW<h>  start the tile load described by the operand into hidden slot h (no stack effect)
- *   PfTakeIssue..<h>     PfTake<h>, then start the load described by the operand into the slot just emptied
+ * it turns tile loads into "issue early, take later" pairs over a ring of staging slots in shared memory (see
+ * exec_all / tile_issue in gint_interp.cuh):
+ *   PfTake               push the four values waiting in the ring's current slot, advance the ring
+ *   PfIssue1D / 2DW      start the tile load described by the operand into the current slot, advance (program prologue)
+ *   PfTakeIssue1D / 2DW  PfTake, then start the load described by the operand into the slot just emptied
+ *   PfSkip               advance the ring without touching it (pads a prologue shorter than the ring)
  */
-#define GINT_MAX_HIDDEN 4
 #define GINT_INTERNAL_OPCODE_LIST(X) \
-    X(PfTake0, 106, 0, 1) X(PfTake1, 107, 0, 1) X(PfTake2, 108, 0, 1) X(PfTake3, 109, 0, 1) \
-    X(PfIssue1D0, 110, 0, 0) X(PfIssue1D1, 111, 0, 0) X(PfIssue1D2, 112, 0, 0) X(PfIssue1D3, 113, 0, 0) \
-    X(PfIssue2DW0, 114, 0, 0) X(PfIssue2DW1, 115, 0, 0) X(PfIssue2DW2, 116, 0, 0) X(PfIssue2DW3, 117, 0, 0) \
-    X(PfTakeIssue1D0, 118, 0, 1) X(PfTakeIssue1D1, 119, 0, 1) X(PfTakeIssue1D2, 120, 0, 1) X(PfTakeIssue1D3, 121, 0, 1) \
-    X(PfTakeIssue2DW0, 122, 0, 1) X(PfTakeIssue2DW1, 123, 0, 1) X(PfTakeIssue2DW2, 124, 0, 1) X(PfTakeIssue2DW3, 125, 0, 1)
-#define GINT_N_DISPATCH 126   /* opcodes the kernels dispatch on: the 106 of the format + 20 internal ones */
+    X(PfTake, 106, 0, 1) X(PfIssue1D, 107, 0, 0) X(PfIssue2DW, 108, 0, 0) X(PfTakeIssue1D, 109, 0, 1) X(PfTakeIssue2DW, 110, 0, 1) \
+    X(PfSkip, 111, 0, 0)
+#define GINT_N_DISPATCH 141   /* opcodes the kernels dispatch on: the 106 of the format, the 6 above and the fused
+                                 handlers of gint_fused.h */
 
 enum gint_opcode {
 #define GINT_X_ENUM(name, num, md, net) OP_##name = num,

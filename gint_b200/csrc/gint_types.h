@@ -55,6 +55,8 @@ struct LaunchArgs {
     uint32_t end;             // one past the last logical program
     uint32_t code_smem_bytes; // shared-memory bytes reserved for the program
     uint32_t prefetch_mask;   // bit t set: prefetch tensor t's footprint into L2 when a tile's descriptors are decoded
+    uint32_t zero;            // always 0; a zero the assembler cannot see (fma_barrier in gint_interp.cuh)
+    uint32_t reserved;
     Footprint fp[GINT_MAX_TENSORS];
     gint_tensor_info ti;      // descriptor block, base pointers patched per call: travels as a kernel parameter
 };
@@ -72,7 +74,7 @@ struct IndirectArgs {
     uint32_t n_tensors;       // maximum over the batch (executor_impl.py:192)
     uint32_t grid_dim;
     uint32_t code_smem_bytes; // shared-memory bytes reserved per warp for its program
-    uint32_t reserved;
+    uint32_t reserved;        // always 0; doubles as the zero the assembler cannot see (fma_barrier in gint_interp.cuh)
 };
 
 }  // namespace gint

@@ -67,6 +67,8 @@ SIGNATURES = {
     "gint_sizeof_tensor_info": (c_int, []),
     "gint_analyze": (c_int, [POINTER(c_int32), c_int, POINTER(BytecodeStatsC)]),
     "gint_predecode": (c_int, [POINTER(c_int32), c_int, POINTER(c_uint32), c_int]),
+    "gint_debug_transform": (c_int, [POINTER(c_int32), c_int, POINTER(HTensorInfo), c_int, c_int, c_int, POINTER(c_int32), POINTER(c_uint32), c_int]),
+    "gint_debug_fused_table": (c_int, [POINTER(c_int32), c_int]),
     "gint_create": (c_int, [c_int, POINTER(c_void_p)]),
     "gint_destroy": (None, [c_void_p]),
     "gint_last_error": (c_char_p, [c_void_p]),

@@ -100,6 +100,15 @@ int gint_analyze(const int32_t *code, int n_words, gint_bytecode_stats *out);
  * instruction i (stack depth * number of opcodes + opcode). Returns the instruction count incl. Halt, or < 0. */
 int gint_predecode(const int32_t *code, int n_words, uint32_t *out_keys, int max_keys);
 
+/* The instruction list the kernels actually run for a program, after the optional early-issue and fusion passes (for
+ * tests; no GPU needed): out_ops[i] is a format opcode, an internal opcode (>= 106) or -1 for an instruction absorbed into
+ * the fused handler before it. Returns the number of instructions (including the Halt) or < 0. */
+int gint_debug_transform(const int32_t *code, int n_words, const gint_tensor_info *ti, int n_tensors, int early_issue, int fuse,
+                         int32_t *out_ops, uint32_t *out_operands, int max_insns);
+
+/* The fused-handler table: rows of 7 ints {opcode number, length, member opcodes (padded with -1)}. Returns the row count. */
+int gint_debug_fused_table(int32_t *out, int max_entries);
+
 /* ---- context ------------------------------------------------------------------------------------ */
 
 /* Create the executor state for one device, using that device's primary context (the one PyTorch uses).
@@ -171,7 +180,8 @@ int gint_execute_indirect_static(gint_ctx *ctx, const uint64_t *handles, int n_p
 /* ---- tuning knobs (benchmarks / tests) ---------------------------------------------------------- */
 
 /* Knobs for later launches: "tiles_per_warp" (0 = automatic, else upper bound 1/2/4), "early_issue" (1 = start tile
- * loads ahead of their use when safe, default; 0 = run programs exactly as written), "prefetch" (L2 footprint prefetch,
+ * loads ahead of their use when safe, default; 0 = keep loads where they are), "fuse" (1 = replace known instruction
+ * sequences by fused handlers, default; applies to programs created afterwards), "prefetch" (L2 footprint prefetch,
  * default 0), "max_blocks" (cap on the persistent grid, 0 = none). */
 int gint_set_option(gint_ctx *ctx, const char *name, int value);
 

@@ -360,6 +360,19 @@ def special_math(x, o_sqrt, o_exp, o_log, o_trig, o_misc, REGW, WARP):
     halt()
 
 
+@bytecode
+def fused_idioms(a, b, c, o0, o1, o2, REGW, WARP):
+    """Instruction sequences that the pre-decoder replaces by fused handlers, in contexts where a contracted
+    multiply-add would show (the product's other factor comes from a permute, a register, an immediate)."""
+    N, = a.shape
+    ab, bb, cb, b0, b1, b2 = [make_block_1d(t, N, 1, cdiv(N, 128), 128) for t in (a, b, c, o0, o1, o2)]
+    fldg_1d(0, cb); fldg_1d(0, ab); fldg_1d(0, bb); fperm_w(1, 2, 1, 2); fmul(); fadd(); fstg_1d(0, b0)      # perm; [mul, add]
+    fldg_1d(0, cb); fstore_reg(1); fldg_1d(0, ab); fload_reg(1); fmul(); fldg_1d(0, bb); fsub(); fstg_1d(0, b1)  # mul; [load, sub]
+    fldg_1d(0, ab); dup(); fneg(); fexp(); faddimm(1.0); frdiv()                                              # SiLU idiom
+    fldg_1d(0, bb); fmulimm(0.3); faddimm(-1.25); fmul(); fldg_1d(0, cb); fadd(); fstg_1d(0, b2)              # mulimm; addimm; [mul] [load, add, store]
+    halt()
+
+
 # ------------------------------------------------------------------------------------------------ case list
 
 def _z(*shape, dtype=torch.float32):
@@ -450,6 +463,11 @@ def build_cases() -> list[Case]:
         def mkw(g, n=n):
             return [torch.randn(n, generator=g)] + [_z(n) for _ in range(3)]
         cases.append(Case(f"width_ops_n{n}", width_ops, mkw, cdiv(n, 128), [1, 2, 3]))
+
+    for n in [1, 128, 1000]:
+        def mkf(g, n=n):
+            return [torch.randn(n, generator=g) for _ in range(3)] + [_z(n) for _ in range(3)]
+        cases.append(Case(f"fused_idioms_n{n}", fused_idioms, mkf, cdiv(n, 128), [3, 4, 5], exact=False, rtol=2e-6, atol=2e-6))
 
     for r, c in [(1, 1), (7, 33), (64, 100)]:
         def mk(g, r=r, c=c):

@@ -60,6 +60,22 @@ def test_case_matches_oracle(case, k):
             torch.testing.assert_close(got.float(), ref.reshape(got.shape).float(), rtol=max(case.rtol, 1.3e-6), atol=max(case.atol, 1e-5))
 
 
+@pytest.mark.parametrize("k", KS)
+def test_fused_handlers_keep_separate_roundings(k):
+    """mul followed by add inside one fused handler must stay two roundings (the bytecode has an FMA opcode for the other
+    meaning): outputs 0 and 1 of fused_idioms contain no transcendental and must equal the oracle bit for bit."""
+    case = next(c for c in CASES if c.name == "fused_idioms_n1000")
+    host, dev = _run_both(case, k)
+    assert bits_equal(dev[3], host[3]), mismatch_report(dev[3], host[3])
+    assert bits_equal(dev[4], host[4]), mismatch_report(dev[4], host[4])
+    a, b, c = host[0], host[1], host[2]
+    n = a.numel()
+    pad = torch.zeros(((n + 127) // 128) * 128)
+    pad[:n] = b
+    bt = pad.view(-1, 4, 32)[:, [1, 2, 1, 2], :].reshape(-1)[:n]
+    assert torch.equal(host[3], (a * bt) + c)
+
+
 def test_inputs_are_left_untouched():
     case = next(c for c in CASES if c.name == "vector_add_s12345")
     host, dev = _run_both(case, 0)

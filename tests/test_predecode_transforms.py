@@ -1,0 +1,150 @@
+"""The host pre-decoder's program transformations (early-issued loads, fused handlers) are checked on the CPU by undoing
+them: expanding every fused handler into its members and replaying the ring of early-issued loads must give back the
+original instruction list (with an immediately repeated load folded into Dup), for every recorded program and for random
+programs."""
+import ctypes
+
+import numpy as np
+import pytest
+
+from fuzz import FuzzProgram
+from gint_b200 import opcodes as O
+from gint_b200.host import capi
+from gint_b200.host.utils import fill_tensor_info
+from gint_b200.programs import load_records, recorded
+
+PF_TAKE, PF_ISSUE_1D, PF_ISSUE_2DW, PF_TAKE_ISSUE_1D, PF_TAKE_ISSUE_2DW, PF_SKIP = range(106, 112)
+
+
+def fused_table():
+    lib = capi.load_library()
+    buf = (ctypes.c_int32 * (64 * 7))()
+    n = lib.gint_debug_fused_table(buf, 64)
+    assert n > 0
+    return {buf[7 * k]: [buf[7 * k + 2 + j] for j in range(buf[7 * k + 1])] for k in range(n)}
+
+
+def transform(bytecode, infos, early, fuse):
+    lib = capi.load_library()
+    code = np.ascontiguousarray(np.asarray(bytecode, dtype=np.int32).reshape(-1))
+    ti = capi.HTensorInfo()
+    fill_tensor_info(ti, infos)
+    n_max = code.size // 2 + 16
+    ops = (ctypes.c_int32 * n_max)()
+    operands = (ctypes.c_uint32 * n_max)()
+    n = lib.gint_debug_transform(code.ctypes.data_as(ctypes.POINTER(ctypes.c_int32)), code.size, ctypes.byref(ti), len(infos),
+                                 int(early), int(fuse), ops, operands, n_max)
+    assert n > 0, n
+    return list(zip(ops[:n], operands[:n]))
+
+
+def normalised(bytecode):
+    """What the kernels run with both passes off, plus the Dup fold the early-issue pass applies."""
+    out = []
+    for op, operand in np.asarray(bytecode, dtype=np.int64).reshape(-1, 2):
+        op, operand = int(op), int(operand) & 0xFFFFFFFF
+        if op == O.DupBroadcastW:
+            s = operand - (1 << 32) if operand >= 1 << 31 else operand
+            operand = min(max(s, 0), 3)
+        elif op in (O.FPermW, O.FShuf2):
+            operand = sum(min((operand >> (8 * w)) & 0xFF, 3) << (8 * w) for w in range(4))
+        out.append((op, operand))
+        if op == O.Halt:
+            break
+    return out
+
+
+def fold_repeated_loads(prog):
+    loads = {O.LoadGlobal1DF32, O.LoadGlobal1DF16, O.LoadGlobal1DBF16, O.LoadGlobal1DU8, O.LoadGlobal2DTF32, O.LoadGlobal2DTF16,
+             O.LoadGlobal2DTBF16, O.LoadGlobal2DTU8, O.LoadGlobal2DWF32, O.LoadGlobal2DWF16, O.LoadGlobal2DWBF16, O.LoadGlobal2DWU8}
+    out = []
+    for op, operand in prog:
+        if out and op in loads and out[-1] == (op, operand):    # compares with the already folded predecessor
+            out.append((O.Dup, 0))
+        else:
+            out.append((op, operand))
+    return out
+
+
+def undo(prog, table):
+    # 1. fused handlers -> members (operands come from the absorbed instructions that follow)
+    flat = []
+    i = 0
+    while i < len(prog):
+        op, operand = prog[i]
+        if op in table:
+            members = table[op]
+            for j, m in enumerate(members):
+                assert j == 0 or prog[i + j][0] == -1
+                flat.append((m, prog[i + j][1]))
+            i += len(members)
+        else:
+            assert op != -1
+            flat.append((op, operand))
+            i += 1
+    # 2. replay the ring of early-issued loads
+    out, ring = [], []
+    for op, operand in flat:
+        if op in (PF_ISSUE_1D, PF_ISSUE_2DW):
+            ring.append((O.LoadGlobal1DF32 if op == PF_ISSUE_1D else O.LoadGlobal2DWF32, operand))
+        elif op == PF_SKIP:
+            pass
+        elif op == PF_TAKE:
+            out.append(ring.pop(0))
+        elif op in (PF_TAKE_ISSUE_1D, PF_TAKE_ISSUE_2DW):
+            out.append(ring.pop(0))
+            ring.append((O.LoadGlobal1DF32 if op == PF_TAKE_ISSUE_1D else O.LoadGlobal2DWF32, operand))
+        else:
+            out.append((op, operand))
+    assert not ring, "loads were issued but never taken"
+    return out
+
+
+def zero_operands(prog):
+    """Operands of instructions that ignore them are not preserved by fused handlers."""
+    uses = set(range(O.LoadImm, O.LoadGlobal1DU8 + 1)) | {O.FApprox, O.FPermW, O.FShuf2} | set(range(O.LoadGlobal1DF32Indirect, O.DupBroadcastW + 1))
+    return [(op, operand if op in uses else 0) for op, operand in prog]
+
+
+@pytest.mark.parametrize("early,fuse", [(0, 0), (1, 0), (0, 1), (1, 1)])
+def test_transforms_are_invertible_on_recorded_programs(early, fuse):
+    table = fused_table()
+    for name, rec in load_records().items():
+        if name == "execute_everything":
+            continue
+        prog = recorded(name)
+        got = transform(prog.bytecode, prog.tensor_infos, early, fuse)
+        want = normalised(prog.bytecode)
+        if early:
+            want = fold_repeated_loads(want)
+        assert zero_operands(undo(got, table)) == zero_operands(want), name
+
+
+@pytest.mark.parametrize("family", ["float", "int"])
+def test_transforms_are_invertible_on_random_programs(family):
+    table = fused_table()
+    for seed in range(40):
+        depth, regs = [(3, 1), (4, 0), (6, 1), (7, 4), (8, 4), (4, 8), (5, 7), (2, 2)][seed % 8]
+        prog = FuzzProgram(seed, family, depth, regs, length=80 + 5 * seed, rows=33, cols=36)
+        pd = prog.get_program()
+        got = transform(pd.program, pd.input_infos, 1, 1)
+        want = fold_repeated_loads(normalised(pd.program))
+        assert zero_operands(undo(got, table)) == zero_operands(want), seed
+
+
+def test_named_programs_get_the_expected_shape():
+    """The conductor's RMSNorm lowering: 363 instructions become about a hundred dispatches."""
+    table = fused_table()
+    prog = recorded("rmsnorm_r16384_n4096")
+    plain = transform(prog.bytecode, prog.tensor_infos, 0, 0)
+    both = transform(prog.bytecode, prog.tensor_infos, 1, 1)
+    dispatches = sum(1 for op, _ in both if op != -1)
+    assert len(plain) == 363
+    assert dispatches < 130
+    assert sum(1 for op, _ in both if op in (PF_TAKE_ISSUE_1D, PF_TAKE) or (op in table and any(m in (PF_TAKE_ISSUE_1D, PF_TAKE) for m in table[op]))) == 96
+    # a store between two loads of the same tensor keeps the second load where it is
+    from gint_b200.host import frontend as fe
+    bc = [[fe.LoadGlobal1DF32, 0], [fe.StoreGlobal1DF32, 16 * 128 + 0], [fe.LoadGlobal1DF32, 16 * 128 + 0], [fe.StoreGlobal1DF32, 1], [0, 0]]
+    infos = [fe.ProgramTensorInfo(4, [], [], [256, 1], [1, 0], [1, 1], [0, 0]) for _ in range(2)]
+    got = transform(np.array(bc, dtype=np.int32), infos, 1, 0)
+    assert [op for op, _ in got].count(fe.LoadGlobal1DF32) == 1      # the second load was not moved across the store
