@@ -273,12 +273,15 @@ def main():
     ap.add_argument("--workload", default="rmsnorm", choices=["add", "rmsnorm", "bmm4x4", "inv4x4", "graph"])
     ap.add_argument("--programs", default="all", choices=["all", "none"], help="also time the other named programs")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--leading", type=int, default=0, help="override the leading dimension (a recorded size; small profiler captures)")
     opts = ap.parse_args()
     warmup = max(opts.warmup, 3)
     peak, peak_kind = measured_peak()
     metric = "achieved HBM GB/s per bytecode program (algorithmic bytes / device time)"
     name = opts.workload
     from gint_b200.workloads import FULL_SIZES
+    if opts.leading:
+        FULL_SIZES[name] = (opts.leading, FULL_SIZES[name][1])
     leading, inner = FULL_SIZES[name]
     config = {"workload": {"add": "configs[0] a+b fp32 [1048576]", "rmsnorm": "configs[1] RMSNorm x fp32 [16384,4096], conductor-lowered bytecode (363 insns)",
                            "bmm4x4": "configs[2] batched 4x4 matmul [4194304,4,4]", "inv4x4": "configs[3] batched 4x4 inverse [4194304,4,4]",

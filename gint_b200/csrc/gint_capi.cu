@@ -133,7 +133,7 @@ int net_effect(int op)
         for (int j = 0; j < f.len; j++) net += net_effect(f.ops[j]);
         return net;
     }
-    return (op == OP_PfTake || op == OP_PfTakeIssue1D || op == OP_PfTakeIssue2DW) ? 1 : 0;
+    return (op == OP_PfTake || op == OP_PfTakeIssue1D) ? 1 : 0;
 }
 
 /* Replace known instruction sequences by fused handlers (gint_fused.h): greedy, longest match first. The absorbed
@@ -199,8 +199,9 @@ bool writes_tensor(int op)
  * Early-issue transformation. The interpreter consumes every loaded value in the next instruction or two, so as written
  * a program keeps one tile load per logical program in flight and waits out the full memory latency each time. The
  * bytecode is straight-line, though: which tiles it will load, and in which order, is known here. Eligible loads
- * (f32, 1-D or 2DW layout) are numbered 0, 1, 2, ... in program order; load n is STARTED where load n-D is consumed (the
- * first D in a prologue) into hidden register slot n mod D, and at its original place only a register move remains
+ * (f32, 1-D layout) are numbered 0, 1, 2, ... in program order; load n is STARTED where load n-D is consumed (the
+ * first D in a prologue) into staging slot n mod D of the warp's ring in shared memory, and at its original place only a
+ * read of that slot remains
  * (PfTake / PfTakeIssue, gint_opcodes.h). A load keeps its place when starting it early could change what it reads:
  *   - a store or scatter to the SAME tensor slot, or an AdvanceBlock2D / AdvanceBase on it, lies in between (checked here);
  *   - a store to ANOTHER slot lies in between and the two tensors overlap in memory: that depends on the base pointers
@@ -223,7 +224,7 @@ void early_issue_transform(const std::vector<Insn> &in, int D, EarlyIssue *out)
                              (op >= OP_LoadGlobal2DTF32 && op <= OP_LoadGlobal2DWU8 && !writes_tensor(op));
         if (is_load && prog[i - 1].op == op && prog[i - 1].operand == prog[i].operand) prog[i] = Insn{OP_Dup, 0u};
     }
-    struct Member { size_t site; int layout; uint32_t operand; };
+    struct Member { size_t site; uint32_t operand; };
     std::vector<Member> ring;
     for (size_t i = 0; i < prog.size(); i++) {
         const int op = prog[i].op;
@@ -242,14 +243,14 @@ void early_issue_transform(const std::vector<Insn> &in, int D, EarlyIssue *out)
         if (hazard) continue;
         for (size_t j = from; j < i; j++)
             if (writes_tensor(prog[j].op)) out->alias_slots[slot] |= (uint8_t)(1u << (prog[j].operand & 7u));
-        ring.push_back(Member{i, op == OP_LoadGlobal1DF32 ? 1 : 2, prog[i].operand});
+        ring.push_back(Member{i, prog[i].operand});
     }
     out->n_early = (int)ring.size();
     out->prog.clear();
     if (ring.empty()) { out->prog = prog; return; }
     const size_t R = ring.size();
     for (size_t n = 0; n < (size_t)D; n++) {   // prologue: fill the ring (padded so that it wraps back to slot 0)
-        if (n < R) out->prog.push_back(Insn{ring[n].layout == 1 ? OP_PfIssue1D : OP_PfIssue2DW, ring[n].operand});
+        if (n < R) out->prog.push_back(Insn{OP_PfIssue1D, ring[n].operand});
         else out->prog.push_back(Insn{OP_PfSkip, 0u});
     }
     size_t next = 0;
@@ -257,7 +258,7 @@ void early_issue_transform(const std::vector<Insn> &in, int D, EarlyIssue *out)
         if (next < R && ring[next].site == i) {
             if (next + (size_t)D < R) {
                 const Member &f = ring[next + (size_t)D];
-                out->prog.push_back(Insn{f.layout == 1 ? OP_PfTakeIssue1D : OP_PfTakeIssue2DW, f.operand});
+                out->prog.push_back(Insn{OP_PfTakeIssue1D, f.operand});
             } else {
                 out->prog.push_back(Insn{OP_PfTake, 0u});
             }

@@ -11,7 +11,7 @@
  * The sequences below are the idioms of the gint frontend and conductor lowerings: the chunk bodies of row reductions and
  * of scale-and-store loops, SiLU, the width-lane combine after a warp reduction, and the inner step of the 4x4 matmul.
  * Loads appear in three flavours (as written, early-issued, and early-issued without a successor), because the
- * early-issue transformation (gint_capi.cu) rewrites them before fusion runs.
+ * early-issue transformation (gint_capi.cu) rewrites 1-D loads before fusion runs.
  *
  * X(number, length, op0, op1, ...). Numbers continue the internal opcode space of gint_opcodes.h.
  */
@@ -20,7 +20,7 @@
 
 #include "gint_opcodes.h"
 
-#define GINT_FUSED_FIRST 112
+#define GINT_FUSED_FIRST 110
 
 /* one entry per load flavour L for the 1-D idioms */
 #define GINT_FUSED_1D(X, base, L)                                                        \
@@ -36,25 +36,23 @@
     X(base + 0, 4, OP_DupBroadcastW, L, OP_FMul, OP_Swap)   /* bmm inner step         */
 
 #define GINT_FUSED_LIST(X)                                                               \
-    GINT_FUSED_1D(X, 112, OP_LoadGlobal1DF32)                                            \
-    GINT_FUSED_1D(X, 119, OP_PfTakeIssue1D)                                              \
-    GINT_FUSED_1D(X, 126, OP_PfTake)                                                     \
-    GINT_FUSED_2DW(X, 133, OP_LoadGlobal2DWF32)                                          \
-    GINT_FUSED_2DW(X, 134, OP_PfTakeIssue2DW)                                            \
-    GINT_FUSED_2DW(X, 135, OP_PfTake)                                                    \
-    X(136, 5, OP_Dup, OP_FNeg, OP_FExp, OP_FAddImm, OP_FRDiv)            /* SiLU      */ \
-    X(137, 3, OP_Dup, OP_FPermW, OP_FAdd)                                /* width combine */ \
-    X(138, 5, OP_Pop, OP_FAdd, OP_FAdd, OP_FAdd, OP_StoreGlobal2DWF32)   /* bmm row end */ \
-    X(139, 2, OP_FMul, OP_FAdd)                                                          \
-    X(140, 2, OP_FMul, OP_StoreGlobal1DF32)
+    GINT_FUSED_1D(X, 110, OP_LoadGlobal1DF32)                                            \
+    GINT_FUSED_1D(X, 117, OP_PfTakeIssue1D)                                              \
+    GINT_FUSED_1D(X, 124, OP_PfTake)                                                     \
+    GINT_FUSED_2DW(X, 131, OP_LoadGlobal2DWF32)                                          \
+    X(132, 5, OP_Dup, OP_FNeg, OP_FExp, OP_FAddImm, OP_FRDiv)            /* SiLU      */ \
+    X(133, 3, OP_Dup, OP_FPermW, OP_FAdd)                                /* width combine */ \
+    X(134, 5, OP_Pop, OP_FAdd, OP_FAdd, OP_FAdd, OP_StoreGlobal2DWF32)   /* bmm row end */ \
+    X(135, 2, OP_FMul, OP_FAdd)                                                          \
+    X(136, 2, OP_FMul, OP_StoreGlobal1DF32)
 
-#define GINT_N_FUSED 29
-#define GINT_N_DISPATCH_ALL (GINT_FUSED_FIRST + GINT_N_FUSED)   /* 141 */
+#define GINT_N_FUSED 27
+#define GINT_N_DISPATCH_ALL (GINT_FUSED_FIRST + GINT_N_FUSED)   /* 137 */
 #define GINT_MAX_FUSED_LEN 5
 
 /* does the instruction read its operand word? (fused handlers fetch operands only for those that do) */
 #define GINT_OP_USES_OPERAND(op)                                                                                           \
     (((op) >= OP_LoadImm && (op) <= OP_LoadGlobal1DU8) || (op) == OP_FApprox || ((op) >= OP_LoadGlobal1DF32Indirect && (op) <= OP_DupBroadcastW) || \
-     (op) == OP_FPermW || (op) == OP_FShuf2 || (op) == OP_PfIssue1D || (op) == OP_PfIssue2DW || (op) == OP_PfTakeIssue1D || (op) == OP_PfTakeIssue2DW)
+     (op) == OP_FPermW || (op) == OP_FShuf2 || (op) == OP_PfIssue1D || (op) == OP_PfTakeIssue1D)
 
 #endif /* GINT_FUSED_H */

@@ -461,7 +461,7 @@ template <int K, int A, int B, int KI> __device__ __forceinline__ void slot_swap
 struct Ctx {
     TileInfo *tiles;   // this warp's K tile descriptors (shared memory)
     int lane;
-    uint32_t hidden;   // shared-memory address of this lane's 16 bytes in slot 0, tile 0 of the warp's load staging area
+    uint32_t hidden;   // shared-memory address of slot 0, tile 0 of the warp's load staging area, plus 4 * lane
 };
 
 template <int OP> struct OpInfo;
@@ -558,19 +558,24 @@ GINT_MEMOP(LoadGlobal2DWU8, LAY_2DW, DT_U8, false)
 #undef GINT_MEMOP
 
 /*
- * Start a tile load whose values are not needed yet. Each lane copies the (up to) four elements it will consume with
- * cp.async into its own 16 bytes of a per-warp ring of staging slots in shared memory -- slot h, tile k, lane l at
- * ((h*K + k)*32 + l)*16, the current slot being tracked in the named register %gring -- and commits them as one group; masked elements are zero-filled by the copy itself (source size
- * 0). Nothing here waits for memory. PfTake later waits for exactly this group (cp.async groups complete in order, and at
- * that point D-1 newer groups are in flight) and reads the 16 bytes back with one shared-memory load. Completion is tracked
- * by the copy engine per thread, so a lane only ever reads what it wrote itself and no warp synchronisation is needed.
- * Same addressing and masking rules as tile_rw.
+ * Start a 1-D tile load whose values are not needed yet. The warp copies the tile with cp.async into a slot of its ring of
+ * staging slots in shared memory and commits the copies as one group; nothing here waits for memory. A slot holds the tile
+ * in ELEMENT order (element e of the tile at byte 4e of the slot's 512 bytes; K tiles back to back; the current slot is
+ * tracked in the named register %gring):
+ *   - a full unit-stride tile whose first byte is 16-byte aligned is ONE 16-byte copy per lane (lane l moves elements
+ *     4l..4l+3), i.e. one instruction and four conflict-free shared-memory wavefronts per 512 bytes;
+ *   - anything else is four 4-byte copies per lane (lane l moves elements l, l+32, l+64, l+96: consecutive lanes write
+ *     consecutive words), masked elements being zero-filled by the copy itself (source size 0).
+ * PfTake later waits for exactly this group (cp.async groups complete in order, and at that point D-1 newer groups are in
+ * flight), synchronises the warp -- a lane consumes words that other lanes copied -- and reads its four values, elements
+ * l + 32w, with four conflict-free 4-byte loads. Same addressing and masking rules as tile_rw.
+ * `slot` is the shared-memory address of the slot's tile 0 plus 4 * lane.
  */
 __device__ __forceinline__ void cp_async_f32(uint32_t dst, const void *src, bool ok)
 {
     asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(dst), "l"(src), "r"(ok ? 4 : 0) : "memory");
 }
-template <int LAYOUT, int K, int KI>
+template <int K, int KI>
 __device__ __forceinline__ void tile_issue(const TileInfo *ti, uint32_t operand, const Ctx &cx, uint32_t slot)
 {
     const int arg = operand & 15;
@@ -578,48 +583,35 @@ __device__ __forceinline__ void tile_issue(const TileInfo *ti, uint32_t operand,
     const int lane = cx.lane;
     char *base = reinterpret_cast<char *>(ti->ptr[arg]);
     const int2 s1 = ti->s1[arg];
-    const uint32_t dst = slot + (uint32_t)(KI * 512);   // `slot` already includes this lane's 16-byte offset
-    if constexpr (LAYOUT == LAY_1D) {
-        const int e = lane + off;
-        if (s1.y == 1 && off + 128 <= s1.x) {  // full unit-stride tile: four unmasked copies at fixed offsets
-            const char *p = base + (long long)e * 4;
-            asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n\t"
-                         "cp.async.ca.shared.global [%0+4], [%1+128], 4;\n\t"
-                         "cp.async.ca.shared.global [%0+8], [%1+256], 4;\n\t"
-                         "cp.async.ca.shared.global [%0+12], [%1+384], 4;" ::"r"(dst), "l"(p) : "memory");
-            return;
-        }
-        const char *p = base + (long long)(e * s1.y) * 4;
-        const long long pstep = (long long)(s1.y * 32) * 4;
-#pragma unroll
-        for (int w = 0; w < 4; w++) {
-            const bool ok = e + 32 * w < s1.x;
-            cp_async_f32(dst + 4 * w, ok ? p + w * pstep : base, ok);
-        }
-    } else {  // LAY_2DW
-        const int2 s2 = ti->s2[arg];
-        const int adv = ti->adv[arg];
-        const int t = lane + adv;
-        const int j0 = off;
-        const bool tok = t < s1.x;
-        if ((ti->flags[arg] & kVecRows) && (j0 & 3) == 0 && j0 + 4 <= s2.x) {
-            const char *p = base + (long long)(t * s1.y + j0) * 4;
-            asm volatile("cp.async.ca.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(tok ? p : base), "r"(tok ? 16 : 0) : "memory");
+    const uint32_t dst = slot + (uint32_t)(KI * 512);
+    const int e = lane + off;
+    if (s1.y == 1 && off + 128 <= s1.x) {  // full unit-stride tile
+        const char *p0 = base + (long long)off * 4;
+        if ((reinterpret_cast<u64>(p0) & 15) == 0) {
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + (uint32_t)(lane * 12)), "l"(p0 + lane * 16) : "memory");
         } else {
-            const char *p = base + (long long)(t * s1.y + j0 * s2.y) * 4;
-            const long long pstep = (long long)s2.y * 4;
-#pragma unroll
-            for (int w = 0; w < 4; w++) {
-                const bool ok = tok && (j0 + w < s2.x);
-                cp_async_f32(dst + 4 * w, ok ? p + w * pstep : base, ok);
-            }
+            const char *p = p0 + lane * 4;
+            asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n\t"
+                         "cp.async.ca.shared.global [%0+128], [%1+128], 4;\n\t"
+                         "cp.async.ca.shared.global [%0+256], [%1+256], 4;\n\t"
+                         "cp.async.ca.shared.global [%0+384], [%1+384], 4;" ::"r"(dst), "l"(p) : "memory");
         }
+        return;
+    }
+    const char *p = base + (long long)(e * s1.y) * 4;
+    const long long pstep = (long long)(s1.y * 32) * 4;
+#pragma unroll
+    for (int w = 0; w < 4; w++) {
+        const bool ok = e + 32 * w < s1.x;
+        cp_async_f32(dst + 128 * w, ok ? p + w * pstep : base, ok);
     }
 }
 template <int K, int SLOT, int KI> __device__ __forceinline__ void take_hidden(uint32_t slot)
 {
     const uint32_t src = slot + (uint32_t)(KI * 512);
-    asm volatile("ld.shared.v2.b64 {%%gs%0, %%gs%1}, [%2];" ::"n"(gs<K>(SLOT, KI, 0)), "n"(gs<K>(SLOT, KI, 1)), "r"(src) : "memory");
+    asm volatile("{\n\t.reg .b32 t<4>;\n\t"
+                 "ld.shared.b32 t0, [%2];\n\tld.shared.b32 t1, [%2+128];\n\tld.shared.b32 t2, [%2+256];\n\tld.shared.b32 t3, [%2+384];\n\t"
+                 "mov.b64 %%gs%0, {t0, t1};\n\tmov.b64 %%gs%1, {t2, t3};\n\t}" ::"n"(gs<K>(SLOT, KI, 0)), "n"(gs<K>(SLOT, KI, 1)), "r"(src) : "memory");
 }
 
 template <int OP, int SP, int P, int K, int KI>
@@ -795,15 +787,17 @@ __device__ __forceinline__ void exec_all(const uint32_t operand, const Ctx &cx, 
          * after it are in flight, so "all but the newest D-1 groups have landed" is exactly "load n has landed"; a plain
          * PfTake belongs to the tail of the program, where fewer are in flight, and simply waits for everything. */
         constexpr int D = hidden_slots(P);
-        constexpr bool take = OP == OP_PfTake || OP == OP_PfTakeIssue1D || OP == OP_PfTakeIssue2DW;
+        constexpr bool take = OP == OP_PfTake || OP == OP_PfTakeIssue1D;
         uint32_t ring;
         asm volatile("mov.b32 %0, %%gring;" : "=r"(ring));
         const uint32_t slot = cx.hidden + ring;
         if constexpr (OP == OP_PfTake) asm volatile("cp.async.wait_group 0;" ::: "memory");
         else if constexpr (take) asm volatile("cp.async.wait_group %0;" ::"n"(D - 1) : "memory");
-        if constexpr (take) (take_hidden<K, SP, KI>(slot), ...);
-        if constexpr (OP == OP_PfIssue1D || OP == OP_PfTakeIssue1D) (tile_issue<LAY_1D, K, KI>(cx.tiles + KI, operand, cx, slot), ...);
-        if constexpr (OP == OP_PfIssue2DW || OP == OP_PfTakeIssue2DW) (tile_issue<LAY_2DW, K, KI>(cx.tiles + KI, operand, cx, slot), ...);
+        if constexpr (take) {
+            __syncwarp();   // the group has landed for every lane: make the other lanes' copies visible to this one
+            (take_hidden<K, SP, KI>(slot), ...);
+        }
+        if constexpr (OP == OP_PfIssue1D || OP == OP_PfTakeIssue1D) (tile_issue<K, KI>(cx.tiles + KI, operand, cx, slot), ...);
         if constexpr (OP != OP_PfTake && OP != OP_PfSkip) asm volatile("cp.async.commit_group;" ::: "memory");
         asm volatile("add.u32 %%gring, %%gring, %0;\n\tand.b32 %%gring, %%gring, %1;" ::"n"(K * 512), "n"(D * K * 512 - 1));
     } else {
@@ -1070,7 +1064,7 @@ __device__ __forceinline__ void geval_direct_body(const LaunchArgs &a)
     cx.lane = lane;
     {   // load staging area: after the tile descriptors, hidden_slots(P) * K * 512 bytes per warp
         unsigned char *stage = reinterpret_cast<unsigned char *>(tiles_s + kWarpsPerBlock * K) +
-                               (size_t)warp * (hidden_slots(P) * K * 512) + lane * 16;
+                               (size_t)warp * (hidden_slots(P) * K * 512) + lane * 4;
         cx.hidden = (uint32_t)__cvta_generic_to_shared(stage);
     }
 

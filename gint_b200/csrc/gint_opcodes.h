@@ -125,14 +125,13 @@
  * it turns tile loads into "issue early, take later" pairs over a ring of staging slots in shared memory (see
  * exec_all / tile_issue in gint_interp.cuh):
  *   PfTake               push the four values waiting in the ring's current slot, advance the ring
- *   PfIssue1D / 2DW      start the tile load described by the operand into the current slot, advance (program prologue)
- *   PfTakeIssue1D / 2DW  PfTake, then start the load described by the operand into the slot just emptied
+ *   PfIssue1D            start the 1-D tile load described by the operand into the current slot, advance (program prologue)
+ *   PfTakeIssue1D        PfTake, then start the load described by the operand into the slot just emptied
  *   PfSkip               advance the ring without touching it (pads a prologue shorter than the ring)
  */
 #define GINT_INTERNAL_OPCODE_LIST(X) \
-    X(PfTake, 106, 0, 1) X(PfIssue1D, 107, 0, 0) X(PfIssue2DW, 108, 0, 0) X(PfTakeIssue1D, 109, 0, 1) X(PfTakeIssue2DW, 110, 0, 1) \
-    X(PfSkip, 111, 0, 0)
-#define GINT_N_DISPATCH 141   /* opcodes the kernels dispatch on: the 106 of the format, the 6 above and the fused
+    X(PfTake, 106, 0, 1) X(PfIssue1D, 107, 0, 0) X(PfTakeIssue1D, 108, 0, 1) X(PfSkip, 109, 0, 0)
+#define GINT_N_DISPATCH 137   /* opcodes the kernels dispatch on: the 106 of the format, the 4 above and the fused
                                  handlers of gint_fused.h */
 
 enum gint_opcode {

@@ -13,7 +13,7 @@ from gint_b200.host import capi
 from gint_b200.host.utils import fill_tensor_info
 from gint_b200.programs import load_records, recorded
 
-PF_TAKE, PF_ISSUE_1D, PF_ISSUE_2DW, PF_TAKE_ISSUE_1D, PF_TAKE_ISSUE_2DW, PF_SKIP = range(106, 112)
+PF_TAKE, PF_ISSUE_1D, PF_TAKE_ISSUE_1D, PF_SKIP = range(106, 110)
 
 
 def fused_table():
@@ -85,15 +85,15 @@ def undo(prog, table):
     # 2. replay the ring of early-issued loads
     out, ring = [], []
     for op, operand in flat:
-        if op in (PF_ISSUE_1D, PF_ISSUE_2DW):
-            ring.append((O.LoadGlobal1DF32 if op == PF_ISSUE_1D else O.LoadGlobal2DWF32, operand))
+        if op == PF_ISSUE_1D:
+            ring.append((O.LoadGlobal1DF32, operand))
         elif op == PF_SKIP:
             pass
         elif op == PF_TAKE:
             out.append(ring.pop(0))
-        elif op in (PF_TAKE_ISSUE_1D, PF_TAKE_ISSUE_2DW):
+        elif op == PF_TAKE_ISSUE_1D:
             out.append(ring.pop(0))
-            ring.append((O.LoadGlobal1DF32 if op == PF_TAKE_ISSUE_1D else O.LoadGlobal2DWF32, operand))
+            ring.append((O.LoadGlobal1DF32, operand))
         else:
             out.append((op, operand))
     assert not ring, "loads were issued but never taken"
