@@ -29,7 +29,7 @@ CSRC = os.path.join(PKG_DIR, "csrc")
 KERNELS = os.path.join(CSRC, "kernels")
 OBJ_DIR = os.path.join(CSRC, "build")
 LIB_PATH = os.path.join(PKG_DIR, "libgint_b200.so")
-N_OPS = 137          # GINT_N_DISPATCH: the 106 opcodes of the format + the internal ones
+N_OPS = 134          # GINT_N_DISPATCH: the 106 opcodes of the format + the internal ones
 N_KEYS = 9 * N_OPS   # (GINT_MAX_STACK + 1) * GINT_N_DISPATCH
 
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
@@ -44,8 +44,14 @@ def _nvcc() -> str:
     return exe
 
 
+STEP_TIMEOUT_S = 900    # a compiler step that runs this long is stuck (ptxas on an unlucky control-flow graph): fail, do not hang
+
+
 def _run(cmd: list[str], what: str) -> str:
-    r = subprocess.run(cmd, capture_output=True, text=True)
+    try:
+        r = subprocess.run(cmd, capture_output=True, text=True, timeout=STEP_TIMEOUT_S)
+    except subprocess.TimeoutExpired:
+        raise RuntimeError(f"{what} did not finish within {STEP_TIMEOUT_S} s:\n{' '.join(cmd)}")
     if r.returncode != 0:
         raise RuntimeError(f"{what} failed:\n{' '.join(cmd)}\n{r.stdout}\n{r.stderr}")
     return r.stderr + r.stdout

@@ -121,11 +121,12 @@ const FusedDef kFused[GINT_N_FUSED] = {
     GINT_FUSED_LIST(GINT_X_FDEF)
 #undef GINT_X_FDEF
 };
-constexpr int OP_CARRIER = -1;   // an instruction absorbed into the fused handler before it: only its operand is used
+constexpr int OP_CARRIER = -1;        // an instruction absorbed into the fused handler before it: only its operand is used
+constexpr int OP_CARRIER_UNUSED = -2; // the same, for a member that reads no operand: it gets no stream entry
 
 int net_effect(int op)
 {
-    if (op == OP_CARRIER) return 0;
+    if (op == OP_CARRIER || op == OP_CARRIER_UNUSED) return 0;
     if (op < GINT_N_OPCODES) return kEffects[op].net;
     if (op >= GINT_FUSED_FIRST) {
         int net = 0;
@@ -133,7 +134,8 @@ int net_effect(int op)
         for (int j = 0; j < f.len; j++) net += net_effect(f.ops[j]);
         return net;
     }
-    return (op == OP_PfTake || op == OP_PfTakeIssue1D) ? 1 : 0;
+    if (op == OP_StoreGlobal1DF32Fast) return -1;
+    return (op == OP_PfTake || op == OP_PfTakeIssue1D || op == OP_PfTakeIssue1DFast || op == OP_LoadGlobal1DF32Fast) ? 1 : 0;
 }
 
 /* Replace known instruction sequences by fused handlers (gint_fused.h): greedy, longest match first. The absorbed
@@ -152,16 +154,22 @@ void fuse_sequences(std::vector<Insn> *prog)
         }
         if (best < 0) { i++; continue; }
         p[i].op = kFused[best].num;
-        for (int j = 1; j < kFused[best].len; j++) p[i + (size_t)j].op = OP_CARRIER;
+        for (int j = 1; j < kFused[best].len; j++)
+            p[i + (size_t)j].op = GINT_OP_USES_OPERAND(kFused[best].ops[j]) ? OP_CARRIER : OP_CARRIER_UNUSED;
         i += (size_t)kFused[best].len;
     }
 }
 
 /* Stream layout, skewed for threaded dispatch: entry 0 = {0, opcode of insn 0}; entry i+1 = {operand of insn i, opcode of
  * insn i+1}; the opcode after the final Halt is Halt again. The stack depth before every instruction is static
- * (straight-line code) and is baked into the handlers, not the stream. */
-void emit_stream(const std::vector<Insn> &prog, std::vector<uint2> *out, std::vector<int> *depth_out = nullptr)
+ * (straight-line code) and is baked into the handlers, not the stream. Members of a fused sequence that read no operand
+ * get no entry. */
+void emit_stream(const std::vector<Insn> &full, std::vector<uint2> *out, std::vector<int> *depth_out = nullptr)
 {
+    std::vector<Insn> prog;
+    prog.reserve(full.size());
+    for (const Insn &in : full)
+        if (in.op != OP_CARRIER_UNUSED) prog.push_back(in);
     const size_t n = prog.size();
     out->clear();
     out->reserve(n + 4);
@@ -192,7 +200,7 @@ bool writes_tensor(int op)
 {
     return op == OP_StoreGlobal1DF32 || op == OP_StoreGlobal1DF16 || op == OP_StoreGlobal1DBF16 || op == OP_StoreGlobal1DF32Indirect ||
            op == OP_StoreGlobal2DTF32 || op == OP_StoreGlobal2DTF16 || op == OP_StoreGlobal2DTBF16 || op == OP_StoreGlobal2DWF32 ||
-           op == OP_StoreGlobal2DWF16 || op == OP_StoreGlobal2DWBF16;
+           op == OP_StoreGlobal2DWF16 || op == OP_StoreGlobal2DWBF16 || op == OP_StoreGlobal1DF32Fast;
 }
 
 /*
@@ -267,6 +275,58 @@ void early_issue_transform(const std::vector<Insn> &in, int D, EarlyIssue *out)
             out->prog.push_back(prog[i]);
         }
     }
+}
+
+/*
+ * Fast accesses. A 1-D f32 access can skip all shape, stride and mask handling when, for every logical program of the
+ * grid, it covers a full unit-stride tile whose first byte is 16-byte aligned. With the descriptors of program creation
+ * this is decidable up to the alignment of the base pointer: the tile's first element is at
+ *   base + (b1*grid_step1*stride1 + b2*grid_step2*stride2 + sum(batch_index*batch_stride) + off) * 4
+ * and its extent along dimension 1 is shape1 - b1*grid_step1 (descriptor decode, gint_interp.cuh: decode_tiles), so it is
+ * enough that every step that can be non-zero is a multiple of 4 elements, that off is, and that off + 128 fits the
+ * smallest extent. Slots that the program moves (AdvanceBase / AdvanceBlock2D) are left alone. The slots that fast
+ * accesses rely on are returned as a mask; a launch whose base pointer for one of them is not 16-byte aligned runs the
+ * plain stream instead.
+ */
+uint32_t apply_fast_accesses(std::vector<Insn> *prog, const gint_tensor_info &ti, int n_tensors)
+{
+    bool ok[GINT_MAX_TENSORS];
+    int64_t min_extent[GINT_MAX_TENSORS];
+    for (int t = 0; t < GINT_MAX_TENSORS; t++) {
+        ok[t] = false;
+        min_extent[t] = 0;
+        if (t >= n_tensors) continue;
+        const int64_t shape1 = ti.block_shape_stride_1[t][0], stride1 = ti.block_shape_stride_1[t][1];
+        const int64_t stride2 = ti.block_shape_stride_2[t][1];
+        const int64_t gd1 = (uint32_t)ti.block_grid_dims[t][0], gd2 = (uint32_t)ti.block_grid_dims[t][1];
+        const int64_t gs1 = ti.block_grid_steps[t][0], gs2 = ti.block_grid_steps[t][1];
+        bool good = ti.elm_size[t] == 4 && stride1 == 1 && gd1 >= 1 && gd2 >= 1 && gs1 >= 0;
+        if (good && gd1 != 1 && (gs1 * stride1) % 4 != 0) good = false;
+        if (good && gd2 != 1 && (gs2 * stride2) % 4 != 0) good = false;
+        for (int j = 0; good && j < 4; j++)
+            if (ti.batch_shape[t][j] != 1 && ti.batch_strides[t][j] % 4 != 0) good = false;
+        ok[t] = good;
+        min_extent[t] = shape1 - (gd1 - 1) * gs1;
+    }
+    for (const Insn &in : *prog)
+        if (in.op == OP_AdvanceBlock2D || in.op == OP_AdvanceBase) ok[in.operand & 7u] = false;
+    uint32_t used = 0;
+    for (Insn &in : *prog) {
+        int fast;
+        switch (in.op) {
+        case OP_LoadGlobal1DF32: fast = OP_LoadGlobal1DF32Fast; break;
+        case OP_StoreGlobal1DF32: fast = OP_StoreGlobal1DF32Fast; break;
+        case OP_PfIssue1D: fast = OP_PfIssue1DFast; break;
+        case OP_PfTakeIssue1D: fast = OP_PfTakeIssue1DFast; break;
+        default: continue;
+        }
+        const int slot = (int)(in.operand & 15u);
+        const int64_t off = (int64_t)(in.operand >> 4);
+        if (slot >= n_tensors || !ok[slot] || (off & 3) != 0 || off + 128 > min_extent[slot]) continue;
+        in.op = fast;
+        used |= 1u << slot;
+    }
+    return used;
 }
 
 /* Conservative byte extent a program can touch from a tensor's base pointer; 0 = unknown (negative strides). */
@@ -347,6 +407,7 @@ struct Program {
     uint32_t early_slots = 0;
     int n_early = 0;
     uint8_t alias_slots[GINT_MAX_TENSORS] = {};
+    uint32_t fast_slots = 0;   // tensor slots whose base pointer must be 16-byte aligned for the early-issue stream
     uint64_t extent[GINT_MAX_TENSORS] = {};
 };
 
@@ -524,6 +585,8 @@ int launch_direct(gint_ctx *ctx, uint64_t handle, const uint64_t *base_ptrs, int
             if (a0 < b1 && b0 < a1) early = false;
         }
     }
+    for (int t = 0; early && t < n_tensors; t++)
+        if (((p->fast_slots >> t) & 1u) && (base_ptrs[t] & 15u) != 0) early = false;   // fast accesses need aligned bases
     Program view = *p;   // geometry depends on the stream length
     if (early) view.n_slots = p->early_slots;
     Geometry g;
@@ -748,6 +811,7 @@ int gint_program_create(gint_ctx *ctx, const int32_t *code, int n_words, const g
                 if ((ei.alias_slots[t] >> b) & 1u) { if (tensor_extent_bytes(p->ti, b) == 0) usable = false; }
         }
         if (usable) {
+            p->fast_slots = apply_fast_accesses(&ei.prog, p->ti, n_tensors);
             if (ctx->opt_fuse) fuse_sequences(&ei.prog);
             emit_stream(ei.prog, &early);
             p->n_early = ei.n_early;
@@ -1001,12 +1065,15 @@ int gint_debug_transform(const int32_t *code, int n_words, const gint_tensor_inf
         EarlyIssue ei;
         early_issue_transform(prog, gint::hidden_slots(st.pool_size), &ei);
         prog = ei.prog;
+        if (ei.n_early > 0 && ti) {
+            gint_tensor_info t0 = *ti;
+            apply_fast_accesses(&prog, t0, n_tensors);
+        }
     }
     if (fuse) fuse_sequences(&prog);
-    (void)ti;
     if ((int)prog.size() > max_insns) return GINT_ERR_INVALID_ARGUMENT;
     for (size_t i = 0; i < prog.size(); i++) {
-        if (out_ops) out_ops[i] = prog[i].op;
+        if (out_ops) out_ops[i] = prog[i].op == OP_CARRIER_UNUSED ? OP_CARRIER : prog[i].op;
         if (out_operands) out_operands[i] = prog[i].operand;
     }
     return (int)prog.size();

@@ -10,8 +10,11 @@
  *
  * The sequences below are the idioms of the gint frontend and conductor lowerings: the chunk bodies of row reductions and
  * of scale-and-store loops, SiLU, the width-lane combine after a warp reduction, and the inner step of the 4x4 matmul.
- * Loads appear in three flavours (as written, early-issued, and early-issued without a successor), because the
- * early-issue transformation (gint_capi.cu) rewrites 1-D loads before fusion runs.
+ * 1-D loads appear in the two flavours the early-issue transformation (gint_capi.cu) produces for provably full, aligned
+ * tiles before fusion runs: taken from the ring while the next one is started, and taken without a successor.
+ *
+ * In the pre-decoded stream a fused instruction occupies one entry, plus one entry for every member after the first
+ * that reads an operand word.
  *
  * X(number, length, op0, op1, ...). Numbers continue the internal opcode space of gint_opcodes.h.
  */
@@ -20,39 +23,35 @@
 
 #include "gint_opcodes.h"
 
-#define GINT_FUSED_FIRST 110
+#define GINT_FUSED_FIRST 114
 
 /* one entry per load flavour L for the 1-D idioms */
 #define GINT_FUSED_1D(X, base, L)                                                        \
     X(base + 0, 4, L, OP_Dup, OP_FMul, OP_FAdd)             /* acc += x*x             */ \
     X(base + 1, 3, L, OP_Dup, OP_FMul)                      /* x*x                    */ \
     X(base + 2, 4, OP_Dup, L, OP_Swap, OP_FMul)             /* s, s*x                 */ \
-    X(base + 3, 3, L, OP_FMul, OP_StoreGlobal1DF32)         /* store(top * w)         */ \
+    X(base + 3, 3, L, OP_FMul, OP_StoreGlobal1DF32Fast)     /* store(top * w)         */ \
     X(base + 4, 2, L, OP_FMul)                                                           \
     X(base + 5, 2, L, OP_FAdd)                                                           \
-    X(base + 6, 3, L, OP_FAdd, OP_StoreGlobal1DF32)
-
-#define GINT_FUSED_2DW(X, base, L)                                                       \
-    X(base + 0, 4, OP_DupBroadcastW, L, OP_FMul, OP_Swap)   /* bmm inner step         */
+    X(base + 6, 3, L, OP_FAdd, OP_StoreGlobal1DF32Fast)
 
 #define GINT_FUSED_LIST(X)                                                               \
-    GINT_FUSED_1D(X, 110, OP_LoadGlobal1DF32)                                            \
-    GINT_FUSED_1D(X, 117, OP_PfTakeIssue1D)                                              \
-    GINT_FUSED_1D(X, 124, OP_PfTake)                                                     \
-    GINT_FUSED_2DW(X, 131, OP_LoadGlobal2DWF32)                                          \
-    X(132, 5, OP_Dup, OP_FNeg, OP_FExp, OP_FAddImm, OP_FRDiv)            /* SiLU      */ \
-    X(133, 3, OP_Dup, OP_FPermW, OP_FAdd)                                /* width combine */ \
-    X(134, 5, OP_Pop, OP_FAdd, OP_FAdd, OP_FAdd, OP_StoreGlobal2DWF32)   /* bmm row end */ \
-    X(135, 2, OP_FMul, OP_FAdd)                                                          \
-    X(136, 2, OP_FMul, OP_StoreGlobal1DF32)
+    GINT_FUSED_1D(X, 114, OP_PfTakeIssue1DFast)                                          \
+    GINT_FUSED_1D(X, 121, OP_PfTake)                                                     \
+    X(128, 4, OP_DupBroadcastW, OP_LoadGlobal2DWF32, OP_FMul, OP_Swap)   /* bmm inner step */ \
+    X(129, 5, OP_Dup, OP_FNeg, OP_FExp, OP_FAddImm, OP_FRDiv)            /* SiLU      */ \
+    X(130, 3, OP_Dup, OP_FPermW, OP_FAdd)                                /* width combine */ \
+    X(131, 5, OP_Pop, OP_FAdd, OP_FAdd, OP_FAdd, OP_StoreGlobal2DWF32)   /* bmm row end */ \
+    X(132, 2, OP_FMul, OP_FAdd)                                                          \
+    X(133, 2, OP_FMul, OP_StoreGlobal1DF32Fast)
 
-#define GINT_N_FUSED 27
-#define GINT_N_DISPATCH_ALL (GINT_FUSED_FIRST + GINT_N_FUSED)   /* 137 */
+#define GINT_N_FUSED 20
+#define GINT_N_DISPATCH_ALL (GINT_FUSED_FIRST + GINT_N_FUSED)   /* 134 */
 #define GINT_MAX_FUSED_LEN 5
 
 /* does the instruction read its operand word? (fused handlers fetch operands only for those that do) */
 #define GINT_OP_USES_OPERAND(op)                                                                                           \
     (((op) >= OP_LoadImm && (op) <= OP_LoadGlobal1DU8) || (op) == OP_FApprox || ((op) >= OP_LoadGlobal1DF32Indirect && (op) <= OP_DupBroadcastW) || \
-     (op) == OP_FPermW || (op) == OP_FShuf2 || (op) == OP_PfIssue1D || (op) == OP_PfTakeIssue1D)
+     (op) == OP_FPermW || (op) == OP_FShuf2 || (op) == OP_PfIssue1D || (op) == OP_PfTakeIssue1D || ((op) >= OP_LoadGlobal1DF32Fast && (op) <= OP_PfTakeIssue1DFast))
 
 #endif /* GINT_FUSED_H */

@@ -324,7 +324,9 @@ __device__ __forceinline__ void decode_tiles(const gint_tensor_info *__restrict_
 {
     const int k = lane >> 3, t = lane & 7;
     if (k < K) {
-        const uint32_t bidx = first_idx + (uint32_t)k;
+        /* A group at the end of the range may have fewer than K logical programs: the spare tiles repeat the last one
+         * (same loads, same values, same stores from the same threads), so that no handler needs to know about them. */
+        const uint32_t bidx = min(first_idx + (uint32_t)k, end_idx - 1u);
         u64 ptr = 0;
         int2 s1 = make_int2(INT32_MIN, 0);  // x < INT32_MIN never holds: every access of this slot is masked
         int2 s2 = make_int2(INT32_MIN, 0);
@@ -474,7 +476,25 @@ GINT_INTERNAL_OPCODE_LIST(GINT_X_INFO)
 template <int OP, int SP, int P> __host__ __device__ constexpr bool op_valid();
 
 /* Fused handlers (gint_fused.h): a sequence's stack effect and validity follow from its members. */
-template <int... OPS> struct Seq { static constexpr int n = sizeof...(OPS); };
+template <int... OPS> struct Seq {
+    static constexpr int n = sizeof...(OPS);
+    /* stream entries the sequence occupies: one, plus one for every member after the first that reads an operand word */
+    static __host__ __device__ constexpr int entries()
+    {
+        constexpr int ops[] = {OPS..., 0};
+        int m = 1;
+        for (int j = 1; j < n; j++) m += GINT_OP_USES_OPERAND(ops[j]) ? 1 : 0;
+        return m;
+    }
+    /* 1-based index, among those extra entries, of the entry that carries member j's operand (j >= 1, operand-reading) */
+    static __host__ __device__ constexpr int entry_of(int j)
+    {
+        constexpr int ops[] = {OPS..., 0};
+        int e = 0;
+        for (int i = 1; i <= j; i++) e += GINT_OP_USES_OPERAND(ops[i]) ? 1 : 0;
+        return e;
+    }
+};
 template <int NUM> struct FusedSeq;
 #define GINT_X_FSEQ(num, len, ...) template <> struct FusedSeq<num> { using type = Seq<__VA_ARGS__>; static_assert(Seq<__VA_ARGS__>::n == len, "length"); };
 GINT_FUSED_LIST(GINT_X_FSEQ)
@@ -605,6 +625,13 @@ __device__ __forceinline__ void tile_issue(const TileInfo *ti, uint32_t operand,
         const bool ok = e + 32 * w < s1.x;
         cp_async_f32(dst + 128 * w, ok ? p + w * pstep : base, ok);
     }
+}
+/* The same for a tile that the host proved full, unit-stride and 16-byte aligned: no shape, stride or mask handling. */
+template <int K, int KI>
+__device__ __forceinline__ void tile_issue_fast(const TileInfo *ti, uint32_t operand, const Ctx &cx, uint32_t slot)
+{
+    const char *p = reinterpret_cast<const char *>(ti->ptr[operand & 15]) + ((operand >> 4) * 4u) + cx.lane * 16;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(slot + (uint32_t)(KI * 512 + cx.lane * 12)), "l"(p) : "memory");
 }
 template <int K, int SLOT, int KI> __device__ __forceinline__ void take_hidden(uint32_t slot)
 {
@@ -748,7 +775,18 @@ __device__ __forceinline__ void exec_tile(const uint32_t operand, const Ctx &cx)
         slot_write<K, T, KI>(t);
     }
     /* ---- global memory (load_store.py) ---- */
-    else if constexpr (MemOp<OP>::is) {
+    else if constexpr (OP == OP_LoadGlobal1DF32Fast) {  // full unit-stride tile (proved by the host): elem = off + lane + 32 w
+        const char *p = reinterpret_cast<const char *>(cx.tiles[KI].ptr[operand & 15]) + ((operand >> 4) * 4u) + cx.lane * 4;
+        asm volatile("{\n\t.reg .b32 t<4>;\n\t"
+                     "ld.global.b32 t0, [%2];\n\tld.global.b32 t1, [%2+128];\n\tld.global.b32 t2, [%2+256];\n\tld.global.b32 t3, [%2+384];\n\t"
+                     "mov.b64 %%gs%0, {t0, t1};\n\tmov.b64 %%gs%1, {t2, t3};\n\t}" ::"n"(LO(SP)), "n"(HI(SP)), "l"(p) : "memory");
+    } else if constexpr (OP == OP_StoreGlobal1DF32Fast) {
+        char *p = reinterpret_cast<char *>(cx.tiles[KI].ptr[operand & 15]) + ((operand >> 4) * 4u) + cx.lane * 4;
+        asm volatile("{\n\t.reg .b32 t<4>;\n\t"
+                     "mov.b64 {t0, t1}, %%gs%0;\n\tmov.b64 {t2, t3}, %%gs%1;\n\t"
+                     "st.global.b32 [%2], t0;\n\tst.global.b32 [%2+128], t1;\n\tst.global.b32 [%2+256], t2;\n\tst.global.b32 [%2+384], t3;\n\t}"
+                     ::"n"(LO(T)), "n"(HI(T)), "l"(p) : "memory");
+    } else if constexpr (MemOp<OP>::is) {
         float v[4];
         if constexpr (MemOp<OP>::store) {
             slot_read<K, T, KI>(v);
@@ -782,12 +820,12 @@ __device__ __forceinline__ void exec_tile(const uint32_t operand, const Ctx &cx)
 template <int OP, int SP, int P, int K, int... KI>
 __device__ __forceinline__ void exec_all(const uint32_t operand, const Ctx &cx, std::integer_sequence<int, KI...>)
 {
-    if constexpr (OP >= OP_PfTake) {
+    if constexpr ((OP >= OP_PfTake && OP <= OP_PfSkip) || OP == OP_PfIssue1DFast || OP == OP_PfTakeIssue1DFast) {
         /* Early-issued loads. One cp.async group per load (all K tiles together). When load n is taken, the D-1 loads
          * after it are in flight, so "all but the newest D-1 groups have landed" is exactly "load n has landed"; a plain
          * PfTake belongs to the tail of the program, where fewer are in flight, and simply waits for everything. */
         constexpr int D = hidden_slots(P);
-        constexpr bool take = OP == OP_PfTake || OP == OP_PfTakeIssue1D;
+        constexpr bool take = OP == OP_PfTake || OP == OP_PfTakeIssue1D || OP == OP_PfTakeIssue1DFast;
         uint32_t ring;
         asm volatile("mov.b32 %0, %%gring;" : "=r"(ring));
         const uint32_t slot = cx.hidden + ring;
@@ -798,6 +836,7 @@ __device__ __forceinline__ void exec_all(const uint32_t operand, const Ctx &cx, 
             (take_hidden<K, SP, KI>(slot), ...);
         }
         if constexpr (OP == OP_PfIssue1D || OP == OP_PfTakeIssue1D) (tile_issue<K, KI>(cx.tiles + KI, operand, cx, slot), ...);
+        if constexpr (OP == OP_PfIssue1DFast || OP == OP_PfTakeIssue1DFast) (tile_issue_fast<K, KI>(cx.tiles + KI, operand, cx, slot), ...);
         if constexpr (OP != OP_PfTake && OP != OP_PfSkip) asm volatile("cp.async.commit_group;" ::: "memory");
         asm volatile("add.u32 %%gring, %%gring, %0;\n\tand.b32 %%gring, %%gring, %1;" ::"n"(K * 512), "n"(D * K * 512 - 1));
     } else {
@@ -841,16 +880,22 @@ template <int OP0, int... REST, int SP, int P, int K, int J> struct SeqRun<Seq<O
         SeqRun<Seq<REST...>, SP + OpInfo<OP0>::net_effect, P, K, J + 1>::run(cx, ops);
     }
 };
-template <typename S, int J> struct SeqFetch;
-template <int J> struct SeqFetch<Seq<>, J> {
-    static __device__ __forceinline__ void run(uint32_t, uint32_t *) {}
+/* Operands of the members after the first: member J's operand is word 0 of the sequence's extra entry number
+ * S::entry_of(J) (1-based), i.e. at [base + 8*(entry_of(J)-1)]; the last extra entry also carries, as word 1, the opcode to
+ * dispatch on afterwards, so it is fetched as a pair. */
+template <typename S, typename Rest, int J> struct SeqFetch;
+template <typename S, int J> struct SeqFetch<S, Seq<>, J> {
+    static __device__ __forceinline__ void run(uint32_t, uint32_t *, uint32_t &) {}
 };
-template <int OP0, int... REST, int J> struct SeqFetch<Seq<OP0, REST...>, J> {
-    static __device__ __forceinline__ void run(uint32_t base, uint32_t *ops)
+template <typename S, int OP0, int... REST, int J> struct SeqFetch<S, Seq<OP0, REST...>, J> {
+    static __device__ __forceinline__ void run(uint32_t base, uint32_t *ops, uint32_t &next_opcode)
     {
-        /* member J >= 1 has its operand in stream entry (first entry of the sequence) + J, i.e. at [base + 8*(J-1)] */
-        if constexpr (J >= 1 && GINT_OP_USES_OPERAND(OP0)) asm volatile("ld.shared.u32 %0, [%1+%2];" : "=r"(ops[J]) : "r"(base), "n"(8 * (J - 1)));
-        SeqFetch<Seq<REST...>, J + 1>::run(base, ops);
+        if constexpr (J >= 1 && GINT_OP_USES_OPERAND(OP0)) {
+            constexpr int e = S::entry_of(J);
+            if constexpr (e == S::entries() - 1) asm volatile("ld.shared.v2.u32 {%0, %1}, [%2+%3];" : "=r"(ops[J]), "=r"(next_opcode) : "r"(base), "n"(8 * (e - 1)));
+            else asm volatile("ld.shared.u32 %0, [%1+%2];" : "=r"(ops[J]) : "r"(base), "n"(8 * (e - 1)));
+        }
+        SeqFetch<S, Seq<REST...>, J + 1>::run(base, ops, next_opcode);
     }
 };
 
@@ -906,24 +951,27 @@ template <bool SMEM> __device__ __forceinline__ void state_advance(uint32_t &ope
  * (depth, opcode) keys) and handlers branch back to it: one more branch per instruction, but a control-flow graph that
  * ptxas digests in seconds whatever surrounds the interpreter.
  */
-/* A fused handler covers n consecutive instructions i .. i+n-1. On entry %ge holds stream entry i+1 = {operand_i, -} and
- * %gc points at entry i+2; the opcode to dispatch on afterwards sits in entry i+n and the entry the next handler expects
- * in %ge is entry i+n+1. (Direct mode only: the stream is in shared memory.) */
+/* A fused handler covers n consecutive instructions but only m = S::entries() stream entries (see SeqFetch). On entry %ge
+ * holds the first of them, {operand of the first member, opcode after the sequence if m == 1}, and %gc points at the
+ * next entry. (Shared-memory streams only.) */
 template <int NUM, int SP, int P, int K>
 __device__ __forceinline__ void run_fused(const Ctx &cx, uint32_t &next_opcode)
 {
     using S = typename FusedSeq<NUM>::type;
-    constexpr int n = S::n;
+    constexpr int m = S::entries();
     uint32_t ops[GINT_MAX_FUSED_LEN];
-    uint32_t base;
-    asm volatile("mov.b32 %0, %%ge0; mov.b32 %1, %%gc;" : "=r"(ops[0]), "=r"(base));
-    asm volatile("ld.shared.u32 %0, [%1+%2];" : "=r"(next_opcode) : "r"(base), "n"(8 * (n - 2) + 4));
-    asm volatile("ld.shared.v2.u32 {%%ge0, %%ge1}, [%%gc+%0]; add.u32 %%gc, %%gc, %1;" ::"n"(8 * (n - 1)), "n"(8 * n) : "memory");
-    SeqFetch<S, 0>::run(base, ops);
+    if constexpr (m == 1) {
+        state_advance<true>(ops[0], next_opcode);
+    } else {
+        uint32_t base;
+        asm volatile("mov.b32 %0, %%ge0; mov.b32 %1, %%gc;" : "=r"(ops[0]), "=r"(base));
+        SeqFetch<S, S, 0>::run(base, ops, next_opcode);
+        asm volatile("ld.shared.v2.u32 {%%ge0, %%ge1}, [%%gc+%0]; add.u32 %%gc, %%gc, %1;" ::"n"(8 * (m - 1)), "n"(8 * m) : "memory");
+    }
 #ifdef GINT_GUARD
     {
         uint32_t left;
-        asm volatile("sub.u32 %%gbudget, %%gbudget, %1; mov.u32 %0, %%gbudget;" : "=r"(left) : "n"(n));
+        asm volatile("sub.u32 %%gbudget, %%gbudget, %1; mov.u32 %0, %%gbudget;" : "=r"(left) : "n"(S::n));
         if ((int)left < 0) return;
     }
 #endif

@@ -128,10 +128,15 @@
  *   PfIssue1D            start the 1-D tile load described by the operand into the current slot, advance (program prologue)
  *   PfTakeIssue1D        PfTake, then start the load described by the operand into the slot just emptied
  *   PfSkip               advance the ring without touching it (pads a prologue shorter than the ring)
+ * and when it can prove, from a program's descriptors, that a 1-D f32 access is always a full unit-stride tile that starts
+ * on a 16-byte boundary (given a 16-byte aligned base pointer, which is checked at every launch):
+ *   LoadGlobal1DF32Fast / StoreGlobal1DF32Fast   the same access without shape, stride or mask handling
+ *   PfIssue1DFast / PfTakeIssue1DFast            PfIssue1D / PfTakeIssue1D likewise: one 16-byte copy per lane
  */
 #define GINT_INTERNAL_OPCODE_LIST(X) \
-    X(PfTake, 106, 0, 1) X(PfIssue1D, 107, 0, 0) X(PfTakeIssue1D, 108, 0, 1) X(PfSkip, 109, 0, 0)
-#define GINT_N_DISPATCH 137   /* opcodes the kernels dispatch on: the 106 of the format, the 4 above and the fused
+    X(PfTake, 106, 0, 1) X(PfIssue1D, 107, 0, 0) X(PfTakeIssue1D, 108, 0, 1) X(PfSkip, 109, 0, 0) \
+    X(LoadGlobal1DF32Fast, 110, 0, 1) X(StoreGlobal1DF32Fast, 111, 1, -1) X(PfIssue1DFast, 112, 0, 0) X(PfTakeIssue1DFast, 113, 0, 1)
+#define GINT_N_DISPATCH 134   /* opcodes the kernels dispatch on: the 106 of the format, the 8 above and the fused
                                  handlers of gint_fused.h */
 
 enum gint_opcode {

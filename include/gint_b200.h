@@ -102,7 +102,8 @@ int gint_predecode(const int32_t *code, int n_words, uint32_t *out_keys, int max
 
 /* The instruction list the kernels actually run for a program, after the optional early-issue and fusion passes (for
  * tests; no GPU needed): out_ops[i] is a format opcode, an internal opcode (>= 106) or -1 for an instruction absorbed into
- * the fused handler before it. Returns the number of instructions (including the Halt) or < 0. */
+ * the fused handler before it. With early_issue != 0 the descriptors in `ti` also decide which 1-D accesses become their
+ * "fast" forms (provably full, aligned tiles). Returns the number of instructions (including the Halt) or < 0. */
 int gint_debug_transform(const int32_t *code, int n_words, const gint_tensor_info *ti, int n_tensors, int early_issue, int fuse,
                          int32_t *out_ops, uint32_t *out_operands, int max_insns);
 

@@ -49,9 +49,10 @@ def test_c_header_table_matches_python():
     path = os.path.join(os.path.dirname(os.path.dirname(__file__)), "gint_b200", "csrc", "gint_opcodes.h")
     import re
     rows = re.findall(r"X\((\w+), (\d+), (-?\d+), (-?\d+)\)", open(path).read())
-    internal = [r for r in rows if r[0].startswith("Pf")]      # the kernels' internal opcodes sit above the format's 106
+    internal = [r for r in rows if int(r[1]) >= opcodes.N_OPCODES]   # the kernels' internal opcodes sit above the format's 106
+    assert all(r[0].startswith("Pf") or r[0].endswith("Fast") for r in internal)
     assert sorted(int(r[1]) for r in internal) == list(range(opcodes.N_OPCODES, opcodes.N_OPCODES + len(internal)))
-    rows = [r for r in rows if not r[0].startswith("Pf")]
+    rows = [r for r in rows if int(r[1]) < opcodes.N_OPCODES]
     assert len(rows) == opcodes.N_OPCODES
     for name, num, md, net in rows:
         assert opcodes.OPCODES[name] == int(num)

@@ -13,7 +13,7 @@ from gint_b200.host import capi
 from gint_b200.host.utils import fill_tensor_info
 from gint_b200.programs import load_records, recorded
 
-PF_TAKE, PF_ISSUE_1D, PF_TAKE_ISSUE_1D, PF_SKIP = range(106, 110)
+PF_TAKE, PF_ISSUE_1D, PF_TAKE_ISSUE_1D, PF_SKIP, LOAD_1D_FAST, STORE_1D_FAST, PF_ISSUE_1D_FAST, PF_TAKE_ISSUE_1D_FAST = range(106, 114)
 
 
 def fused_table():
@@ -82,7 +82,11 @@ def undo(prog, table):
             assert op != -1
             flat.append((op, operand))
             i += 1
-    # 2. replay the ring of early-issued loads
+    # 2. fast accesses -> the generic opcodes they specialise
+    generic = {LOAD_1D_FAST: O.LoadGlobal1DF32, STORE_1D_FAST: O.StoreGlobal1DF32, PF_ISSUE_1D_FAST: PF_ISSUE_1D,
+               PF_TAKE_ISSUE_1D_FAST: PF_TAKE_ISSUE_1D}
+    flat = [(generic.get(op, op), operand) for op, operand in flat]
+    # 3. replay the ring of early-issued loads
     out, ring = [], []
     for op, operand in flat:
         if op == PF_ISSUE_1D:
@@ -141,10 +145,29 @@ def test_named_programs_get_the_expected_shape():
     dispatches = sum(1 for op, _ in both if op != -1)
     assert len(plain) == 363
     assert dispatches < 130
-    assert sum(1 for op, _ in both if op in (PF_TAKE_ISSUE_1D, PF_TAKE) or (op in table and any(m in (PF_TAKE_ISSUE_1D, PF_TAKE) for m in table[op]))) == 96
+    takes = (PF_TAKE_ISSUE_1D, PF_TAKE_ISSUE_1D_FAST, PF_TAKE)
+    assert sum(1 for op, _ in both if op in takes or (op in table and any(m in takes for m in table[op]))) == 96
+    # every tile of this program is full, unit-stride and 16-byte aligned: only the fast forms remain
+    members = [m for op, _ in both for m in (table[op] if op in table else [op])]
+    assert PF_TAKE_ISSUE_1D not in members and PF_ISSUE_1D not in members and O.StoreGlobal1DF32 not in members
+    assert members.count(STORE_1D_FAST) == 32
     # a store between two loads of the same tensor keeps the second load where it is
     from gint_b200.host import frontend as fe
     bc = [[fe.LoadGlobal1DF32, 0], [fe.StoreGlobal1DF32, 16 * 128 + 0], [fe.LoadGlobal1DF32, 16 * 128 + 0], [fe.StoreGlobal1DF32, 1], [0, 0]]
     infos = [fe.ProgramTensorInfo(4, [], [], [256, 1], [1, 0], [1, 1], [0, 0]) for _ in range(2)]
     got = transform(np.array(bc, dtype=np.int32), infos, 1, 0)
-    assert [op for op, _ in got].count(fe.LoadGlobal1DF32) == 1      # the second load was not moved across the store
+    assert [op for op, _ in got].count(LOAD_1D_FAST) == 1      # the second load was not moved across the store
+
+
+def test_fast_accesses_need_full_aligned_tiles():
+    from gint_b200.host import frontend as fe
+
+    def ops_for(n, off=0, stride=1):
+        bc = [[fe.LoadGlobal1DF32, 16 * off + 0], [fe.LoadGlobal1DF32, 16 * off + 1], [fe.FAdd, 0], [fe.StoreGlobal1DF32, 16 * off + 2], [0, 0]]
+        infos = [fe.ProgramTensorInfo(4, [], [], [n, stride], [1, 0], [(n + 127) // 128, 1], [128, 0]) for _ in range(3)]
+        return [op for op, _ in transform(np.array(bc, dtype=np.int32), infos, 1, 0)]
+
+    assert ops_for(1024) == [PF_ISSUE_1D_FAST, PF_ISSUE_1D_FAST, PF_SKIP, PF_SKIP, PF_TAKE, PF_TAKE, fe.FAdd, STORE_1D_FAST, 0]
+    assert STORE_1D_FAST not in ops_for(1000) and PF_ISSUE_1D_FAST not in ops_for(1000)      # ragged last tile
+    assert STORE_1D_FAST not in ops_for(1024 + 2, off=2)                                    # tile starts off a 16-byte boundary
+    assert STORE_1D_FAST not in ops_for(1024, stride=2)                                     # not unit-stride
