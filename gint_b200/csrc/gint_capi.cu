@@ -257,10 +257,8 @@ void early_issue_transform(const std::vector<Insn> &in, int D, EarlyIssue *out)
     out->prog.clear();
     if (ring.empty()) { out->prog = prog; return; }
     const size_t R = ring.size();
-    for (size_t n = 0; n < (size_t)D; n++) {   // prologue: fill the ring (padded so that it wraps back to slot 0)
-        if (n < R) out->prog.push_back(Insn{OP_PfIssue1D, ring[n].operand});
-        else out->prog.push_back(Insn{OP_PfSkip, 0u});
-    }
+    for (size_t n = 0; n < (size_t)D && n < R; n++) out->prog.push_back(Insn{OP_PfIssue1D, ring[n].operand});   // prologue: fill the ring
+    if (R < (size_t)D) out->prog.push_back(Insn{OP_PfSkip, (uint32_t)((size_t)D - R)});   // ... and step over the unused slots, back to slot 0
     size_t next = 0;
     for (size_t i = 0; i < prog.size(); i++) {
         if (next < R && ring[next].site == i) {
@@ -408,6 +406,7 @@ struct Program {
     int n_early = 0;
     uint8_t alias_slots[GINT_MAX_TENSORS] = {};
     uint32_t fast_slots = 0;   // tensor slots whose base pointer must be 16-byte aligned for the early-issue stream
+    bool prefer_narrow = false; // one tile per warp unless told otherwise (see plan_direct)
     uint64_t extent[GINT_MAX_TENSORS] = {};
 };
 
@@ -532,9 +531,13 @@ int plan_direct(gint_ctx *ctx, const Program *p, uint32_t count, Geometry *g)
     Geometry best{};
     bool have = false;
     for (int K : ks) {
-        /* upper bound on K: the option if set, else 2 (measured: 4 tiles per warp lose more to the lower occupancy of
-         * the 96-register kernels than they gain from amortised dispatch) */
-        if (K > (ctx->opt_tiles_per_warp ? ctx->opt_tiles_per_warp : 2)) continue;
+        /* upper bound on K: the option if set; else 2 (measured: 4 tiles per warp lose more to the lower occupancy of
+         * the 96-register kernels than they gain from amortised dispatch), and 1 for programs that are bound by memory
+         * instructions rather than by dispatch: those in which at least 2 of 5 instructions access memory (measured on
+         * RMSNorm rows: load/store issue is not amortised by more tiles per warp) and those in which at least 1 of 5
+         * instructions is a load that is not issued early (measured on the batched 4x4 product: its latency is hidden only
+         * by more resident warps, which the narrower kernel gives) */
+        if (K > (ctx->opt_tiles_per_warp ? ctx->opt_tiles_per_warp : p->prefer_narrow ? 1 : 2)) continue;
         Variant *v = find_variant(ctx, P, K);
         if (!v) continue;
         Geometry c{};
@@ -816,6 +819,14 @@ int gint_program_create(gint_ctx *ctx, const int32_t *code, int n_words, const g
             emit_stream(ei.prog, &early);
             p->n_early = ei.n_early;
         }
+        int n_mem = 0, n_loads = 0;
+        for (const Insn &in : prog) {
+            if (!is_tensor_op(in.op) || in.op == OP_AdvanceBlock2D || in.op == OP_AdvanceBase) continue;
+            n_mem++;
+            if (!writes_tensor(in.op)) n_loads++;
+        }
+        const int n_insns = (int)prog.size(), n_direct = n_loads - (usable ? ei.n_early : 0);
+        p->prefer_narrow = 5 * n_mem >= 2 * n_insns || 5 * n_direct >= n_insns;
     }
     {
         DeviceGuard guard(ctx->device);

@@ -52,6 +52,6 @@
 /* does the instruction read its operand word? (fused handlers fetch operands only for those that do) */
 #define GINT_OP_USES_OPERAND(op)                                                                                           \
     (((op) >= OP_LoadImm && (op) <= OP_LoadGlobal1DU8) || (op) == OP_FApprox || ((op) >= OP_LoadGlobal1DF32Indirect && (op) <= OP_DupBroadcastW) || \
-     (op) == OP_FPermW || (op) == OP_FShuf2 || (op) == OP_PfIssue1D || (op) == OP_PfTakeIssue1D || ((op) >= OP_LoadGlobal1DF32Fast && (op) <= OP_PfTakeIssue1DFast))
+     (op) == OP_FPermW || (op) == OP_FShuf2 || (op) == OP_PfIssue1D || (op) == OP_PfTakeIssue1D || (op) == OP_PfSkip || ((op) >= OP_LoadGlobal1DF32Fast && (op) <= OP_PfTakeIssue1DFast))
 
 #endif /* GINT_FUSED_H */

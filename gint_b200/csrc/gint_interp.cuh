@@ -838,7 +838,8 @@ __device__ __forceinline__ void exec_all(const uint32_t operand, const Ctx &cx, 
         if constexpr (OP == OP_PfIssue1D || OP == OP_PfTakeIssue1D) (tile_issue<K, KI>(cx.tiles + KI, operand, cx, slot), ...);
         if constexpr (OP == OP_PfIssue1DFast || OP == OP_PfTakeIssue1DFast) (tile_issue_fast<K, KI>(cx.tiles + KI, operand, cx, slot), ...);
         if constexpr (OP != OP_PfTake && OP != OP_PfSkip) asm volatile("cp.async.commit_group;" ::: "memory");
-        asm volatile("add.u32 %%gring, %%gring, %0;\n\tand.b32 %%gring, %%gring, %1;" ::"n"(K * 512), "n"(D * K * 512 - 1));
+        if constexpr (OP == OP_PfSkip) asm volatile("mad.lo.u32 %%gring, %0, %1, %%gring;\n\tand.b32 %%gring, %%gring, %2;" ::"r"(operand), "n"(K * 512), "n"(D * K * 512 - 1));
+        else asm volatile("add.u32 %%gring, %%gring, %0;\n\tand.b32 %%gring, %%gring, %1;" ::"n"(K * 512), "n"(D * K * 512 - 1));
     } else {
         if constexpr (OP == OP_AdvanceBlock2D || OP == OP_AdvanceBase) __syncwarp();
         (exec_tile<OP, SP, P, K, KI>(operand, cx), ...);

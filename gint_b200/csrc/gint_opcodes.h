@@ -127,7 +127,7 @@
  *   PfTake               push the four values waiting in the ring's current slot, advance the ring
  *   PfIssue1D            start the 1-D tile load described by the operand into the current slot, advance (program prologue)
  *   PfTakeIssue1D        PfTake, then start the load described by the operand into the slot just emptied
- *   PfSkip               advance the ring without touching it (pads a prologue shorter than the ring)
+ *   PfSkip               advance the ring by `operand` slots without touching them (after a prologue shorter than the ring)
  * and when it can prove, from a program's descriptors, that a 1-D f32 access is always a full unit-stride tile that starts
  * on a 16-byte boundary (given a 16-byte aligned base pointer, which is checked at every launch):
  *   LoadGlobal1DF32Fast / StoreGlobal1DF32Fast   the same access without shape, stride or mask handling

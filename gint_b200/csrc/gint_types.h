@@ -19,7 +19,7 @@ constexpr int kTensorInfoSmemBytes = 640;  // 608-byte descriptor block, padded 
 constexpr int kNumKeys = (GINT_MAX_STACK + 1) * GINT_N_DISPATCH;
 
 /* Hidden load slots per kernel geometry: how many tile loads per logical program may be in flight ahead of their use. */
-__host__ __device__ constexpr int hidden_slots(int P) { return P <= 4 ? 4 : 2; }
+__host__ __device__ constexpr int hidden_slots(int P) { (void)P; return 4; }
 
 /* Minimum resident blocks per SM requested from the compiler (caps registers per thread): the pool itself takes 4*P*K
  * registers; addresses and interpreter state take about 40 more. */

@@ -167,7 +167,7 @@ def test_fast_accesses_need_full_aligned_tiles():
         infos = [fe.ProgramTensorInfo(4, [], [], [n, stride], [1, 0], [(n + 127) // 128, 1], [128, 0]) for _ in range(3)]
         return [op for op, _ in transform(np.array(bc, dtype=np.int32), infos, 1, 0)]
 
-    assert ops_for(1024) == [PF_ISSUE_1D_FAST, PF_ISSUE_1D_FAST, PF_SKIP, PF_SKIP, PF_TAKE, PF_TAKE, fe.FAdd, STORE_1D_FAST, 0]
+    assert ops_for(1024) == [PF_ISSUE_1D_FAST, PF_ISSUE_1D_FAST, PF_SKIP, PF_TAKE, PF_TAKE, fe.FAdd, STORE_1D_FAST, 0]
     assert STORE_1D_FAST not in ops_for(1000) and PF_ISSUE_1D_FAST not in ops_for(1000)      # ragged last tile
     assert STORE_1D_FAST not in ops_for(1024 + 2, off=2)                                    # tile starts off a 16-byte boundary
     assert STORE_1D_FAST not in ops_for(1024, stride=2)                                     # not unit-stride
