@@ -36,6 +36,10 @@ import torch  # noqa: E402
 FALLBACK_HBM_GBS = 6650.0   # earlier measurement on this pool, used only when MEASURED_PEAKS.json is absent
 NOMINAL_HBM_GBS = 8000.0
 L2_BYTES = 126 * 1024 * 1024
+# dram__bytes_read.sum + dram__bytes_write.sum per leading unit (row / matrix) of one launch, from the ncu captures summarised
+# under profiles/ (small cases of the same kernels; traffic grows in proportion to the units). Lines written late in a
+# kernel are still in L2 when it ends, so the write part is a lower bound.
+NCU_DRAM_BYTES_PER_UNIT = {"rmsnorm": 299955968 / 8192, "bmm4x4": 172342528 / 1048576, "inv4x4": 87388928 / 1048576}
 
 
 def measured_peak():
@@ -339,7 +343,9 @@ def main():
             "clocks": clocks, "e2e": e2e, "gpu_launches": res["launches"],
             "roofline": {"bound": "hbm", "achieved": res["gbs"] / world, "peak": peak, "unit": "GB/s",
                          "frac": res["gbs"] / world / peak, "peak_kind": f"of {peak_kind}", "frac_of_8TBs": res["frac_of_8TBs"],
-                         "traffic": None, "algorithmic_bytes_per_launch": res["algorithmic_bytes"] // world,
+                         "traffic": (NCU_DRAM_BYTES_PER_UNIT[name] * (leading // world)) if name in NCU_DRAM_BYTES_PER_UNIT else None,
+                         "traffic_source": "ncu dram bytes per row of the 8192-row capture (profiles/) x rows of this launch",
+                         "algorithmic_bytes_per_launch": res["algorithmic_bytes"] // world,
                          "kernel_ms": res["ms_per_step"] / res["launches_per_step"]},
             "programs": {k: {kk: vv for kk, vv in v.items() if kk not in ("launches",)} for k, v in programs.items()},
         }
