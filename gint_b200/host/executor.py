@@ -192,6 +192,7 @@ class B200Executor(BaseExecutor):
         self._ctxs: dict[int, ctypes.c_void_p] = {}
         self._lock = threading.Lock()
         self.launches = 0          # number of kernel launches issued through this executor
+        self._copy_streams: dict[int, tuple] = {}   # per device: (host-to-device, device-to-host) copy streams
 
     # ------------------------------------------------------------------ plumbing
     def warp_size(self) -> int:
@@ -308,6 +309,119 @@ class B200Executor(BaseExecutor):
         if rc != 0:
             self._check(ctx, rc, "gint_execute_indirect_static" if static_tables else "gint_execute_indirect")
         self.launches += 1
+
+    def execute_streamed(self, program: BaseExecutableProgram, args: Sequence[torch.Tensor], grid_dim: int,
+                         host_inputs: dict, host_outputs: dict, n_chunks: int = 16, **extra_kwargs):
+        """Run ``program`` on data that lives in HOST memory, overlapping the transfers with the kernels.
+
+        ``args`` are the device tensors the program works on (one per argument, as for ``execute``); ``host_inputs`` maps
+        argument indices to (pinned) host tensors that are copied into those device tensors first, ``host_outputs`` maps
+        argument indices to (pinned) host tensors that receive the results. The logical grid is cut into ``n_chunks``
+        contiguous ranges; range c is copied in on one copy stream, run with ``gint_execute_range`` on the current stream
+        and copied out on a second copy stream, so the host-to-device copy of range c+1, the kernel of range c and the
+        device-to-host copy of range c-1 proceed at the same time (the two directions of the link are independent). A
+        tensor is cut along with the grid when the descriptor decode places logical program i at i times a fixed offset
+        from the base pointer (the rule of ``gint_b200.shard.element_offset``); any other tensor (broadcast operands,
+        irregular layouts) is copied whole, inputs before the first range and outputs after the last. On return the
+        current stream waits for the last copy. No counterpart in the reference, which takes device tensors only."""
+        from ..shard import element_offset, shard_range
+        device, _ = self._ctx()
+        conv = [_convert_arg(a) for a in args]
+        ctx, line = self._cacheline(program, conv, extra_kwargs)
+        infos = line.pd.input_infos
+
+        code = numpy.asarray(line.pd.program, dtype=numpy.int64).reshape(-1, 2)
+
+        def reach(slot: int):
+            """Upper bound (elements) on how far from its tile's first element a logical program reaches into slot `slot`,
+            ignoring the shape masks; None if it cannot be bounded (gather/scatter, moving base)."""
+            from .. import opcodes as O
+            info = infos[slot]
+            s1, s2 = abs(info.block_shape_stride_1[1]), abs(info.block_shape_stride_2[1])
+            far = 0
+            for op, operand in code:
+                op, operand = int(op), int(operand) & 0xFFFFFFFF
+                name = O.NAMES[op] if 0 <= op < len(O.NAMES) else ""
+                if not (name.startswith("LoadGlobal") or name.startswith("StoreGlobal") or name.startswith("Advance")) or (operand & 15) != slot:
+                    continue
+                if name.startswith("Advance") or name.endswith("Indirect"):
+                    return None
+                off = operand >> 4
+                if "1D" in name:
+                    far = max(far, (off + 127) * s1)
+                else:   # 32 rows or columns of four values
+                    far = max(far, 31 * s1 + (off + 3) * s2, (off + 3) * s1 + 31 * s2)
+            return far
+
+        def cut(arg_index: int):
+            """bytes per logical program if the tensor can be cut along the grid (logical program i touches only bytes
+            [i*step, (i+1)*step) of it), else None"""
+            slots = [i for i, a in enumerate(line.indices) if a == arg_index]
+            if not slots:
+                return None
+            steps = set()
+            for i in slots:
+                if infos[i].block_shape_stride_1[1] < 0 or infos[i].block_shape_stride_2[1] < 0:
+                    return None
+                one = element_offset(infos[i], 1)
+                probes = {grid_dim - 1, grid_dim // 2, 2}
+                if one == 0 or any(element_offset(infos[i], k) != k * one for k in probes if 0 <= k < grid_dim):
+                    return None
+                far = reach(i)
+                if far is None or far >= one:
+                    return None
+                steps.add(one * infos[i].elm_size)
+            return steps.pop() if len(steps) == 1 else None
+
+        def as_bytes(t: torch.Tensor) -> torch.Tensor:
+            return t.contiguous().view(torch.uint8).reshape(-1) if not t.is_contiguous() else t.view(torch.uint8).reshape(-1)
+
+        plan = []   # (device bytes, host bytes, bytes per logical program or None, is_input)
+        for table, is_input in ((host_inputs, True), (host_outputs, False)):
+            for a, host in table.items():
+                dev = args[a]
+                if not (dev.is_contiguous() and host.is_contiguous()) or dev.numel() * dev.element_size() != host.numel() * host.element_size():
+                    raise ValueError("execute_streamed needs contiguous host and device tensors of equal size")
+                plan.append((as_bytes(dev), as_bytes(host), cut(a), is_input))
+        streams = self._copy_streams.get(device)
+        if streams is None:
+            streams = self._copy_streams[device] = (torch.cuda.Stream(device), torch.cuda.Stream(device))
+        h2d, d2h = streams
+        compute = torch.cuda.current_stream(device)
+        start = torch.cuda.Event()
+        start.record(compute)
+        h2d.wait_event(start)
+        d2h.wait_event(start)
+        with torch.cuda.stream(h2d):
+            for dev, host, step, is_input in plan:
+                if is_input and step is None:
+                    dev.copy_(host, non_blocking=True)
+        n_chunks = max(1, min(int(n_chunks), grid_dim))
+        for c in range(n_chunks):
+            first, count = shard_range(grid_dim, n_chunks, c)
+            last = c == n_chunks - 1
+            with torch.cuda.stream(h2d):
+                for dev, host, step, is_input in plan:
+                    if is_input and step is not None:
+                        lo, hi = first * step, (dev.numel() if last else min((first + count) * step, dev.numel()))
+                        if lo < hi:
+                            dev[lo:hi].copy_(host[lo:hi], non_blocking=True)
+                arrived = torch.cuda.Event()
+                arrived.record(h2d)
+            compute.wait_event(arrived)
+            self.execute_range(program, conv, first, count, cuda_stream=compute.cuda_stream, **extra_kwargs)
+            computed = torch.cuda.Event()
+            computed.record(compute)
+            with torch.cuda.stream(d2h):
+                d2h.wait_event(computed)
+                for dev, host, step, is_input in plan:
+                    if not is_input and (step is not None or last):
+                        lo, hi = (0, dev.numel()) if step is None else (first * step, dev.numel() if last else min((first + count) * step, dev.numel()))
+                        if lo < hi:
+                            host[lo:hi].copy_(dev[lo:hi], non_blocking=True)
+        done = torch.cuda.Event()
+        done.record(d2h)
+        compute.wait_event(done)
 
     # ------------------------------------------------------------------ introspection / tuning
     def launch_info(self, program: BaseExecutableProgram, args: Sequence, grid_dim: int, **extra_kwargs) -> dict:

@@ -203,6 +203,30 @@ def test_execute_range_shards_cover_the_grid():
         assert torch.equal(out_loc, want[rows])
 
 
+@pytest.mark.parametrize("name,leading,inner,chunks", [("rmsnorm", 64, 4096, 5), ("rmsnorm", 7, 256, 16), ("add", 4096, 1, 4),
+                                                       ("add", 1000, 1, 3), ("bmm4x4", 1000, 16, 7), ("inv4x4", 33, 16, 2)])
+def test_execute_streamed_matches_execute(name, leading, inner, chunks):
+    """Host data, transfers overlapped with the kernels range by range: same bits as copy-in, one launch, copy-out."""
+    from gint_b200.workloads import make_workload
+    ex = get_executor()
+    wl = make_workload(name, leading, inner, device="cuda")
+    st = wl.steps[0]
+    host = {r: t.cpu().pin_memory() for r, t in wl.tensors.items()}
+    wl.run(ex)
+    torch.cuda.synchronize()
+    want = {r: wl.tensors[r].cpu() for r in wl.outputs}
+    dev = [torch.full_like(wl.tensors[r], float("nan")) for r in st.roles]           # staging buffers hold no data yet
+    ins = {i: host[r] for i, r in enumerate(st.roles) if r not in wl.outputs}
+    outs = {i: torch.zeros_like(host[r]).pin_memory() for i, r in enumerate(st.roles) if r in wl.outputs}
+    launches = ex.launches
+    ex.execute_streamed(st.program, dev, st.grid_dim, ins, outs, n_chunks=chunks)
+    torch.cuda.synchronize()
+    assert ex.launches - launches == min(chunks, st.grid_dim)
+    for i, r in enumerate(st.roles):
+        if r in wl.outputs:
+            assert bits_equal(outs[i], want[r]), mismatch_report(outs[i], want[r])
+
+
 def test_launch_info_reports_geometry():
     from gint_b200.workloads import make_workload
     ex = get_executor()
