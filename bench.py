@@ -5,8 +5,8 @@
 
 Headline workload: the conductor-lowered RMSNorm bytecode program over x fp32 [16384, 4096] (the configuration the
 metric is quoted on), one "step" = one pass of the program over the whole batch. With N > 1 (launched by torchrun, one
-process per GPU) the rows are split N ways, every rank runs its shard with no data-path collective, and the reported
-value is all ranks' bytes divided by the slowest rank's device time.
+process per GPU) the batch is N times as large and sharded by rows: every rank runs its own 16384-row shard (weak scaling),
+with no data-path collective, and the reported value is all ranks' bytes divided by the slowest rank's device time.
 
 Prints ONE JSON line. `value` is achieved HBM GB/s = algorithmic bytes / device time with inputs resident in HBM;
 `e2e` is the same metric through the public executor API with HOST buffers (pinned host -> device copy of the inputs and
@@ -200,7 +200,6 @@ def run_program_bench(name: str, world: int, rank: int, steps: int, warmup: int,
     from gint_b200.workloads import FULL_SIZES, make_workload
     ex = get_executor()
     leading, inner = FULL_SIZES[name]
-    leading //= world
     seed = 42 + rank
     # a+b is 12 MB and would sit in L2: rotate over enough independent buffer sets to exceed it
     n_sets = 1
@@ -245,7 +244,6 @@ def run_e2e(name: str, world: int, rank: int, steps: int, warmup: int, overlappe
     from gint_b200.workloads import FULL_SIZES, make_workload
     ex = get_executor()
     leading, inner = FULL_SIZES[name]
-    leading //= world
     wl = make_workload(name, leading, inner, device="cuda", seed=42 + rank)
     in_roles = [r for r in wl.tensors if r not in wl.outputs and r not in ("g", "x_rows")]
     host_in = {r: wl.tensors[r].cpu().pin_memory() for r in in_roles}
@@ -301,7 +299,7 @@ def main():
     config = {"workload": {"add": "configs[0] a+b fp32 [1048576]", "rmsnorm": "configs[1] RMSNorm x fp32 [16384,4096], conductor-lowered bytecode (363 insns)",
                            "bmm4x4": "configs[2] batched 4x4 matmul [4194304,4,4]", "inv4x4": "configs[3] batched 4x4 inverse [4194304,4,4]",
                            "graph": "configs[4] conductor graph x [65536,1024]"}[name],
-              "leading": leading, "inner": inner, "sharding": f"rows split {opts.gpus} ways, no collective"}
+              "leading": leading, "inner": inner, "sharding": f"{opts.gpus} rank(s), each running its own {leading}-unit shard of a {opts.gpus * leading}-unit batch; no collective"}
 
     if opts.impl == "reference":
         rank = int(os.environ.get("RANK", "0"))
@@ -357,7 +355,7 @@ def main():
             "clocks": clocks, "e2e": e2e, "gpu_launches": res["launches"],
             "roofline": {"bound": "hbm", "achieved": res["gbs"] / world, "peak": peak, "unit": "GB/s",
                          "frac": res["gbs"] / world / peak, "peak_kind": f"of {peak_kind}", "frac_of_8TBs": res["frac_of_8TBs"],
-                         "traffic": (NCU_DRAM_BYTES_PER_UNIT[name] * (leading // world)) if name in NCU_DRAM_BYTES_PER_UNIT else None,
+                         "traffic": (NCU_DRAM_BYTES_PER_UNIT[name] * leading) if name in NCU_DRAM_BYTES_PER_UNIT else None,
                          "traffic_source": "ncu dram bytes per row of the 8192-row capture (profiles/) x rows of this launch",
                          "algorithmic_bytes_per_launch": res["algorithmic_bytes"] // world,
                          "kernel_ms": res["ms_per_step"] / res["launches_per_step"]},
