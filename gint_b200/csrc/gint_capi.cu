@@ -320,8 +320,9 @@ uint32_t apply_fast_accesses(std::vector<Insn> *prog, const gint_tensor_info &ti
         }
         const int slot = (int)(in.operand & 15u);
         const int64_t off = (int64_t)(in.operand >> 4);
-        if (slot >= n_tensors || !ok[slot] || (off & 3) != 0 || off + 128 > min_extent[slot]) continue;
+        if (slot >= n_tensors || slot >= 8 || !ok[slot] || (off & 3) != 0 || off + 128 > min_extent[slot] || off * 4 >= (1 << 26)) continue;
         in.op = fast;
+        in.operand = ((uint32_t)slot << 29) | (uint32_t)(off * 4);   // {8 * slot, byte offset}: see fast_tile_address in gint_interp.cuh
         used |= 1u << slot;
     }
     return used;

@@ -43,11 +43,17 @@
     X(130, 3, OP_Dup, OP_FPermW, OP_FAdd)                                /* width combine */ \
     X(131, 5, OP_Pop, OP_FAdd, OP_FAdd, OP_FAdd, OP_StoreGlobal2DWF32)   /* bmm row end */ \
     X(132, 2, OP_FMul, OP_FAdd)                                                          \
-    X(133, 2, OP_FMul, OP_StoreGlobal1DF32Fast)
+    X(133, 2, OP_FMul, OP_StoreGlobal1DF32Fast)                                          \
+    /* whole chunk bodies: two reduction steps; scale by s and by w, store; the same without the store; SiLU, add, store */ \
+    X(134, 8, OP_PfTakeIssue1DFast, OP_Dup, OP_FMul, OP_FAdd, OP_PfTakeIssue1DFast, OP_Dup, OP_FMul, OP_FAdd) \
+    X(135, 7, OP_Dup, OP_PfTakeIssue1DFast, OP_Swap, OP_FMul, OP_PfTakeIssue1DFast, OP_FMul, OP_StoreGlobal1DF32Fast) \
+    X(136, 6, OP_Dup, OP_PfTakeIssue1DFast, OP_Swap, OP_FMul, OP_PfTakeIssue1DFast, OP_FMul) \
+    X(137, 8, OP_Dup, OP_FNeg, OP_FExp, OP_FAddImm, OP_FRDiv, OP_PfTakeIssue1DFast, OP_FAdd, OP_StoreGlobal1DF32Fast) \
+    X(138, 4, OP_PfTakeIssue1DFast, OP_FAdd, OP_PfTakeIssue1DFast, OP_FAdd)
 
-#define GINT_N_FUSED 20
-#define GINT_N_DISPATCH_ALL (GINT_FUSED_FIRST + GINT_N_FUSED)   /* 134 */
-#define GINT_MAX_FUSED_LEN 5
+#define GINT_N_FUSED 25
+#define GINT_N_DISPATCH_ALL (GINT_FUSED_FIRST + GINT_N_FUSED)   /* 139 */
+#define GINT_MAX_FUSED_LEN 8
 
 /* does the instruction read its operand word? (fused handlers fetch operands only for those that do) */
 #define GINT_OP_USES_OPERAND(op)                                                                                           \

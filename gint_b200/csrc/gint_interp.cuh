@@ -626,11 +626,19 @@ __device__ __forceinline__ void tile_issue(const TileInfo *ti, uint32_t operand,
         cp_async_f32(dst + 128 * w, ok ? p + w * pstep : base, ok);
     }
 }
+/* Operand of the fast accesses, as the host pre-decoder writes it (gint_capi.cu: apply_fast_accesses): byte offset of the
+ * tile from the tensor's tile pointer in bits 0..25, 8 * tensor slot in bits 26..31 -- the byte offset of the slot's
+ * pointer in TileInfo::ptr. */
+__device__ __forceinline__ char *fast_tile_address(const TileInfo *ti, uint32_t operand)
+{
+    const u64 base = *reinterpret_cast<const u64 *>(reinterpret_cast<const char *>(ti->ptr) + (operand >> 26));
+    return reinterpret_cast<char *>(base) + (operand & 0x03FFFFFFu);
+}
 /* The same for a tile that the host proved full, unit-stride and 16-byte aligned: no shape, stride or mask handling. */
 template <int K, int KI>
 __device__ __forceinline__ void tile_issue_fast(const TileInfo *ti, uint32_t operand, const Ctx &cx, uint32_t slot)
 {
-    const char *p = reinterpret_cast<const char *>(ti->ptr[operand & 15]) + ((operand >> 4) * 4u) + cx.lane * 16;
+    const char *p = fast_tile_address(ti, operand) + cx.lane * 16;
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(slot + (uint32_t)(KI * 512 + cx.lane * 12)), "l"(p) : "memory");
 }
 template <int K, int SLOT, int KI> __device__ __forceinline__ void take_hidden(uint32_t slot)
@@ -776,12 +784,12 @@ __device__ __forceinline__ void exec_tile(const uint32_t operand, const Ctx &cx)
     }
     /* ---- global memory (load_store.py) ---- */
     else if constexpr (OP == OP_LoadGlobal1DF32Fast) {  // full unit-stride tile (proved by the host): elem = off + lane + 32 w
-        const char *p = reinterpret_cast<const char *>(cx.tiles[KI].ptr[operand & 15]) + ((operand >> 4) * 4u) + cx.lane * 4;
+        const char *p = fast_tile_address(cx.tiles + KI, operand) + cx.lane * 4;
         asm volatile("{\n\t.reg .b32 t<4>;\n\t"
                      "ld.global.b32 t0, [%2];\n\tld.global.b32 t1, [%2+128];\n\tld.global.b32 t2, [%2+256];\n\tld.global.b32 t3, [%2+384];\n\t"
                      "mov.b64 %%gs%0, {t0, t1};\n\tmov.b64 %%gs%1, {t2, t3};\n\t}" ::"n"(LO(SP)), "n"(HI(SP)), "l"(p) : "memory");
     } else if constexpr (OP == OP_StoreGlobal1DF32Fast) {
-        char *p = reinterpret_cast<char *>(cx.tiles[KI].ptr[operand & 15]) + ((operand >> 4) * 4u) + cx.lane * 4;
+        char *p = fast_tile_address(cx.tiles + KI, operand) + cx.lane * 4;
         asm volatile("{\n\t.reg .b32 t<4>;\n\t"
                      "mov.b64 {t0, t1}, %%gs%0;\n\tmov.b64 {t2, t3}, %%gs%1;\n\t"
                      "st.global.b32 [%2], t0;\n\tst.global.b32 [%2+128], t1;\n\tst.global.b32 [%2+256], t2;\n\tst.global.b32 [%2+384], t3;\n\t}"

@@ -136,7 +136,7 @@
 #define GINT_INTERNAL_OPCODE_LIST(X) \
     X(PfTake, 106, 0, 1) X(PfIssue1D, 107, 0, 0) X(PfTakeIssue1D, 108, 0, 1) X(PfSkip, 109, 0, 0) \
     X(LoadGlobal1DF32Fast, 110, 0, 1) X(StoreGlobal1DF32Fast, 111, 1, -1) X(PfIssue1DFast, 112, 0, 0) X(PfTakeIssue1DFast, 113, 0, 1)
-#define GINT_N_DISPATCH 134   /* opcodes the kernels dispatch on: the 106 of the format, the 8 above and the fused
+#define GINT_N_DISPATCH 139   /* opcodes the kernels dispatch on: the 106 of the format, the 8 above and the fused
                                  handlers of gint_fused.h */
 
 enum gint_opcode {

@@ -107,7 +107,7 @@ int gint_predecode(const int32_t *code, int n_words, uint32_t *out_keys, int max
 int gint_debug_transform(const int32_t *code, int n_words, const gint_tensor_info *ti, int n_tensors, int early_issue, int fuse,
                          int32_t *out_ops, uint32_t *out_operands, int max_insns);
 
-/* The fused-handler table: rows of 7 ints {opcode number, length, member opcodes (padded with -1)}. Returns the row count. */
+/* The fused-handler table: rows of 10 ints {opcode number, length, 8 member opcodes (padded with -1)}. Returns the row count. */
 int gint_debug_fused_table(int32_t *out, int max_entries);
 
 /* ---- context ------------------------------------------------------------------------------------ */

@@ -18,10 +18,10 @@ PF_TAKE, PF_ISSUE_1D, PF_TAKE_ISSUE_1D, PF_SKIP, LOAD_1D_FAST, STORE_1D_FAST, PF
 
 def fused_table():
     lib = capi.load_library()
-    buf = (ctypes.c_int32 * (64 * 7))()
+    buf = (ctypes.c_int32 * (64 * 10))()
     n = lib.gint_debug_fused_table(buf, 64)
     assert n > 0
-    return {buf[7 * k]: [buf[7 * k + 2 + j] for j in range(buf[7 * k + 1])] for k in range(n)}
+    return {buf[10 * k]: [buf[10 * k + 2 + j] for j in range(buf[10 * k + 1])] for k in range(n)}
 
 
 def transform(bytecode, infos, early, fuse):
@@ -85,7 +85,8 @@ def undo(prog, table):
     # 2. fast accesses -> the generic opcodes they specialise
     generic = {LOAD_1D_FAST: O.LoadGlobal1DF32, STORE_1D_FAST: O.StoreGlobal1DF32, PF_ISSUE_1D_FAST: PF_ISSUE_1D,
                PF_TAKE_ISSUE_1D_FAST: PF_TAKE_ISSUE_1D}
-    flat = [(generic.get(op, op), operand) for op, operand in flat]
+    # (their operand is {8 * slot in bits 26..31, byte offset of the tile in bits 0..25})
+    flat = [(generic[op], ((operand & 0x03FFFFFF) // 4) << 4 | operand >> 29) if op in generic else (op, operand) for op, operand in flat]
     # 3. replay the ring of early-issued loads
     out, ring = [], []
     for op, operand in flat:
@@ -146,7 +147,8 @@ def test_named_programs_get_the_expected_shape():
     assert len(plain) == 363
     assert dispatches < 130
     takes = (PF_TAKE_ISSUE_1D, PF_TAKE_ISSUE_1D_FAST, PF_TAKE)
-    assert sum(1 for op, _ in both if op in takes or (op in table and any(m in takes for m in table[op]))) == 96
+    assert sum(sum(m in takes for m in (table[op] if op in table else [op])) for op, _ in both) == 96
+    assert dispatches < 70     # two reduction steps, or a whole scale-and-store chunk, per dispatch
     # every tile of this program is full, unit-stride and 16-byte aligned: only the fast forms remain
     members = [m for op, _ in both for m in (table[op] if op in table else [op])]
     assert PF_TAKE_ISSUE_1D not in members and PF_ISSUE_1D not in members and O.StoreGlobal1DF32 not in members
