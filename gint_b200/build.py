@@ -29,7 +29,7 @@ CSRC = os.path.join(PKG_DIR, "csrc")
 KERNELS = os.path.join(CSRC, "kernels")
 OBJ_DIR = os.path.join(CSRC, "build")
 LIB_PATH = os.path.join(PKG_DIR, "libgint_b200.so")
-N_OPS = 139          # GINT_N_DISPATCH: the 106 opcodes of the format + the internal ones
+N_OPS = 142          # GINT_N_DISPATCH: the 106 opcodes of the format + the internal ones
 N_KEYS = 9 * N_OPS   # (GINT_MAX_STACK + 1) * GINT_N_DISPATCH
 
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]

@@ -136,7 +136,7 @@ int net_effect(int op)
         return net;
     }
     if (op == OP_StoreGlobal1DF32Fast) return -1;
-    return (op == OP_PfTake || op == OP_PfTakeIssue1D || op == OP_PfTakeIssue1DFast || op == OP_LoadGlobal1DF32Fast) ? 1 : 0;
+    return (op == OP_PfTake || op == OP_PfTakeIssue1D || op == OP_PfTakeIssue1DFast || op == OP_LoadGlobal1DF32Fast || op == OP_LoadStagedRows) ? 1 : 0;
 }
 
 /* Replace known instruction sequences by fused handlers (gint_fused.h): greedy, longest match first. The absorbed
@@ -329,6 +329,74 @@ uint32_t apply_fast_accesses(std::vector<Insn> *prog, const gint_tensor_info &ti
     return used;
 }
 
+/*
+ * Staged row blocks. In the small-matrix programs one lane owns one matrix: a 2DW row load is a 16-byte access per lane at
+ * the row stride (64 bytes for a 4x4 matrix), which costs 16 L1 wavefronts per warp request where 512 contiguous bytes
+ * cost 4, and the rows of an operand are loaded again for every output row. When a tensor slot is only read, only through
+ * LoadGlobal2DWF32, and its 32 rows per logical program are R = 4, 8 or 16 floats long and lie back to back (row stride R,
+ * unit column stride, always 32 valid rows, 16-byte aligned given an aligned base pointer), the whole 32 x R block is
+ * copied into shared memory once, at the start of the program, with fully coalesced copies (StageRows) and every row load
+ * reads from there (LoadStagedRows, one conflict-free 16-byte shared-memory access per lane). Returns the slots staged;
+ * *area_bytes receives the shared memory needed per tile. Loads of those slots now happen before every store of the
+ * program, so the stored slots are recorded as alias partners (checked against the launch's address ranges).
+ */
+uint32_t apply_row_staging(std::vector<Insn> *prog, const gint_tensor_info &ti, int n_tensors, uint32_t *area_bytes, uint8_t *alias_slots)
+{
+    *area_bytes = 0;
+    int lq_of[GINT_MAX_TENSORS];
+    bool ok[GINT_MAX_TENSORS];
+    uint32_t stored = 0;
+    for (int t = 0; t < GINT_MAX_TENSORS; t++) {
+        ok[t] = false;
+        lq_of[t] = 0;
+        if (t >= n_tensors) continue;
+        const int64_t rows = ti.block_shape_stride_1[t][0], row_stride = ti.block_shape_stride_1[t][1];
+        const int64_t cols = ti.block_shape_stride_2[t][0], col_stride = ti.block_shape_stride_2[t][1];
+        const int64_t gd1 = (uint32_t)ti.block_grid_dims[t][0], gd2 = (uint32_t)ti.block_grid_dims[t][1];
+        const int64_t gs1 = ti.block_grid_steps[t][0];
+        bool good = ti.elm_size[t] == 4 && col_stride == 1 && (row_stride == 4 || row_stride == 8 || row_stride == 16) &&
+                    cols >= row_stride && gd2 == 1 && gd1 >= 1 && gs1 >= 0 && rows - (gd1 - 1) * gs1 >= 32;
+        if (good && gd1 != 1 && (gs1 * row_stride) % 4 != 0) good = false;
+        for (int j = 0; good && j < 4; j++)
+            if (ti.batch_shape[t][j] != 1 && ti.batch_strides[t][j] % 4 != 0) good = false;
+        ok[t] = good;
+        lq_of[t] = row_stride == 4 ? 0 : row_stride == 8 ? 1 : 2;
+    }
+    for (const Insn &in : *prog) {
+        if (!is_tensor_op(in.op)) continue;
+        const int t = (int)(in.operand & 15u);
+        if (t >= GINT_MAX_TENSORS) continue;
+        if (writes_tensor(in.op)) stored |= 1u << t;
+        if (in.op != OP_LoadGlobal2DWF32) { ok[t] = false; continue; }
+        const int64_t j0 = (int64_t)(in.operand >> 4);
+        if ((j0 & 3) != 0 || j0 + 4 > (4ll << lq_of[t])) ok[t] = false;
+    }
+    uint32_t staged = 0, area_of[GINT_MAX_TENSORS] = {};
+    bool used[GINT_MAX_TENSORS] = {};
+    for (const Insn &in : *prog)
+        if (in.op == OP_LoadGlobal2DWF32 && (in.operand & 15u) < GINT_MAX_TENSORS && ok[in.operand & 15u]) used[in.operand & 15u] = true;
+    std::vector<Insn> head;
+    for (int t = 0; t < n_tensors; t++) {
+        if (!used[t]) continue;
+        if (*area_bytes + (512u << lq_of[t]) > 0xFFFFu) break;
+        area_of[t] = *area_bytes;
+        *area_bytes += 512u << lq_of[t];
+        staged |= 1u << t;
+        alias_slots[t] |= (uint8_t)stored;
+        head.push_back(Insn{OP_StageRows, (uint32_t)t | ((uint32_t)lq_of[t] << 3) | (area_of[t] << 8)});
+    }
+    if (!staged) return 0;
+    for (Insn &in : *prog) {
+        const uint32_t t = in.operand & 15u;
+        if (in.op != OP_LoadGlobal2DWF32 || t >= GINT_MAX_TENSORS || !((staged >> t) & 1u)) continue;
+        const uint32_t part = (in.operand >> 4) >> 2;
+        in.op = OP_LoadStagedRows;
+        in.operand = (uint32_t)lq_of[t] | (part << 2) | (t << 4) | (area_of[t] << 8);
+    }
+    prog->insert(prog->begin(), head.begin(), head.end());
+    return staged;
+}
+
 /* Conservative byte extent a program can touch from a tensor's base pointer; 0 = unknown (negative strides). */
 uint64_t tensor_extent_bytes(const gint_tensor_info &ti, int t)
 {
@@ -411,6 +479,7 @@ struct Program {
     bool prefer_narrow = false; // one tile per warp unless told otherwise (see plan_direct)
     bool rereads = false;       // some tile is loaded more than once: fewer logical programs in flight keep it in L2
     uint64_t uid = 0;           // unique per created program (a handle slot may be reused)
+    uint32_t row_area_bytes = 0; // shared memory per tile for staged row blocks (early-issue stream only)
     uint64_t extent[GINT_MAX_TENSORS] = {};
 };
 
@@ -525,7 +594,8 @@ uint32_t direct_smem(const Program *p, int K, uint32_t *code_smem)
     const uint32_t cs = (p->n_slots * 8u + 127u) & ~127u;
     *code_smem = cs;
     return cs + gint::kTensorInfoSmemBytes + (uint32_t)(gint::kWarpsPerBlock * K) * (uint32_t)sizeof(gint::TileInfo) +
-           (uint32_t)(gint::kWarpsPerBlock * K * gint::hidden_slots(p->st.pool_size) * 512);
+           (uint32_t)(gint::kWarpsPerBlock * K * gint::hidden_slots(p->st.pool_size) * 512) +
+           (uint32_t)(gint::kWarpsPerBlock * K) * p->row_area_bytes;
 }
 
 int plan_direct(gint_ctx *ctx, const Program *p, uint32_t count, Geometry *g)
@@ -600,18 +670,19 @@ int launch_direct(gint_ctx *ctx, uint64_t handle, const uint64_t *base_ptrs, int
         if (((p->fast_slots >> t) & 1u) && (base_ptrs[t] & 15u) != 0) early = false;   // fast accesses need aligned bases
     Program view = *p;   // geometry depends on the stream length
     if (early) view.n_slots = p->early_slots;
+    else view.row_area_bytes = 0;
     Geometry g;
     {
         /* the calling thread's last plan is reused while nothing it depends on changes: saves the occupancy query */
-        struct Memo { gint_ctx *ctx; uint64_t uid; uint32_t count, n_slots; int opt_k, opt_blocks; Geometry g; };
-        static thread_local Memo memo = {nullptr, 0, 0, 0, 0, 0, {}};
+        struct Memo { gint_ctx *ctx; uint64_t uid; uint32_t count, n_slots; int opt_k, opt_blocks; bool early; Geometry g; };
+        static thread_local Memo memo = {nullptr, 0, 0, 0, 0, 0, false, {}};
         if (memo.ctx == ctx && memo.uid == p->uid && memo.count == count && memo.n_slots == view.n_slots &&
-            memo.opt_k == ctx->opt_tiles_per_warp && memo.opt_blocks == ctx->opt_max_blocks) {
+            memo.opt_k == ctx->opt_tiles_per_warp && memo.opt_blocks == ctx->opt_max_blocks && memo.early == early) {
             g = memo.g;
         } else {
             int rc = plan_direct(ctx, &view, count, &g);
             if (rc != GINT_OK) return rc;
-            memo = Memo{ctx, p->uid, count, view.n_slots, ctx->opt_tiles_per_warp, ctx->opt_max_blocks, g};
+            memo = Memo{ctx, p->uid, count, view.n_slots, ctx->opt_tiles_per_warp, ctx->opt_max_blocks, early, g};
         }
     }
     LaunchArgs a;
@@ -623,7 +694,7 @@ int launch_direct(gint_ctx *ctx, uint64_t handle, const uint64_t *base_ptrs, int
     a.code_smem_bytes = g.code_smem;
     a.prefetch_mask = ctx->opt_prefetch ? p->prefetch_mask : 0u;
     a.zero = 0;
-    a.reserved = 0;
+    a.row_area_bytes = view.row_area_bytes;
     for (int t = 0; t < GINT_MAX_TENSORS; t++) a.fp[t] = p->fp[t];
     a.ti = p->ti;
     for (int i = 0; i < n_tensors; i++) a.ti.base_ptr[i] = (int64_t)base_ptrs[i];
@@ -828,7 +899,13 @@ int gint_program_create(gint_ctx *ctx, const int32_t *code, int n_words, const g
         normalise(code, n_words, n_tensors, &prog);
         EarlyIssue ei;
         early_issue_transform(prog, gint::hidden_slots(p->st.pool_size), &ei);
-        bool usable = ei.n_early > 0;
+        uint32_t row_area = 0, staged = 0;
+        int n_staged_loads = 0;
+        if (ei.n_early == 0) {   // (a program with a ring of early-issued loads keeps its cp.async groups to itself)
+            staged = apply_row_staging(&ei.prog, p->ti, n_tensors, &row_area, ei.alias_slots);
+            for (const Insn &in : ei.prog) n_staged_loads += in.op == OP_LoadStagedRows;
+        }
+        bool usable = ei.n_early > 0 || staged != 0;
         for (int t = 0; t < n_tensors; t++) {
             p->extent[t] = tensor_extent_bytes(p->ti, t);
             p->alias_slots[t] = ei.alias_slots[t];
@@ -837,10 +914,14 @@ int gint_program_create(gint_ctx *ctx, const int32_t *code, int n_words, const g
                 if ((ei.alias_slots[t] >> b) & 1u) { if (tensor_extent_bytes(p->ti, b) == 0) usable = false; }
         }
         if (usable) {
-            p->fast_slots = apply_fast_accesses(&ei.prog, p->ti, n_tensors);
+            p->fast_slots = apply_fast_accesses(&ei.prog, p->ti, n_tensors) | staged;
+            p->row_area_bytes = row_area;
             if (ctx->opt_fuse) fuse_sequences(&ei.prog);
             emit_stream(ei.prog, &early);
             p->n_early = ei.n_early;
+        } else {
+            for (int t = 0; t < n_tensors; t++) p->alias_slots[t] = 0;
+            n_staged_loads = 0;
         }
         int n_mem = 0, n_loads = 0;
         for (const Insn &in : prog) {
@@ -857,7 +938,7 @@ int gint_program_create(gint_ctx *ctx, const int32_t *code, int n_words, const g
                 seen.push_back(in.operand);
             }
         }
-        const int n_insns = (int)prog.size(), n_direct = n_loads - (usable ? ei.n_early : 0);
+        const int n_insns = (int)prog.size(), n_direct = n_loads - (usable ? ei.n_early + n_staged_loads : 0);
         p->prefer_narrow = 5 * n_mem >= 2 * n_insns || 5 * n_direct >= n_insns;
     }
     {
@@ -1108,9 +1189,11 @@ int gint_debug_transform(const int32_t *code, int n_words, const gint_tensor_inf
         EarlyIssue ei;
         early_issue_transform(prog, gint::hidden_slots(st.pool_size), &ei);
         prog = ei.prog;
-        if (ei.n_early > 0 && ti) {
+        if (ti) {
             gint_tensor_info t0 = *ti;
-            apply_fast_accesses(&prog, t0, n_tensors);
+            uint32_t row_area = 0, staged = 0;
+            if (ei.n_early == 0) staged = apply_row_staging(&prog, t0, n_tensors, &row_area, ei.alias_slots);
+            if (ei.n_early > 0 || staged) apply_fast_accesses(&prog, t0, n_tensors);
         }
     }
     if (fuse) fuse_sequences(&prog);

@@ -23,7 +23,7 @@
 
 #include "gint_opcodes.h"
 
-#define GINT_FUSED_FIRST 114
+#define GINT_FUSED_FIRST 116
 
 /* one entry per load flavour L for the 1-D idioms */
 #define GINT_FUSED_1D(X, base, L)                                                        \
@@ -36,28 +36,29 @@
     X(base + 6, 3, L, OP_FAdd, OP_StoreGlobal1DF32Fast)
 
 #define GINT_FUSED_LIST(X)                                                               \
-    GINT_FUSED_1D(X, 114, OP_PfTakeIssue1DFast)                                          \
-    GINT_FUSED_1D(X, 121, OP_PfTake)                                                     \
-    X(128, 4, OP_DupBroadcastW, OP_LoadGlobal2DWF32, OP_FMul, OP_Swap)   /* bmm inner step */ \
-    X(129, 5, OP_Dup, OP_FNeg, OP_FExp, OP_FAddImm, OP_FRDiv)            /* SiLU      */ \
-    X(130, 3, OP_Dup, OP_FPermW, OP_FAdd)                                /* width combine */ \
-    X(131, 5, OP_Pop, OP_FAdd, OP_FAdd, OP_FAdd, OP_StoreGlobal2DWF32)   /* bmm row end */ \
-    X(132, 2, OP_FMul, OP_FAdd)                                                          \
-    X(133, 2, OP_FMul, OP_StoreGlobal1DF32Fast)                                          \
+    GINT_FUSED_1D(X, 116, OP_PfTakeIssue1DFast)                                          \
+    GINT_FUSED_1D(X, 123, OP_PfTake)                                                     \
+    X(130, 4, OP_DupBroadcastW, OP_LoadGlobal2DWF32, OP_FMul, OP_Swap)   /* bmm inner step */ \
+    X(131, 5, OP_Dup, OP_FNeg, OP_FExp, OP_FAddImm, OP_FRDiv)            /* SiLU      */ \
+    X(132, 3, OP_Dup, OP_FPermW, OP_FAdd)                                /* width combine */ \
+    X(133, 5, OP_Pop, OP_FAdd, OP_FAdd, OP_FAdd, OP_StoreGlobal2DWF32)   /* bmm row end */ \
+    X(134, 2, OP_FMul, OP_FAdd)                                                          \
+    X(135, 2, OP_FMul, OP_StoreGlobal1DF32Fast)                                          \
     /* whole chunk bodies: two reduction steps; scale by s and by w, store; the same without the store; SiLU, add, store */ \
-    X(134, 8, OP_PfTakeIssue1DFast, OP_Dup, OP_FMul, OP_FAdd, OP_PfTakeIssue1DFast, OP_Dup, OP_FMul, OP_FAdd) \
-    X(135, 7, OP_Dup, OP_PfTakeIssue1DFast, OP_Swap, OP_FMul, OP_PfTakeIssue1DFast, OP_FMul, OP_StoreGlobal1DF32Fast) \
-    X(136, 6, OP_Dup, OP_PfTakeIssue1DFast, OP_Swap, OP_FMul, OP_PfTakeIssue1DFast, OP_FMul) \
-    X(137, 8, OP_Dup, OP_FNeg, OP_FExp, OP_FAddImm, OP_FRDiv, OP_PfTakeIssue1DFast, OP_FAdd, OP_StoreGlobal1DF32Fast) \
-    X(138, 4, OP_PfTakeIssue1DFast, OP_FAdd, OP_PfTakeIssue1DFast, OP_FAdd)
+    X(136, 8, OP_PfTakeIssue1DFast, OP_Dup, OP_FMul, OP_FAdd, OP_PfTakeIssue1DFast, OP_Dup, OP_FMul, OP_FAdd) \
+    X(137, 7, OP_Dup, OP_PfTakeIssue1DFast, OP_Swap, OP_FMul, OP_PfTakeIssue1DFast, OP_FMul, OP_StoreGlobal1DF32Fast) \
+    X(138, 6, OP_Dup, OP_PfTakeIssue1DFast, OP_Swap, OP_FMul, OP_PfTakeIssue1DFast, OP_FMul) \
+    X(139, 8, OP_Dup, OP_FNeg, OP_FExp, OP_FAddImm, OP_FRDiv, OP_PfTakeIssue1DFast, OP_FAdd, OP_StoreGlobal1DF32Fast) \
+    X(140, 4, OP_PfTakeIssue1DFast, OP_FAdd, OP_PfTakeIssue1DFast, OP_FAdd)                \
+    X(141, 4, OP_DupBroadcastW, OP_LoadStagedRows, OP_FMul, OP_Swap)     /* bmm inner step, staged rows */
 
-#define GINT_N_FUSED 25
-#define GINT_N_DISPATCH_ALL (GINT_FUSED_FIRST + GINT_N_FUSED)   /* 139 */
+#define GINT_N_FUSED 26
+#define GINT_N_DISPATCH_ALL (GINT_FUSED_FIRST + GINT_N_FUSED)   /* 142 */
 #define GINT_MAX_FUSED_LEN 8
 
 /* does the instruction read its operand word? (fused handlers fetch operands only for those that do) */
 #define GINT_OP_USES_OPERAND(op)                                                                                           \
     (((op) >= OP_LoadImm && (op) <= OP_LoadGlobal1DU8) || (op) == OP_FApprox || ((op) >= OP_LoadGlobal1DF32Indirect && (op) <= OP_DupBroadcastW) || \
-     (op) == OP_FPermW || (op) == OP_FShuf2 || (op) == OP_PfIssue1D || (op) == OP_PfTakeIssue1D || (op) == OP_PfSkip || ((op) >= OP_LoadGlobal1DF32Fast && (op) <= OP_PfTakeIssue1DFast))
+     (op) == OP_FPermW || (op) == OP_FShuf2 || (op) == OP_PfIssue1D || (op) == OP_PfTakeIssue1D || (op) == OP_PfSkip || ((op) >= OP_LoadGlobal1DF32Fast && (op) <= OP_LoadStagedRows))
 
 #endif /* GINT_FUSED_H */

@@ -464,6 +464,8 @@ struct Ctx {
     TileInfo *tiles;   // this warp's K tile descriptors (shared memory)
     int lane;
     uint32_t hidden;   // shared-memory address of slot 0, tile 0 of the warp's load staging area, plus 4 * lane
+    uint32_t rows;     // shared-memory address of this warp's staged row blocks (tile 0); tile k is rows_stride bytes further
+    uint32_t rows_stride;
 };
 
 template <int OP> struct OpInfo;
@@ -649,6 +651,18 @@ template <int K, int SLOT, int KI> __device__ __forceinline__ void take_hidden(u
                  "mov.b64 %%gs%0, {t0, t1};\n\tmov.b64 %%gs%1, {t2, t3};\n\t}" ::"n"(gs<K>(SLOT, KI, 0)), "n"(gs<K>(SLOT, KI, 1)), "r"(src) : "memory");
 }
 
+/* Staged row blocks (StageRows / LoadStagedRows). Row m of the block (lane m's row) has q = 2^lq chunks of 16 bytes; chunk r
+ * of row m is kept at chunk position m*q + (r ^ ((m >> (3 - lq)) & (q - 1))) of the copy, so that the eight lanes a 16-byte
+ * shared-memory access serves per wavefront hit eight different 16-byte bank groups, whichever chunk they ask for. */
+__device__ __forceinline__ uint32_t staged_row_position(uint32_t m, uint32_t r, uint32_t lq)
+{
+    return (m << lq) + (r ^ ((m >> (3u - lq)) & ((1u << lq) - 1u)));
+}
+template <int K, int SLOT, int KI> __device__ __forceinline__ void take_rows(uint32_t at)
+{
+    asm volatile("ld.shared.v2.b64 {%%gs%0, %%gs%1}, [%2];" ::"n"(gs<K>(SLOT, KI, 0)), "n"(gs<K>(SLOT, KI, 1)), "r"(at) : "memory");
+}
+
 template <int OP, int SP, int P, int K, int KI>
 __device__ __forceinline__ void exec_tile(const uint32_t operand, const Ctx &cx)
 {
@@ -828,7 +842,29 @@ __device__ __forceinline__ void exec_tile(const uint32_t operand, const Ctx &cx)
 template <int OP, int SP, int P, int K, int... KI>
 __device__ __forceinline__ void exec_all(const uint32_t operand, const Ctx &cx, std::integer_sequence<int, KI...>)
 {
-    if constexpr ((OP >= OP_PfTake && OP <= OP_PfSkip) || OP == OP_PfIssue1DFast || OP == OP_PfTakeIssue1DFast) {
+    if constexpr (OP == OP_StageRows) {
+        /* operand: tensor slot (bits 0..2), log2 of the 16-byte chunks per row (bits 3..4), byte offset of the block's copy
+         * in the warp's row area (bits 8..23). The 32 rows of a tile are contiguous: chunk c = 32 i + lane of the block
+         * goes to position swz(c); see staged_row_position. One commit for all tiles. */
+        const uint32_t lq = (operand >> 3) & 3u, area = (operand >> 8) & 0xFFFFu;
+        auto one = [&](int ki) {
+            const char *src = reinterpret_cast<const char *>(cx.tiles[ki].ptr[operand & 7u]) + cx.lane * 16;
+            const uint32_t dst = cx.rows + (uint32_t)ki * cx.rows_stride + area;
+            for (uint32_t i = 0; i < (1u << lq); i++) {
+                const uint32_t c = i * 32u + (uint32_t)cx.lane, m = c >> lq, r = c & ((1u << lq) - 1u);
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + staged_row_position(m, r, lq) * 16u), "l"(src + i * 512u) : "memory");
+            }
+        };
+        (one(KI), ...);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    } else if constexpr (OP == OP_LoadStagedRows) {
+        /* operand: log2 chunks per row (bits 0..1), which chunk of the lane's row (bits 2..3), area offset (bits 8..23) */
+        const uint32_t lq = operand & 3u, part = (operand >> 2) & 3u, area = (operand >> 8) & 0xFFFFu;
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncwarp();
+        const uint32_t at = cx.rows + area + staged_row_position((uint32_t)cx.lane, part, lq) * 16u;
+        (take_rows<K, SP, KI>(at + (uint32_t)KI * cx.rows_stride), ...);
+    } else if constexpr ((OP >= OP_PfTake && OP <= OP_PfSkip) || OP == OP_PfIssue1DFast || OP == OP_PfTakeIssue1DFast) {
         /* Early-issued loads. One cp.async group per load (all K tiles together). When load n is taken, the D-1 loads
          * after it are in flight, so "all but the newest D-1 groups have landed" is exactly "load n has landed"; a plain
          * PfTake belongs to the tail of the program, where fewer are in flight, and simply waits for everything. */
@@ -1123,6 +1159,10 @@ __device__ __forceinline__ void geval_direct_body(const LaunchArgs &a)
         unsigned char *stage = reinterpret_cast<unsigned char *>(tiles_s + kWarpsPerBlock * K) +
                                (size_t)warp * (hidden_slots(P) * K * 512) + lane * 4;
         cx.hidden = (uint32_t)__cvta_generic_to_shared(stage);
+        unsigned char *rows = reinterpret_cast<unsigned char *>(tiles_s + kWarpsPerBlock * K) +
+                              (size_t)kWarpsPerBlock * (hidden_slots(P) * K * 512) + (size_t)(warp * K) * a.row_area_bytes;
+        cx.rows = (uint32_t)__cvta_generic_to_shared(rows);
+        cx.rows_stride = a.row_area_bytes;
     }
 
     const uint32_t n_groups = (a.end - a.first + (uint32_t)K - 1u) / (uint32_t)K;
@@ -1151,7 +1191,9 @@ __device__ __forceinline__ void geval_indirect_body(const IndirectArgs &a)
     Ctx cx;
     cx.tiles = reinterpret_cast<TileInfo *>(mine);
     cx.lane = lane;
-    cx.hidden = 0;   // indirect mode runs programs as written (no early-issued loads)
+    cx.hidden = 0;   // indirect mode runs programs as written (no early-issued loads, no staged rows)
+    cx.rows = 0;
+    cx.rows_stride = 0;
     for (uint32_t g = blockIdx.x * kWarpsPerBlock + warp; g < a.grid_dim; g += gridDim.x * kWarpsPerBlock) {
         const IndirectEntry e = a.table[g];
         __syncwarp();  // every lane is done with the previous program's code and descriptors

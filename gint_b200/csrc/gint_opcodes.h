@@ -132,11 +132,17 @@
  * on a 16-byte boundary (given a 16-byte aligned base pointer, which is checked at every launch):
  *   LoadGlobal1DF32Fast / StoreGlobal1DF32Fast   the same access without shape, stride or mask handling
  *   PfIssue1DFast / PfTakeIssue1DFast            PfIssue1D / PfTakeIssue1D likewise: one 16-byte copy per lane
+ * and for a tensor that a program only reads through 2DW row loads, whose 32 rows per logical program are short (4, 8 or 16
+ * floats) and lie back to back in memory (one lane = one small matrix):
+ *   StageRows        copy the whole 32-row block into shared memory with fully coalesced 16-byte copies (program start)
+ *   LoadStagedRows   the row load, served from that copy
+ * (a row load by itself is a 16-byte access per lane at the row stride: 16 L1 wavefronts per warp where 4 would do)
  */
 #define GINT_INTERNAL_OPCODE_LIST(X) \
     X(PfTake, 106, 0, 1) X(PfIssue1D, 107, 0, 0) X(PfTakeIssue1D, 108, 0, 1) X(PfSkip, 109, 0, 0) \
-    X(LoadGlobal1DF32Fast, 110, 0, 1) X(StoreGlobal1DF32Fast, 111, 1, -1) X(PfIssue1DFast, 112, 0, 0) X(PfTakeIssue1DFast, 113, 0, 1)
-#define GINT_N_DISPATCH 139   /* opcodes the kernels dispatch on: the 106 of the format, the 8 above and the fused
+    X(LoadGlobal1DF32Fast, 110, 0, 1) X(StoreGlobal1DF32Fast, 111, 1, -1) X(PfIssue1DFast, 112, 0, 0) X(PfTakeIssue1DFast, 113, 0, 1) \
+    X(StageRows, 114, 0, 0) X(LoadStagedRows, 115, 0, 1)
+#define GINT_N_DISPATCH 142   /* opcodes the kernels dispatch on: the 106 of the format, the 8 above and the fused
                                  handlers of gint_fused.h */
 
 enum gint_opcode {

@@ -16,7 +16,7 @@ This module rewrites the PTX text of one kernel: after the DISPATCH marker it in
 where ``L_op`` is the label of the basic block that starts with ``GINT_TARGET D*n_ops+op`` (the default block for
 combinations without a case) and D is the stack depth after the handler the marker sits in -- programs are straight
 line, so the depth before every instruction is static and only the opcode has to be looked up at run time. Restricting
-each branch to the ~139 targets of one depth also keeps the control-flow graph ptxas has to digest small. The compare tree that follows becomes unreachable and is dropped by ptxas. The key is warp-uniform by
+each branch to the ~142 targets of one depth also keeps the control-flow graph ptxas has to digest small. The compare tree that follows becomes unreachable and is dropped by ptxas. The key is warp-uniform by
 construction (every lane of a warp interprets the same program), hence ``.uni``.
 
 The rewrite is validated structurally (exactly one DISPATCH marker, unique TARGET keys, every marker at the head of a
@@ -36,7 +36,7 @@ class PtxDispatchError(RuntimeError):
     pass
 
 
-def rewrite(ptx: str, n_keys: int, n_ops: int = 139) -> tuple[str, dict]:
+def rewrite(ptx: str, n_keys: int, n_ops: int = 142) -> tuple[str, dict]:
     """Return (rewritten PTX, stats). ``n_keys`` is the size of the dispatch key space."""
     lines = ptx.split("\n")
     # depth -1 stands for "all": the non-threaded form, one table over every (depth, opcode) key

@@ -50,7 +50,7 @@ def test_c_header_table_matches_python():
     import re
     rows = re.findall(r"X\((\w+), (\d+), (-?\d+), (-?\d+)\)", open(path).read())
     internal = [r for r in rows if int(r[1]) >= opcodes.N_OPCODES]   # the kernels' internal opcodes sit above the format's 106
-    assert all(r[0].startswith("Pf") or r[0].endswith("Fast") for r in internal)
+    assert all(r[0].startswith("Pf") or r[0].endswith("Fast") or r[0].endswith("Rows") for r in internal)
     assert sorted(int(r[1]) for r in internal) == list(range(opcodes.N_OPCODES, opcodes.N_OPCODES + len(internal)))
     rows = [r for r in rows if int(r[1]) < opcodes.N_OPCODES]
     assert len(rows) == opcodes.N_OPCODES

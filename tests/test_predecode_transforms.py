@@ -13,7 +13,7 @@ from gint_b200.host import capi
 from gint_b200.host.utils import fill_tensor_info
 from gint_b200.programs import load_records, recorded
 
-PF_TAKE, PF_ISSUE_1D, PF_TAKE_ISSUE_1D, PF_SKIP, LOAD_1D_FAST, STORE_1D_FAST, PF_ISSUE_1D_FAST, PF_TAKE_ISSUE_1D_FAST = range(106, 114)
+PF_TAKE, PF_ISSUE_1D, PF_TAKE_ISSUE_1D, PF_SKIP, LOAD_1D_FAST, STORE_1D_FAST, PF_ISSUE_1D_FAST, PF_TAKE_ISSUE_1D_FAST, STAGE_ROWS, LOAD_STAGED_ROWS = range(106, 116)
 
 
 def fused_table():
@@ -87,6 +87,10 @@ def undo(prog, table):
                PF_TAKE_ISSUE_1D_FAST: PF_TAKE_ISSUE_1D}
     # (their operand is {8 * slot in bits 26..31, byte offset of the tile in bits 0..25})
     flat = [(generic[op], ((operand & 0x03FFFFFF) // 4) << 4 | operand >> 29) if op in generic else (op, operand) for op, operand in flat]
+    # staged row blocks: the copy at the program start disappears, the row loads get their tensor slot and column back
+    # (operand of LoadStagedRows: log2 chunks per row in bits 0..1, chunk of the row in bits 2..3, slot in bits 4..6)
+    flat = [(O.LoadGlobal2DWF32, (((operand >> 2) & 3) * 4) << 4 | (operand >> 4) & 7) if op == LOAD_STAGED_ROWS else (op, operand)
+            for op, operand in flat if op != STAGE_ROWS]
     # 3. replay the ring of early-issued loads
     out, ring = [], []
     for op, operand in flat:
@@ -173,3 +177,17 @@ def test_fast_accesses_need_full_aligned_tiles():
     assert STORE_1D_FAST not in ops_for(1000) and PF_ISSUE_1D_FAST not in ops_for(1000)      # ragged last tile
     assert STORE_1D_FAST not in ops_for(1024 + 2, off=2)                                    # tile starts off a 16-byte boundary
     assert STORE_1D_FAST not in ops_for(1024, stride=2)                                     # not unit-stride
+
+
+def test_small_matrix_operands_are_staged_as_row_blocks():
+    """bmm4x4: A and B (32 matrices of 16 floats back to back per logical program) are copied to shared memory once and all
+    20 row loads read from there; a ragged batch keeps its masked row loads."""
+    table = fused_table()
+    prog = recorded("bmm4x4_b4194304")
+    got = transform(prog.bytecode, prog.tensor_infos, 1, 1)
+    members = [m for op, _ in got for m in (table[op] if op in table else [op])]
+    assert members.count(STAGE_ROWS) == 2 and members.count(LOAD_STAGED_ROWS) == 20 and O.LoadGlobal2DWF32 not in members
+    assert [op for op, _ in got[:2]] == [STAGE_ROWS, STAGE_ROWS]
+    ragged = recorded("bmm4x4_b1000")
+    members = [m for op, _ in transform(ragged.bytecode, ragged.tensor_infos, 1, 1) for m in (table[op] if op in table else [op])]
+    assert STAGE_ROWS not in members and members.count(O.LoadGlobal2DWF32) == 20
