@@ -36,10 +36,11 @@ import torch  # noqa: E402
 FALLBACK_HBM_GBS = 6650.0   # earlier measurement on this pool, used only when MEASURED_PEAKS.json is absent
 NOMINAL_HBM_GBS = 8000.0
 L2_BYTES = 126 * 1024 * 1024
-# dram__bytes_read.sum + dram__bytes_write.sum per leading unit (row / matrix) of one launch, from the ncu captures summarised
-# under profiles/ (small cases of the same kernels; traffic grows in proportion to the units). Lines written late in a
-# kernel are still in L2 when it ends, so the write part is a lower bound.
-NCU_DRAM_BYTES_PER_UNIT = {"rmsnorm": 299955968 / 8192, "bmm4x4": 172342528 / 1048576, "inv4x4": 87388928 / 1048576}
+# DRAM bytes per leading unit (row / matrix) of one launch, from the ncu captures summarised under profiles/ (small cases of
+# the same kernels; traffic grows in proportion to the units): dram__bytes_read.sum per unit as captured, plus the unit's
+# output bytes for the write side -- in the captures part of the output is still dirty in L2 when the kernel ends (89 MB
+# of 134 MB written for RMSNorm), so dram__bytes_write.sum itself understates what a launch eventually writes.
+NCU_DRAM_BYTES_PER_UNIT = {"rmsnorm": 164331264 / 8192 + 16384, "bmm4x4": 135265280 / 1048576 + 64, "inv4x4": 67534080 / 1048576 + 64}
 
 
 def measured_peak():
@@ -213,7 +214,7 @@ def run_program_bench(name: str, world: int, rank: int, steps: int, warmup: int,
     def step():
         wls[state["i"] % n_sets].run(ex, stream)
         state["i"] += 1
-    for _ in range(max(3, warmup)):
+    for _ in range(max(3, warmup, n_sets)):   # every buffer set once at least: its program is built on first use
         step()
     launches0 = ex.launches
     ms = time_device(step, steps, world)
@@ -356,7 +357,7 @@ def main():
             "roofline": {"bound": "hbm", "achieved": res["gbs"] / world, "peak": peak, "unit": "GB/s",
                          "frac": res["gbs"] / world / peak, "peak_kind": f"of {peak_kind}", "frac_of_8TBs": res["frac_of_8TBs"],
                          "traffic": (NCU_DRAM_BYTES_PER_UNIT[name] * leading) if name in NCU_DRAM_BYTES_PER_UNIT else None,
-                         "traffic_source": "ncu dram bytes per row of the 8192-row capture (profiles/) x rows of this launch",
+                         "traffic_source": "ncu dram__bytes_read per row of the 8192-row capture (profiles/) + output bytes per row, x rows of this launch",
                          "algorithmic_bytes_per_launch": res["algorithmic_bytes"] // world,
                          "kernel_ms": res["ms_per_step"] / res["launches_per_step"]},
             "programs": {k: {kk: vv for kk, vv in v.items() if kk not in ("launches",)} for k, v in programs.items()},

@@ -589,13 +589,16 @@ struct Geometry {
     uint32_t grid;
 };
 
+/* the ring of early-issued loads exists only in streams that have such loads (n_early is zeroed in the launch's view of
+ * the program when the plain stream runs) */
+uint32_t ring_bytes_per_tile(const Program *p) { return p->n_early > 0 ? (uint32_t)gint::hidden_slots(p->st.pool_size) * 512u : 0u; }
+
 uint32_t direct_smem(const Program *p, int K, uint32_t *code_smem)
 {
     const uint32_t cs = (p->n_slots * 8u + 127u) & ~127u;
     *code_smem = cs;
     return cs + gint::kTensorInfoSmemBytes + (uint32_t)(gint::kWarpsPerBlock * K) * (uint32_t)sizeof(gint::TileInfo) +
-           (uint32_t)(gint::kWarpsPerBlock * K * gint::hidden_slots(p->st.pool_size) * 512) +
-           (uint32_t)(gint::kWarpsPerBlock * K) * p->row_area_bytes;
+           (uint32_t)(gint::kWarpsPerBlock * K) * (ring_bytes_per_tile(p) + p->row_area_bytes);
 }
 
 int plan_direct(gint_ctx *ctx, const Program *p, uint32_t count, Geometry *g)
@@ -670,7 +673,7 @@ int launch_direct(gint_ctx *ctx, uint64_t handle, const uint64_t *base_ptrs, int
         if (((p->fast_slots >> t) & 1u) && (base_ptrs[t] & 15u) != 0) early = false;   // fast accesses need aligned bases
     Program view = *p;   // geometry depends on the stream length
     if (early) view.n_slots = p->early_slots;
-    else view.row_area_bytes = 0;
+    else { view.row_area_bytes = 0; view.n_early = 0; }
     Geometry g;
     {
         /* the calling thread's last plan is reused while nothing it depends on changes: saves the occupancy query */
@@ -695,6 +698,8 @@ int launch_direct(gint_ctx *ctx, uint64_t handle, const uint64_t *base_ptrs, int
     a.prefetch_mask = ctx->opt_prefetch ? p->prefetch_mask : 0u;
     a.zero = 0;
     a.row_area_bytes = view.row_area_bytes;
+    a.ring_bytes = ring_bytes_per_tile(&view);
+    a.reserved = 0;
     for (int t = 0; t < GINT_MAX_TENSORS; t++) a.fp[t] = p->fp[t];
     a.ti = p->ti;
     for (int i = 0; i < n_tensors; i++) a.ti.base_ptr[i] = (int64_t)base_ptrs[i];

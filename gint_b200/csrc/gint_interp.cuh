@@ -1155,13 +1155,10 @@ __device__ __forceinline__ void geval_direct_body(const LaunchArgs &a)
     Ctx cx;
     cx.tiles = tiles_s + warp * K;
     cx.lane = lane;
-    {   // load staging area: after the tile descriptors, hidden_slots(P) * K * 512 bytes per warp
-        unsigned char *stage = reinterpret_cast<unsigned char *>(tiles_s + kWarpsPerBlock * K) +
-                               (size_t)warp * (hidden_slots(P) * K * 512) + lane * 4;
-        cx.hidden = (uint32_t)__cvta_generic_to_shared(stage);
-        unsigned char *rows = reinterpret_cast<unsigned char *>(tiles_s + kWarpsPerBlock * K) +
-                              (size_t)kWarpsPerBlock * (hidden_slots(P) * K * 512) + (size_t)(warp * K) * a.row_area_bytes;
-        cx.rows = (uint32_t)__cvta_generic_to_shared(rows);
+    {   // after the tile descriptors: the ring of early-issued loads (ring_bytes per tile), then the staged row blocks
+        unsigned char *after = reinterpret_cast<unsigned char *>(tiles_s + kWarpsPerBlock * K);
+        cx.hidden = (uint32_t)__cvta_generic_to_shared(after + (size_t)(warp * K) * a.ring_bytes + lane * 4);
+        cx.rows = (uint32_t)__cvta_generic_to_shared(after + (size_t)(kWarpsPerBlock * K) * a.ring_bytes + (size_t)(warp * K) * a.row_area_bytes);
         cx.rows_stride = a.row_area_bytes;
     }
 

@@ -57,6 +57,8 @@ struct LaunchArgs {
     uint32_t prefetch_mask;   // bit t set: prefetch tensor t's footprint into L2 when a tile's descriptors are decoded
     uint32_t zero;            // always 0; a zero the assembler cannot see (fma_barrier in gint_interp.cuh)
     uint32_t row_area_bytes;  // shared-memory bytes per tile for staged row blocks (StageRows), 0 if the program has none
+    uint32_t ring_bytes;      // shared-memory bytes per tile for the ring of early-issued loads, 0 if the stream has none
+    uint32_t reserved;
     Footprint fp[GINT_MAX_TENSORS];
     gint_tensor_info ti;      // descriptor block, base pointers patched per call: travels as a kernel parameter
 };

@@ -373,6 +373,26 @@ def fused_idioms(a, b, c, o0, o1, o2, REGW, WARP):
     halt()
 
 
+STATIC_FPERM = [(0, 0, 0, 0), (2, 3, 0, 1), (1, 0, 3, 2), (0, 0, 1, 1), (1, 1, 1, 1), (2, 1, 2, 1), (1, 1, 2, 2), (2, 2, 2, 2),
+                (3, 3, 2, 2), (3, 0, 3, 0), (0, 3, 0, 3), (0, 2, 1, 3), (3, 3, 0, 0), (3, 3, 3, 3), (3, 2, 1, 0), (1, 3, 0, 2)]
+STATIC_FSHUF2 = [(0, 1, 0, 1), (3, 1, 3, 1), (2, 0, 2, 0), (0, 2, 0, 2), (1, 3, 1, 3), (2, 3, 2, 3), (3, 3, 0, 1), (0, 0, 0, 0)]
+
+
+@bytecode
+def permute_selectors(a, b, out, REGW, WARP):
+    """FPermW / FShuf2 with the selectors that have handlers of their own (the first 14 / 6 of each list) and with two that do
+    not; every result is scaled by a different constant and accumulated, so a wrong lane shows in the sum."""
+    N, = a.shape
+    ab, bb, ob = [make_block_1d(t, N, 1, cdiv(N, 128), 128) for t in (a, b, out)]
+    fpush(0.0)
+    for i, sel in enumerate(STATIC_FPERM):
+        fldg_1d(0, ab); fperm_w(*sel); fmulimm(float(i + 1)); fadd()
+    for i, sel in enumerate(STATIC_FSHUF2):
+        fldg_1d(0, ab); fldg_1d(0, bb); fshuf2(*sel); fmulimm(float(2 * i + 3)); fadd()
+    fstg_1d(0, ob)
+    halt()
+
+
 # ------------------------------------------------------------------------------------------------ case list
 
 def _z(*shape, dtype=torch.float32):
@@ -463,6 +483,11 @@ def build_cases() -> list[Case]:
         def mkw(g, n=n):
             return [torch.randn(n, generator=g)] + [_z(n) for _ in range(3)]
         cases.append(Case(f"width_ops_n{n}", width_ops, mkw, cdiv(n, 128), [1, 2, 3]))
+
+    for n in [128, 1000]:
+        def mkp(g, n=n):
+            return [torch.randn(n, generator=g), torch.randn(n, generator=g), _z(n)]
+        cases.append(Case(f"permute_selectors_n{n}", permute_selectors, mkp, cdiv(n, 128), [2]))
 
     for n in [1, 128, 1000]:
         def mkf(g, n=n):
