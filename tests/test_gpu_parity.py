@@ -144,6 +144,28 @@ def test_named_program_full_size(name):
         assert bits_equal(wl.tensors["c"][:1000], small.tensors["c"])
 
 
+@pytest.mark.parametrize("name,leading,inner", [("add", 131072, 1), ("rmsnorm", 2048, 4096), ("bmm4x4", 524288, 16), ("inv4x4", 524288, 16),
+                                                ("graph", 8192, 1024)])
+def test_transformed_streams_give_the_same_bits_as_the_plain_stream(name, leading, inner):
+    """Early-issued loads, fast accesses, staged row blocks and fused handlers only reschedule the program: at sizes where
+    all of them apply (full tiles, aligned, 32 matrices per tile), the outputs equal those of the untransformed stream."""
+    ex = get_executor()
+    outs = []
+    try:
+        for early, fuse in ((1, 1), (0, 0)):
+            ex.set_option("early_issue", early)
+            ex.set_option("fuse", fuse)
+            wl = make_workload(name, leading, inner, device="cuda")      # a fresh program object: built with these options
+            wl.run(ex, torch.cuda.current_stream().cuda_stream)
+            torch.cuda.synchronize()
+            outs.append({r: wl.tensors[r].clone() for r in wl.outputs})
+    finally:
+        ex.set_option("early_issue", 1)
+        ex.set_option("fuse", 1)
+    for r in outs[0]:
+        assert bits_equal(outs[0][r], outs[1][r]), mismatch_report(outs[0][r], outs[1][r])
+
+
 # ------------------------------------------------------------------------------------------------ random programs
 
 def _fuzz_inputs(prog: FuzzProgram, seed: int):
