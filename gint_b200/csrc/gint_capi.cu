@@ -1022,6 +1022,24 @@ int gint_execute_range(gint_ctx *ctx, uint64_t handle, const uint64_t *base_ptrs
     return launch_direct(ctx, handle, base_ptrs, n_tensors, first, count, cuda_stream);
 }
 
+int gint_execute_plan(gint_ctx *ctx, const gint_plan_step *steps, int n_steps, void *cuda_stream)
+{
+    if (!ctx || (!steps && n_steps > 0) || n_steps < 0) return fail(ctx, GINT_ERR_INVALID_ARGUMENT, "null or negative plan");
+    for (int i = 0; i < n_steps; i++) {
+        const gint_plan_step &st = steps[i];
+        if (st.grid_dim == 0) continue;
+        if (st.n_tensors < 0 || st.n_tensors > GINT_MAX_TENSORS) return fail(ctx, GINT_ERR_INVALID_ARGUMENT, "plan step: tensor count out of range");
+        const int rc = launch_direct(ctx, st.handle, st.base_ptrs, st.n_tensors, 0u, st.grid_dim, cuda_stream);
+        if (rc != GINT_OK) {
+            char msg[320];
+            snprintf(msg, sizeof msg, "plan step %d of %d: %s", i, n_steps, ctx->last_error.c_str());
+            ctx->last_error = msg;
+            return rc;
+        }
+    }
+    return GINT_OK;
+}
+
 int gint_execute_indirect(gint_ctx *ctx, const uint64_t *handles, int n_programs, const uint64_t *base_ptrs, const int32_t *indices,
                           uint32_t grid_dim, void *cuda_stream)
 {

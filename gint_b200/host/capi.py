@@ -60,6 +60,11 @@ GINT_ERR_NO_DEVICE = -9
 GINT_ERR_TOO_LARGE = -10
 GINT_ERR_OUT_OF_MEMORY = -11
 
+class PlanStepC(ctypes.Structure):
+    """gint_plan_step"""
+    _fields_ = [("handle", c_uint64), ("base_ptrs", c_uint64 * 8), ("n_tensors", c_int32), ("grid_dim", c_uint32)]
+
+
 # every symbol include/gint_b200.h declares: name -> (restype, argtypes)
 SIGNATURES = {
     "gint_version": (c_int, []),
@@ -77,6 +82,7 @@ SIGNATURES = {
     "gint_program_launch_info": (c_int, [c_void_p, c_uint64, c_uint32, POINTER(LaunchInfoC)]),
     "gint_execute": (c_int, [c_void_p, c_uint64, POINTER(c_uint64), c_int, c_uint32, c_void_p]),
     "gint_execute_range": (c_int, [c_void_p, c_uint64, POINTER(c_uint64), c_int, c_uint32, c_uint32, c_void_p]),
+    "gint_execute_plan": (c_int, [c_void_p, POINTER(PlanStepC), c_int, c_void_p]),
     "gint_execute_indirect": (c_int, [c_void_p, POINTER(c_uint64), c_int, POINTER(c_uint64), POINTER(c_int32), c_uint32, c_void_p]),
     "gint_execute_indirect_static": (c_int, [c_void_p, POINTER(c_uint64), c_int, POINTER(c_uint64), POINTER(c_int32), c_uint32, c_void_p]),
     "gint_set_option": (c_int, [c_void_p, c_char_p, c_int]),

@@ -310,6 +310,27 @@ class B200Executor(BaseExecutor):
             self._check(ctx, rc, "gint_execute_indirect_static" if static_tables else "gint_execute_indirect")
         self.launches += 1
 
+    def build_plan(self, steps: Sequence[tuple]) -> "Plan":
+        """Lower a list of ``(program, args, grid_dim)`` steps -- what a compiled graph is after the conductor has run --
+        into one reusable ``Plan``: programs are built (or found in their caches) now, the tensor addresses are written
+        into a C array, and ``Plan.run(cuda_stream)`` launches every step with a single library call
+        (``gint_execute_plan``). Replaces the Python loop of the conductor's ``execute`` closure
+        (``gint/conductor/compiler.py:1442-1485``). ``Plan.set_arg`` re-points one argument of one step (fresh
+        input / output tensors per call)."""
+        plan_steps = (capi.PlanStepC * len(steps))()
+        ctx = None
+        slots = []
+        for i, (program, args, grid_dim) in enumerate(steps):
+            conv = [_convert_arg(a) for a in args]
+            ctx, line = self._cacheline(program, conv, {})
+            plan_steps[i].handle = line.handle
+            plan_steps[i].n_tensors = line.n
+            plan_steps[i].grid_dim = grid_dim
+            for j, a in enumerate(line.indices):
+                plan_steps[i].base_ptrs[j] = conv[a].base_ptr
+            slots.append(list(line.indices))
+        return Plan(self, ctx, plan_steps, slots)
+
     def execute_streamed(self, program: BaseExecutableProgram, args: Sequence[torch.Tensor], grid_dim: int,
                          host_inputs: dict, host_outputs: dict, n_chunks: int = 16, **extra_kwargs):
         """Run ``program`` on data that lives in HOST memory, overlapping the transfers with the kernels.
@@ -441,6 +462,32 @@ class B200Executor(BaseExecutor):
         for ctx in self._ctxs.values():
             self._lib.gint_destroy(ctx)
         self._ctxs.clear()
+
+
+class Plan:
+    """A lowered list of launches (see ``B200Executor.build_plan``). Valid on the device it was built on, for as long as
+    the programs live; the tensors whose addresses it holds must outlive every ``run``."""
+
+    def __init__(self, owner: "B200Executor", ctx, steps, slots) -> None:
+        self._owner, self._ctx, self._steps, self._slots = owner, ctx, steps, slots
+
+    def __len__(self) -> int:
+        return len(self._steps)
+
+    def set_arg(self, step: int, arg_index: int, tensor) -> None:
+        """Point argument ``arg_index`` of step ``step`` at another tensor of the same shape and strides."""
+        ptr = _convert_arg(tensor).base_ptr
+        for j, a in enumerate(self._slots[step]):
+            if a == arg_index:
+                self._steps[step].base_ptrs[j] = ptr
+
+    def run(self, cuda_stream: int = 0) -> None:
+        if len(self._steps) == 0:
+            return
+        rc = self._owner._lib.gint_execute_plan(self._ctx, self._steps, len(self._steps), cuda_stream)
+        if rc != 0:
+            self._owner._check(self._ctx, rc, "gint_execute_plan")
+        self._owner.launches += sum(1 for s in self._steps if s.grid_dim)
 
 
 executor: Optional[BaseExecutor] = None

@@ -52,6 +52,10 @@ class Workload:
         for st in self.steps:
             executor.execute(st.program, [_convert_arg(self.tensors[r]) for r in st.roles], st.grid_dim, cuda_stream=stream)
 
+    def plan(self, executor):
+        """The bytecode steps as one reusable launch plan (``B200Executor.build_plan``); ``pre`` stays with the caller."""
+        return executor.build_plan([(st.program, [self.tensors[r] for r in st.roles], st.grid_dim) for st in self.steps])
+
     def launches_per_run(self) -> int:
         return len(self.steps)
 

@@ -150,6 +150,22 @@ int gint_execute(gint_ctx *ctx, uint64_t handle, const uint64_t *base_ptrs, int 
 int gint_execute_range(gint_ctx *ctx, uint64_t handle, const uint64_t *base_ptrs, int n_tensors, uint32_t first,
                        uint32_t count, void *cuda_stream);
 
+/* One step of a plan: a program, the device addresses of its tensors and its logical grid. */
+typedef struct gint_plan_step {
+    uint64_t handle;
+    uint64_t base_ptrs[GINT_MAX_TENSORS];
+    int32_t n_tensors;
+    uint32_t grid_dim;
+} gint_plan_step;
+
+/* Launch a list of programs back to back on one stream with a single call: what a compiled graph is once it has been
+ * lowered -- the conductor's `execute` closure walks such a list in Python, one executor call and one 608-byte upload
+ * per subgraph (gint/conductor/compiler.py:1442-1485; the reference measured 36-90 us of CPU dispatch per call against a
+ * 62 us kernel, docs/conductor.md:94). Steps run in order (stream order); the call stops at the first step that fails,
+ * returns its status and names the step in gint_last_error. Same properties as gint_execute: no allocation, no copy,
+ * legal during stream capture. A step with grid_dim 0 is skipped. */
+int gint_execute_plan(gint_ctx *ctx, const gint_plan_step *steps, int n_steps, void *cuda_stream);
+
 /* One launch in which logical program i runs programs[indices[i]] with that program's own tensors.
  * base_ptrs holds n_programs rows of GINT_MAX_TENSORS addresses. Replaces CudaExecutor.execute_indirect
  * (gint/host/cuda/executor_impl.py:135-201). Uses context-owned scratch for the per-warp tables; may grow

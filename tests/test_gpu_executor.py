@@ -227,6 +227,41 @@ def test_execute_streamed_matches_execute(name, leading, inner, chunks):
             assert bits_equal(outs[i], want[r]), mismatch_report(outs[i], want[r])
 
 
+def test_plan_runs_all_steps_with_one_call():
+    """The conductor graph's two bytecode programs as a plan: same bits as one execute() per step; set_arg re-points an
+    output; a bad step is reported with its index."""
+    from gint_b200.workloads import make_workload
+    ex = get_executor()
+    wl = make_workload("graph", 8192, 1024, device="cuda")
+    wl.run(ex)
+    torch.cuda.synchronize()
+    want = {r: wl.tensors[r].clone() for r in wl.outputs}
+    for r in wl.outputs:
+        wl.tensors[r].zero_()
+    plan = wl.plan(ex)
+    assert len(plan) == len(wl.steps) == 2
+    wl.pre(wl.tensors)
+    launches = ex.launches
+    plan.run(torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    assert ex.launches - launches == 2
+    for r in wl.outputs:
+        assert bits_equal(wl.tensors[r], want[r])
+    # re-point the last step's output at another buffer
+    last = wl.steps[-1]
+    out_role = "s"   # the row sums: written by the last step only
+    other = torch.zeros_like(wl.tensors[out_role])
+    plan.set_arg(len(wl.steps) - 1, last.roles.index(out_role), other)
+    plan.run(torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    assert bits_equal(other, want[out_role])
+    # a step whose handle is unknown fails with its position in the message, after the steps before it were queued
+    plan._steps[1].handle = 0xDEAD
+    with pytest.raises(capi.GintError, match="plan step 1 of 2"):
+        plan.run()
+    torch.cuda.synchronize()
+
+
 def test_launch_info_reports_geometry():
     from gint_b200.workloads import make_workload
     ex = get_executor()
