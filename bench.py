@@ -115,11 +115,14 @@ def dist_setup(n_gpus: int):
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         os.environ.setdefault("MASTER_PORT", "29511")
         torch.cuda.set_device(local)
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        # the data path has no collective: the process group only carries the barrier and the max-over-ranks of the timing,
+        # so the CPU backend is enough (and nothing but the JSON line reaches stdout)
+        dist.init_process_group("gloo")
     return rank, world, local
 
 
 def barrier(world: int):
+    torch.cuda.synchronize()
     if world > 1:
         import torch.distributed as dist
         dist.barrier()
@@ -130,7 +133,7 @@ def max_over_ranks(value: float, world: int) -> float:
     if world == 1:
         return value
     import torch.distributed as dist
-    t = torch.tensor([value], dtype=torch.float64, device="cuda")
+    t = torch.tensor([value], dtype=torch.float64)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     return float(t.item())
 
