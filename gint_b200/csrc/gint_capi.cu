@@ -477,7 +477,7 @@ struct Program {
     uint8_t alias_slots[GINT_MAX_TENSORS] = {};
     uint32_t fast_slots = 0;   // tensor slots whose base pointer must be 16-byte aligned for the early-issue stream
     bool prefer_narrow = false; // one tile per warp unless told otherwise (see plan_direct)
-    bool rereads = false;       // some tile is loaded more than once: fewer logical programs in flight keep it in L2
+    uint32_t reread_bytes = 0;  // bytes of the 1-D tiles a logical program loads more than once (0: none)
     uint64_t uid = 0;           // unique per created program (a handle slot may be reused)
     uint32_t row_area_bytes = 0; // shared memory per tile for staged row blocks (early-issue stream only)
     uint64_t extent[GINT_MAX_TENSORS] = {};
@@ -630,8 +630,9 @@ int plan_direct(gint_ctx *ctx, const Program *p, uint32_t count, Geometry *g)
         if (e != cudaSuccess || bps < 1) { cudaGetLastError(); continue; }
         /* A program that reads a tile twice (a reduction pass, then a second pass over the same row) finds it in L2 the
          * second time only if the rows in flight, with their write-allocated outputs, fit there: measured on RMSNorm
-         * rows of 16 KB, 6 blocks per SM beat 8 (121 us vs 126 us), fewer lose to exposed latency. */
-        if (p->rereads && bps > 6) bps = 6;
+         * rows of 16 KB, 6 blocks per SM (57 MB of rows in flight) beat 8 (121 us vs 126 us), fewer lose to exposed
+         * latency. Rows of 4 KB (the conductor graph) stay below that bound at full occupancy. */
+        while (bps > 4 && (uint64_t)p->reread_bytes * (uint64_t)(K * gint::kWarpsPerBlock) * (uint64_t)ctx->num_sms * (uint64_t)bps > 60000000ull) bps--;
         c.blocks_per_sm = bps;
         const uint64_t groups = ((uint64_t)count + (uint64_t)K - 1) / (uint64_t)K;
         uint64_t blocks_needed = (groups + gint::kWarpsPerBlock - 1) / gint::kWarpsPerBlock;
@@ -935,13 +936,16 @@ int gint_program_create(gint_ctx *ctx, const int32_t *code, int n_words, const g
             if (!writes_tensor(in.op)) n_loads++;
         }
         {
-            std::vector<uint32_t> seen;
+            std::vector<uint32_t> seen, again;
             for (const Insn &in : prog) {
                 if (in.op != OP_LoadGlobal1DF32) continue;   // row passes; the 4x4 programs' repeated row loads are L1 hits
-                for (uint32_t s : seen)
-                    if (s == in.operand) p->rereads = true;
-                seen.push_back(in.operand);
+                bool known = false, counted = false;
+                for (uint32_t s : seen) known = known || s == in.operand;
+                for (uint32_t s : again) counted = counted || s == in.operand;
+                if (known && !counted) again.push_back(in.operand);
+                if (!known) seen.push_back(in.operand);
             }
+            p->reread_bytes = (uint32_t)again.size() * 512u;
         }
         const int n_insns = (int)prog.size(), n_direct = n_loads - (usable ? ei.n_early + n_staged_loads : 0);
         p->prefer_narrow = 5 * n_mem >= 2 * n_insns || 5 * n_direct >= n_insns;
