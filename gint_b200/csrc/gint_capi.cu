@@ -218,6 +218,20 @@ bool writes_tensor(int op)
  *     time (launch_direct); on any overlap the untransformed stream runs instead.
  * Also folded here: a load that immediately repeats the previous instruction's load becomes Dup.
  */
+/* Ring depth for a program: the deep ring pays for programs that stream long rows -- at least 48 1-D loads and at least 2
+ * of 5 instructions accessing memory (measured on RMSNorm rows of 4096: 110 us with 8 slots at 5 blocks per SM against
+ * 121 us with 4 slots at 6) -- and costs the others occupancy through its shared memory (the conductor graph's 1024-wide
+ * rows, two tiles per warp: 344 us with 8 slots against 332 us with 4). */
+int choose_ring_slots(const std::vector<Insn> &prog)
+{
+    int n_loads = 0, n_mem = 0;
+    for (const Insn &in : prog) {
+        n_loads += in.op == OP_LoadGlobal1DF32;
+        n_mem += is_tensor_op(in.op) && in.op != OP_AdvanceBlock2D && in.op != OP_AdvanceBase;
+    }
+    return n_loads >= 48 && 5 * n_mem >= 2 * (int)prog.size() ? gint::kRingSlotsDeep : gint::kRingSlotsShallow;
+}
+
 struct EarlyIssue {
     std::vector<Insn> prog;
     uint8_t alias_slots[GINT_MAX_TENSORS] = {};   // bit b of [a]: loads of slot a were moved across stores to slot b
@@ -479,6 +493,7 @@ struct Program {
     bool prefer_narrow = false; // one tile per warp unless told otherwise (see plan_direct)
     uint32_t reread_bytes = 0;  // bytes of the 1-D tiles a logical program loads more than once (0: none)
     uint64_t uid = 0;           // unique per created program (a handle slot may be reused)
+    int ring_slots = gint::kRingSlotsShallow;   // depth of the ring of early-issued loads (early-issue stream)
     uint32_t row_area_bytes = 0; // shared memory per tile for staged row blocks (early-issue stream only)
     uint64_t extent[GINT_MAX_TENSORS] = {};
 };
@@ -591,7 +606,7 @@ struct Geometry {
 
 /* the ring of early-issued loads exists only in streams that have such loads (n_early is zeroed in the launch's view of
  * the program when the plain stream runs) */
-uint32_t ring_bytes_per_tile(const Program *p) { return p->n_early > 0 ? (uint32_t)gint::hidden_slots(p->st.pool_size) * 512u : 0u; }
+uint32_t ring_bytes_per_tile(const Program *p) { return p->n_early > 0 ? (uint32_t)p->ring_slots * 512u : 0u; }
 
 uint32_t direct_smem(const Program *p, int K, uint32_t *code_smem)
 {
@@ -630,9 +645,9 @@ int plan_direct(gint_ctx *ctx, const Program *p, uint32_t count, Geometry *g)
         if (e != cudaSuccess || bps < 1) { cudaGetLastError(); continue; }
         /* A program that reads a tile twice (a reduction pass, then a second pass over the same row) finds it in L2 the
          * second time only if the rows in flight, with their write-allocated outputs, fit there: measured on RMSNorm
-         * rows of 16 KB, 6 blocks per SM (57 MB of rows in flight) beat 8 (121 us vs 126 us), fewer lose to exposed
-         * latency. Rows of 4 KB (the conductor graph) stay below that bound at full occupancy. */
-        while (bps > 4 && (uint64_t)p->reread_bytes * (uint64_t)(K * gint::kWarpsPerBlock) * (uint64_t)ctx->num_sms * (uint64_t)bps > 60000000ull) bps--;
+         * rows of 16 KB with the 8-slot ring, 5 blocks per SM (47 MB of rows in flight) beat 6 (110 us vs 118 us); fewer
+         * lose to exposed latency. Rows of 4 KB (the conductor graph) stay below that bound at full occupancy. */
+        while (bps > 4 && (uint64_t)p->reread_bytes * (uint64_t)(K * gint::kWarpsPerBlock) * (uint64_t)ctx->num_sms * (uint64_t)bps > 50000000ull) bps--;
         c.blocks_per_sm = bps;
         const uint64_t groups = ((uint64_t)count + (uint64_t)K - 1) / (uint64_t)K;
         uint64_t blocks_needed = (groups + gint::kWarpsPerBlock - 1) / gint::kWarpsPerBlock;
@@ -904,7 +919,8 @@ int gint_program_create(gint_ctx *ctx, const int32_t *code, int n_words, const g
         std::vector<Insn> prog;
         normalise(code, n_words, n_tensors, &prog);
         EarlyIssue ei;
-        early_issue_transform(prog, gint::hidden_slots(p->st.pool_size), &ei);
+        p->ring_slots = choose_ring_slots(prog);
+        early_issue_transform(prog, p->ring_slots, &ei);
         uint32_t row_area = 0, staged = 0;
         int n_staged_loads = 0;
         if (ei.n_early == 0) {   // (a program with a ring of early-issued loads keeps its cp.async groups to itself)
@@ -1214,7 +1230,7 @@ int gint_debug_transform(const int32_t *code, int n_words, const gint_tensor_inf
         gint_bytecode_stats st;
         analyze(code, n_words, &st);
         EarlyIssue ei;
-        early_issue_transform(prog, gint::hidden_slots(st.pool_size), &ei);
+        early_issue_transform(prog, choose_ring_slots(prog), &ei);
         prog = ei.prog;
         if (ti) {
             gint_tensor_info t0 = *ti;

@@ -375,7 +375,7 @@ __device__ __forceinline__ void decode_tiles(const gint_tensor_info *__restrict_
  * every path (which ptxas does not coalesce across the jump table) cost more than the handlers themselves.
  */
 
-template <int P, int K, int D> __device__ __forceinline__ void pool_declare()
+template <int P, int K> __device__ __forceinline__ void pool_declare()
 {
     asm volatile(".reg .b64 %%gs<%0>;" ::"n"(2 * P * K));
 }
@@ -464,6 +464,7 @@ struct Ctx {
     TileInfo *tiles;   // this warp's K tile descriptors (shared memory)
     int lane;
     uint32_t hidden;   // shared-memory address of slot 0, tile 0 of the warp's load staging area, plus 4 * lane
+    uint32_t ring_mask; // bytes of the warp's ring of early-issued loads (4 or 8 slots of K x 512 bytes) minus 1
     uint32_t rows;     // shared-memory address of this warp's staged row blocks (tile 0); tile k is rows_stride bytes further
     uint32_t rows_stride;
 };
@@ -868,13 +869,17 @@ __device__ __forceinline__ void exec_all(const uint32_t operand, const Ctx &cx, 
         /* Early-issued loads. One cp.async group per load (all K tiles together). When load n is taken, the D-1 loads
          * after it are in flight, so "all but the newest D-1 groups have landed" is exactly "load n has landed"; a plain
          * PfTake belongs to the tail of the program, where fewer are in flight, and simply waits for everything. */
-        constexpr int D = hidden_slots(P);
         constexpr bool take = OP == OP_PfTake || OP == OP_PfTakeIssue1D || OP == OP_PfTakeIssue1DFast;
         uint32_t ring;
         asm volatile("mov.b32 %0, %%gring;" : "=r"(ring));
         const uint32_t slot = cx.hidden + ring;
+        /* the ring has D = 4 or 8 slots, chosen per program by the host (long rows gain from the deeper one); the wait
+         * count is an immediate of the instruction, hence the (warp-uniform) branch */
         if constexpr (OP == OP_PfTake) asm volatile("cp.async.wait_group 0;" ::: "memory");
-        else if constexpr (take) asm volatile("cp.async.wait_group %0;" ::"n"(D - 1) : "memory");
+        else if constexpr (take) {
+            if (cx.ring_mask & (uint32_t)(K * 2048)) asm volatile("cp.async.wait_group 7;" ::: "memory");
+            else asm volatile("cp.async.wait_group 3;" ::: "memory");
+        }
         if constexpr (take) {
             __syncwarp();   // the group has landed for every lane: make the other lanes' copies visible to this one
             (take_hidden<K, SP, KI>(slot), ...);
@@ -882,8 +887,8 @@ __device__ __forceinline__ void exec_all(const uint32_t operand, const Ctx &cx, 
         if constexpr (OP == OP_PfIssue1D || OP == OP_PfTakeIssue1D) (tile_issue<K, KI>(cx.tiles + KI, operand, cx, slot), ...);
         if constexpr (OP == OP_PfIssue1DFast || OP == OP_PfTakeIssue1DFast) (tile_issue_fast<K, KI>(cx.tiles + KI, operand, cx, slot), ...);
         if constexpr (OP != OP_PfTake && OP != OP_PfSkip) asm volatile("cp.async.commit_group;" ::: "memory");
-        if constexpr (OP == OP_PfSkip) asm volatile("mad.lo.u32 %%gring, %0, %1, %%gring;\n\tand.b32 %%gring, %%gring, %2;" ::"r"(operand), "n"(K * 512), "n"(D * K * 512 - 1));
-        else asm volatile("add.u32 %%gring, %%gring, %0;\n\tand.b32 %%gring, %%gring, %1;" ::"n"(K * 512), "n"(D * K * 512 - 1));
+        if constexpr (OP == OP_PfSkip) asm volatile("mad.lo.u32 %%gring, %0, %1, %%gring;\n\tand.b32 %%gring, %%gring, %2;" ::"r"(operand), "n"(K * 512), "r"(cx.ring_mask));
+        else asm volatile("add.u32 %%gring, %%gring, %0;\n\tand.b32 %%gring, %%gring, %1;" ::"n"(K * 512), "r"(cx.ring_mask));
     } else {
         if constexpr (OP == OP_AdvanceBlock2D || OP == OP_AdvanceBase) __syncwarp();
         (exec_tile<OP, SP, P, K, KI>(operand, cx), ...);
@@ -1136,7 +1141,7 @@ template <int P, int K>
 __device__ __forceinline__ void geval_direct_body(const LaunchArgs &a)
 {
     extern __shared__ __align__(16) unsigned char smem[];
-    pool_declare<P, K, hidden_slots(P)>();
+    pool_declare<P, K>();
     state_declare<true>();
     asm volatile("mov.b64 %%gzero, %0;" ::"l"((u64)a.zero));
     uint2 *code_s = reinterpret_cast<uint2 *>(smem);
@@ -1160,6 +1165,7 @@ __device__ __forceinline__ void geval_direct_body(const LaunchArgs &a)
         cx.hidden = (uint32_t)__cvta_generic_to_shared(after + (size_t)(warp * K) * a.ring_bytes + lane * 4);
         cx.rows = (uint32_t)__cvta_generic_to_shared(after + (size_t)(kWarpsPerBlock * K) * a.ring_bytes + (size_t)(warp * K) * a.row_area_bytes);
         cx.rows_stride = a.row_area_bytes;
+        cx.ring_mask = (uint32_t)K * a.ring_bytes - 1u;
     }
 
     const uint32_t n_groups = (a.end - a.first + (uint32_t)K - 1u) / (uint32_t)K;
@@ -1178,7 +1184,7 @@ template <int P>
 __device__ __forceinline__ void geval_indirect_body(const IndirectArgs &a)
 {
     extern __shared__ __align__(16) unsigned char smem[];
-    pool_declare<P, 1, hidden_slots(P)>();
+    pool_declare<P, 1>();
     state_declare<true>();
     asm volatile("mov.b64 %%gzero, %0;" ::"l"((u64)a.reserved));
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -1191,6 +1197,7 @@ __device__ __forceinline__ void geval_indirect_body(const IndirectArgs &a)
     cx.hidden = 0;   // indirect mode runs programs as written (no early-issued loads, no staged rows)
     cx.rows = 0;
     cx.rows_stride = 0;
+    cx.ring_mask = 0;
     for (uint32_t g = blockIdx.x * kWarpsPerBlock + warp; g < a.grid_dim; g += gridDim.x * kWarpsPerBlock) {
         const IndirectEntry e = a.table[g];
         __syncwarp();  // every lane is done with the previous program's code and descriptors

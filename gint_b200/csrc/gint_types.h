@@ -18,8 +18,9 @@ constexpr int kThreadsPerBlock = kWarpsPerBlock * 32;
 constexpr int kTensorInfoSmemBytes = 640;  // 608-byte descriptor block, padded to a 128-byte multiple
 constexpr int kNumKeys = (GINT_MAX_STACK + 1) * GINT_N_DISPATCH;
 
-/* Hidden load slots per kernel geometry: how many tile loads per logical program may be in flight ahead of their use. */
-__host__ __device__ constexpr int hidden_slots(int P) { (void)P; return 4; }
+/* Slots of the ring of early-issued loads: how many tile loads per logical program are in flight ahead of their use. The
+ * host chooses per program: 8 for programs that stream long rows (many loads, mostly memory instructions), 4 otherwise. */
+constexpr int kRingSlotsShallow = 4, kRingSlotsDeep = 8;
 
 /* Minimum resident blocks per SM requested from the compiler (caps registers per thread): the pool itself takes 4*P*K
  * registers; addresses and interpreter state take about 40 more. */
