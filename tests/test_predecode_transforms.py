@@ -157,6 +157,10 @@ def test_named_programs_get_the_expected_shape():
     members = [m for op, _ in both for m in (table[op] if op in table else [op])]
     assert PF_TAKE_ISSUE_1D not in members and PF_ISSUE_1D not in members and O.StoreGlobal1DF32 not in members
     assert members.count(STORE_1D_FAST) == 32
+    # ring depth: 8 loads ahead for this long-row streaming program, 4 for the conductor graph's 1024-wide rows
+    assert [op for op, _ in both[:9]].count(PF_ISSUE_1D_FAST) == 8
+    graph = recorded("graph_fused_r65536_n1024")
+    assert [op for op, _ in transform(graph.bytecode, graph.tensor_infos, 1, 1)[:9]].count(PF_ISSUE_1D_FAST) == 4
     # a store between two loads of the same tensor keeps the second load where it is
     from gint_b200.host import frontend as fe
     bc = [[fe.LoadGlobal1DF32, 0], [fe.StoreGlobal1DF32, 16 * 128 + 0], [fe.LoadGlobal1DF32, 16 * 128 + 0], [fe.StoreGlobal1DF32, 1], [0, 0]]
