@@ -47,7 +47,7 @@ def _info_to_dict(t):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="path of a checkout of eliphatfs/gint (the package directory's parent)")
     opts = ap.parse_args()
     sys.path.insert(0, opts.reference)
 
