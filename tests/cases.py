@@ -393,6 +393,17 @@ def permute_selectors(a, b, out, REGW, WARP):
     halt()
 
 
+@bytecode
+def shifted_in_place(a, out, REGW, WARP):
+    """out[i] = 2 a[i], chunk by chunk, where `out` is the same memory as `a` one chunk further on: every store changes
+    what the next load reads. A launch that had started the loads early would see the old values."""
+    N, = a.shape
+    ab, ob = make_block_1d(a, N, 1), make_block_1d(out, N, 1)
+    for off in range(0, N, 128):
+        fldg_1d(off, ab); fmulimm(2.0); fstg_1d(off, ob)
+    halt()
+
+
 # ------------------------------------------------------------------------------------------------ case list
 
 def _z(*shape, dtype=torch.float32):
@@ -483,6 +494,9 @@ def build_cases() -> list[Case]:
         def mkw(g, n=n):
             return [torch.randn(n, generator=g)] + [_z(n) for _ in range(3)]
         cases.append(Case(f"width_ops_n{n}", width_ops, mkw, cdiv(n, 128), [1, 2, 3]))
+
+    cases.append(Case("shifted_in_place_n1024", shifted_in_place, lambda g: [torch.randn(1024 + 128, generator=g)], 1, [1],
+                      view=lambda ts: [ts[0][:1024], ts[0][128:]]))
 
     for n in [128, 1000]:
         def mkp(g, n=n):
