@@ -33,7 +33,7 @@ if ROOT not in sys.path:
 
 import torch  # noqa: E402
 
-FALLBACK_HBM_GBS = 6650.0   # earlier measurement on this pool, used only when MEASURED_PEAKS.json is absent
+FALLBACK_HBM_GBS = 6650.0   # an earlier copy-bandwidth measurement on B200, used only when MEASURED_PEAKS.json is absent
 NOMINAL_HBM_GBS = 8000.0
 L2_BYTES = 126 * 1024 * 1024
 # DRAM bytes per leading unit (row / matrix) of one launch, from the ncu captures summarised under profiles/ (small cases of
@@ -198,11 +198,53 @@ def oracle_port_speed(wl_cpu, budget_rows: int = 256):
 
 # ---------------------------------------------------------------------------------------------------- GPU side
 
-def run_program_bench(name: str, world: int, rank: int, steps: int, warmup: int, peak_gbs: float):
-    """Device-resident timing of one named program at its benchmark size (sharded `world` ways)."""
+def graph_replay_us(wls, ex, steps: int) -> float:
+    """Device time per pass with the host taken out: all buffer sets' launches captured once into a CUDA graph (the launch
+    entry point allocates nothing and copies nothing, so it can be captured) and the replays timed with CUDA events."""
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        for wl in wls:
+            wl.run(ex, side.cuda_stream)
+        side.synchronize()
+        with torch.cuda.graph(graph, stream=side):
+            for wl in wls:
+                wl.run(ex, torch.cuda.current_stream().cuda_stream)
+    torch.cuda.current_stream().wait_stream(side)
+    for _ in range(3):
+        graph.replay()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    start.record()
+    for _ in range(steps):
+        graph.replay()
+    stop.record()
+    torch.cuda.synchronize()
+    return start.elapsed_time(stop) * 1e3 / (steps * len(wls))
+
+
+def host_dispatch_us(wls, ex, stream: int, reps: int = 200) -> float:
+    """Host time per call of the launch path (argument conversion, cache lookup, the C call), device idle-time excluded:
+    wall clock over a burst of launches that are not waited for."""
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for i in range(reps):
+        wls[i % len(wls)].run(ex, stream)
+    dt = time.perf_counter() - t0
+    torch.cuda.synchronize()
+    n_launch = sum(wls[i % len(wls)].launches_per_run() for i in range(reps))
+    return dt * 1e6 / n_launch
+
+
+def run_program_bench(name: str, world: int, rank: int, steps: int, warmup: int, peak_gbs: float, impl: str = "b200"):
+    """Device-resident timing of one named program at its benchmark size (sharded `world` ways). impl "reference_kernel" runs
+    the same buffers through the reference's own executor and sm_100 kernels (baseline/_ref)."""
     from gint_b200 import get_executor
     from gint_b200.workloads import FULL_SIZES, make_workload
     ex = get_executor()
+    if impl == "reference_kernel":
+        from baseline import ref_harness
     leading, inner = FULL_SIZES[name]
     seed = 42 + rank
     # a+b is 12 MB and would sit in L2: rotate over enough independent buffer sets to exceed it
@@ -215,7 +257,10 @@ def run_program_bench(name: str, world: int, rank: int, steps: int, warmup: int,
     state = {"i": 0}
 
     def step():
-        wls[state["i"] % n_sets].run(ex, stream)
+        if impl == "reference_kernel":
+            ref_harness.run_workload(wls[state["i"] % n_sets], stream)
+        else:
+            wls[state["i"] % n_sets].run(ex, stream)
         state["i"] += 1
     for _ in range(max(3, warmup, n_sets)):   # every buffer set once at least: its program is built on first use
         step()
@@ -226,8 +271,22 @@ def run_program_bench(name: str, world: int, rank: int, steps: int, warmup: int,
     total_bytes = wl.algorithmic_bytes * world
     per_step_ms = ms / steps
     st = wl.steps[0]
+    if impl == "reference_kernel":
+        return {"ms_per_step": per_step_ms, "gbs": total_bytes / (per_step_ms * 1e-3) / 1e9,
+                "kernels": [ref_harness.variant_of(s_.program) for s_ in wl.steps],
+                "frac_of_measured_peak": total_bytes / (per_step_ms * 1e-3) / 1e9 / (peak_gbs * world)}, wls
     info = ex.launch_info(st.program, [wl.tensors[r] for r in st.roles], st.grid_dim)
+    split = {}
+    if wl.pre is None and world == 1:
+        # host and device separated: the event-timed figure above includes whatever the host fails to hide
+        try:
+            split = {"device_us_per_launch": graph_replay_us(wls, ex, max(10, steps)),
+                     "host_dispatch_us_per_launch": host_dispatch_us(wls, ex, stream)}
+            split["gbs_device_only"] = wl.algorithmic_bytes / wl.launches_per_run() / (split["device_us_per_launch"] * 1e-6) / 1e9
+        except Exception as e:   # context only
+            split = {"split_error": str(e)[:200]}
     return {
+        **split,
         "ms_per_step": per_step_ms,
         "gbs": total_bytes / (per_step_ms * 1e-3) / 1e9,
         "elements_per_s": wl.elements * world / (per_step_ms * 1e-3),
@@ -279,6 +338,33 @@ def run_e2e(name: str, world: int, rank: int, steps: int, warmup: int, overlappe
     return {"value": wl.algorithmic_bytes * world / (per_step * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": per_step,
             "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
             "api": "B200Executor.execute_streamed (16 ranges, copies overlapped with kernels)" if single else "B200Executor.execute between whole-tensor copies"}
+
+
+def run_strong_scaling(name: str, world: int, rank: int, steps: int, warmup: int):
+    """The FIXED benchmark configuration cut `world` ways by its leading dimension: every rank launches its contiguous range of
+    the full-size program's logical grid with gint_execute_range (same program, same descriptors, no collective) on rows it holds.
+    Time = slowest rank; value = the whole fixed batch's bytes over that time."""
+    from gint_b200 import get_executor
+    from gint_b200.host.executor import _convert_arg
+    from gint_b200.shard import shard_range
+    from gint_b200.workloads import FULL_SIZES, make_workload
+    ex = get_executor()
+    leading, inner = FULL_SIZES[name]
+    wl = make_workload(name, leading, inner, device="cuda", seed=42)     # same seed everywhere: one batch, replicated for simplicity
+    if len(wl.steps) != 1 or wl.pre is not None:
+        return None
+    st = wl.steps[0]
+    args = [_convert_arg(wl.tensors[r]) for r in st.roles]
+    first, count = shard_range(st.grid_dim, world, rank)
+    stream = torch.cuda.current_stream().cuda_stream
+
+    def step():
+        ex.execute_range(st.program, args, first, count, cuda_stream=stream)
+    for _ in range(max(3, warmup)):
+        step()
+    ms = time_device(step, steps, world) / steps
+    return {"ms_per_step": ms, "gbs": wl.algorithmic_bytes / (ms * 1e-3) / 1e9, "scaling": "strong",
+            "what": f"{leading} leading units in total, {world} contiguous ranges of the one program's grid (gint_execute_range)"}
 
 
 def main():
@@ -349,13 +435,30 @@ def main():
             programs[other] = r
             del w_
             torch.cuda.empty_cache()
+    # the reference's own kernels (its sm_100 build of geval_s7 / geval_l12, through its unmodified executor), same buffers and
+    # timing: what this library replaces, on this box
+    ref_kernel_note = None
+    if world == 1:
+        try:
+            from baseline import ref_harness
+            if not ref_harness.available():
+                ref_kernel_note = ref_harness.why_unavailable()
+            else:
+                for other in (("add", "rmsnorm", "bmm4x4", "inv4x4", "graph") if opts.programs == "all" else (name,)):
+                    r, w_ = run_program_bench(other, world, rank, max(5, min(opts.steps, 20)), warmup, peak, impl="reference_kernel")
+                    (programs[other] if other in programs else res)["reference_kernel"] = r
+                    del w_
+                    torch.cuda.empty_cache()
+        except Exception as e:
+            ref_kernel_note = f"{type(e).__name__}: {str(e)[:300]}"
+    strong = run_strong_scaling(name, world, rank, max(10, min(opts.steps, 30)), warmup) if world > 1 else None
 
     if rank == 0:
         line = {
             "metric": metric, "value": res["gbs"], "unit": "GB/s", "n_gpus": world, "steps": opts.steps, "warmup": warmup,
             "ms_per_step": res["ms_per_step"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "f32", "data": "synthetic (seeded)",
-            "config": dict(config, l2=res["l2"], elements_per_s=res["elements_per_s"], geometry=res["geometry"]),
+            "config": config, "l2": res["l2"], "elements_per_s": res["elements_per_s"], "geometry": res["geometry"],
             "clocks": clocks, "e2e": e2e, "gpu_launches": res["launches"],
             "roofline": {"bound": "hbm", "achieved": res["gbs"] / world, "peak": peak, "unit": "GB/s",
                          "frac": res["gbs"] / world / peak, "peak_kind": f"of {peak_kind}", "frac_of_8TBs": res["frac_of_8TBs"],
@@ -365,6 +468,12 @@ def main():
                          "kernel_ms": res["ms_per_step"] / res["launches_per_step"]},
             "programs": {k: {kk: vv for kk, vv in v.items() if kk not in ("launches",)} for k, v in programs.items()},
         }
+        if "reference_kernel" in res:
+            line["reference_kernel"] = res["reference_kernel"]
+        if ref_kernel_note:
+            line["reference_kernel_unavailable"] = ref_kernel_note
+        if strong is not None:
+            line["strong_scaling"] = strong
         if not opts.no_cpu:
             gbs, desc, cores, ms, wl_cpu = cpu_reference(name, budget_s=10.0)
             line["cpu_baseline"] = {"value": gbs, "unit": "GB/s", "cores": cores, "kind": "reference", "sample": desc}

@@ -9,8 +9,9 @@ from .host.sugar import bytecode
 from .host.executor import (BaseExecutableProgram, BaseExecutor, B200Executor, ProgramData, ProgramTensorInfo,
                             TensorInterface, get_executor)
 from .host.analyzer import analyze_bytecode, BytecodeStats
+from .dropin import install, uninstall
 
 __version__ = "0.1.0"
 
 __all__ = ["cdiv", "bytecode", "BaseExecutableProgram", "BaseExecutor", "B200Executor", "ProgramData", "ProgramTensorInfo",
-           "TensorInterface", "get_executor", "analyze_bytecode", "BytecodeStats", "__version__"]
+           "TensorInterface", "get_executor", "install", "uninstall", "analyze_bytecode", "BytecodeStats", "__version__"]

@@ -552,7 +552,9 @@ struct gint_ctx {
     void *ind_dev = nullptr;
     void *ind_host = nullptr;
     size_t ind_bytes = 0;
-    cudaEvent_t ind_event = nullptr;
+    cudaEvent_t ind_event = nullptr;         // the last indirect launch's table upload has been queued and read the host image
+    cudaEvent_t ind_kernel_event = nullptr;  // the last indirect launch's kernel has finished with the device tables
+    std::mutex ind_mu;                       // serialises indirect launches of this context (shared scratch)
 };
 
 namespace {
@@ -744,21 +746,16 @@ struct StaticScratch {
  * cudaGetSymbolAddress (static_scratch_for_device below). */
 static __device__ __align__(256) unsigned char g_static_scratch[sizeof(StaticScratch)];
 
-/* Zeroes the array once per device at set-up, so its contents are defined before the first table lands in it. */
-static __global__ void static_scratch_clear()
-{
-    uint32_t *w = reinterpret_cast<uint32_t *>(g_static_scratch);
-    for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < sizeof(StaticScratch) / 4; i += gridDim.x * blockDim.x) w[i] = 0u;
-}
-
 namespace {
 
 constexpr int kMaxDevices = 64;
 void *g_static_scratch_dev[kMaxDevices];          // device address of g_static_scratch, per device; nullptr = not set up
 unsigned char g_static_host[sizeof(StaticScratch)];  // host image of the tables for the call in progress
-std::mutex g_static_mu;                            // one allocation-free launch at a time builds its tables here
+std::mutex g_static_mu;                            // one allocation-free launch at a time: set-up, table upload and kernel launch
 
-/* Once per device, with that device current: resolve the device address of the scratch array and clear it. */
+/* Once per device, with that device current: resolve the device address of the scratch array. The caller holds g_static_mu,
+ * so two threads making their first call at the same time do the set-up once and neither sees a half-made entry. Nothing has
+ * to be cleared: every call writes each table entry that its kernel reads before that kernel is queued. */
 int static_scratch_for_device(gint_ctx *ctx, void **out)
 {
     if (ctx->device < 0 || ctx->device >= kMaxDevices) return fail(ctx, GINT_ERR_INVALID_ARGUMENT, "device ordinal out of range");
@@ -766,13 +763,23 @@ int static_scratch_for_device(gint_ctx *ctx, void **out)
         void *ptr = nullptr;
         cudaError_t e = cudaGetSymbolAddress(&ptr, g_static_scratch);
         if (e != cudaSuccess || !ptr) return fail(ctx, GINT_ERR_CUDA, "cudaGetSymbolAddress(static scratch)", e);
-        static_scratch_clear<<<8, 256>>>();
-        e = cudaGetLastError();
-        if (e == cudaSuccess) e = cudaDeviceSynchronize();
-        if (e != cudaSuccess) return fail(ctx, GINT_ERR_CUDA, "clearing the static scratch", e);
         g_static_scratch_dev[ctx->device] = ptr;
     }
     *out = g_static_scratch_dev[ctx->device];
+    return GINT_OK;
+}
+
+/* The indirect entry points upload their tables from a host image that the next call overwrites; a captured copy would read
+ * that image again at every replay. They therefore refuse a stream that is being captured. */
+int refuse_capture(gint_ctx *ctx, cudaStream_t stream, const char *who)
+{
+    cudaStreamCaptureStatus st = cudaStreamCaptureStatusNone;
+    cudaError_t e = cudaStreamIsCapturing(stream, &st);
+    if (e != cudaSuccess) { cudaGetLastError(); return fail(ctx, GINT_ERR_CUDA, "cudaStreamIsCapturing", e); }
+    if (st != cudaStreamCaptureStatusNone) {
+        std::string msg = std::string(who) + ": the stream is being captured; indirect launches cannot be part of a CUDA graph";
+        return fail(ctx, GINT_ERR_INVALID_ARGUMENT, msg.c_str());
+    }
     return GINT_OK;
 }
 
@@ -883,6 +890,7 @@ void gint_destroy(gint_ctx *ctx)
         if (ctx->ind_dev) cudaFree(ctx->ind_dev);
         if (ctx->ind_host) cudaFreeHost(ctx->ind_host);
         if (ctx->ind_event) cudaEventDestroy(ctx->ind_event);
+        if (ctx->ind_kernel_event) cudaEventDestroy(ctx->ind_kernel_event);
     }
     delete ctx;
 }
@@ -928,12 +936,18 @@ int gint_program_create(gint_ctx *ctx, const int32_t *code, int n_words, const g
             for (const Insn &in : ei.prog) n_staged_loads += in.op == OP_LoadStagedRows;
         }
         bool usable = ei.n_early > 0 || staged != 0;
+        /* A slot that the program moves (AdvanceBase / AdvanceBlock2D) reaches beyond the extent its descriptor gives, so
+         * the launch-time overlap check cannot bound it: a program that pairs such a slot with a moved load keeps the
+         * stream as written. */
+        uint32_t advanced = 0;
+        for (const Insn &in : prog)
+            if (in.op == OP_AdvanceBlock2D || in.op == OP_AdvanceBase) advanced |= 1u << (in.operand & 7u);
         for (int t = 0; t < n_tensors; t++) {
             p->extent[t] = tensor_extent_bytes(p->ti, t);
             p->alias_slots[t] = ei.alias_slots[t];
-            if (ei.alias_slots[t] && p->extent[t] == 0) usable = false;
+            if (ei.alias_slots[t] && (p->extent[t] == 0 || ((advanced >> t) & 1u))) usable = false;
             for (int b = 0; b < n_tensors; b++)
-                if ((ei.alias_slots[t] >> b) & 1u) { if (tensor_extent_bytes(p->ti, b) == 0) usable = false; }
+                if ((ei.alias_slots[t] >> b) & 1u) { if (tensor_extent_bytes(p->ti, b) == 0 || ((advanced >> b) & 1u)) usable = false; }
         }
         if (usable) {
             p->fast_slots = apply_fast_accesses(&ei.prog, p->ti, n_tensors) | staged;
@@ -1027,7 +1041,7 @@ int gint_program_launch_info(gint_ctx *ctx, uint64_t handle, uint32_t grid_dim, 
     out->regs_per_thread = g.v->regs;
     out->blocks_per_sm = g.blocks_per_sm;
     out->num_sms = ctx->num_sms;
-    out->staged_row_tensors = p->n_early;   // number of tile loads per logical program that are issued early
+    out->early_loads = p->n_early;
     return GINT_OK;
 }
 
@@ -1084,11 +1098,19 @@ int gint_execute_indirect(gint_ctx *ctx, const uint64_t *handles, int n_programs
 
     DeviceGuard guard(ctx->device);
     cudaStream_t stream = (cudaStream_t)cuda_stream;
+    {
+        int rc = refuse_capture(ctx, stream, "gint_execute_indirect");
+        if (rc != GINT_OK) return rc;
+    }
+    /* One indirect launch of a context at a time builds its tables: the scratch (host image and device copy) is shared by
+     * every call, and its layout depends on n_programs. */
+    std::lock_guard<std::mutex> ind_lock(ctx->ind_mu);
     /* scratch layout: [n_programs x gint_tensor_info | grid_dim x IndirectEntry] */
     const size_t ti_bytes = (size_t)n_programs * sizeof(gint_tensor_info);
     const size_t need = ti_bytes + (size_t)grid_dim * sizeof(IndirectEntry);
     if (need > ctx->ind_bytes) {
         if (ctx->ind_event) cudaEventSynchronize(ctx->ind_event);
+        if (ctx->ind_kernel_event) cudaEventSynchronize(ctx->ind_kernel_event);   // the previous kernel still reads the old scratch
         if (ctx->ind_dev) { cudaFree(ctx->ind_dev); ctx->ind_dev = nullptr; }
         if (ctx->ind_host) { cudaFreeHost(ctx->ind_host); ctx->ind_host = nullptr; }
         ctx->ind_bytes = 0;
@@ -1101,9 +1123,14 @@ int gint_execute_indirect(gint_ctx *ctx, const uint64_t *handles, int n_programs
     }
     if (!ctx->ind_event) {
         cudaError_t e = cudaEventCreateWithFlags(&ctx->ind_event, cudaEventDisableTiming);
+        if (e == cudaSuccess) e = cudaEventCreateWithFlags(&ctx->ind_kernel_event, cudaEventDisableTiming);
         if (e != cudaSuccess) return fail(ctx, GINT_ERR_CUDA, "cudaEventCreate", e);
     } else {
         cudaEventSynchronize(ctx->ind_event);  // the previous launch's upload has left the staging buffer
+        /* ... and the previous launch's KERNEL, possibly on another stream, must be done with the device copy of the
+         * tables before this upload overwrites them: this stream waits for it (a no-op on the same stream) */
+        cudaError_t e = cudaStreamWaitEvent(stream, ctx->ind_kernel_event, 0);
+        if (e != cudaSuccess) return fail(ctx, GINT_ERR_CUDA, "cudaStreamWaitEvent(indirect)", e);
     }
     gint_tensor_info *h_ti = (gint_tensor_info *)ctx->ind_host;
     IndirectEntry *h_tab = (IndirectEntry *)((char *)ctx->ind_host + ti_bytes);
@@ -1140,6 +1167,8 @@ int gint_execute_indirect(gint_ctx *ctx, const uint64_t *handles, int n_programs
     if (blocks > resident) blocks = resident;
     void *args[1] = {&a};
     e = cudaLaunchKernel(ctx->indirect.fn, dim3((unsigned)blocks), dim3(gint::kThreadsPerBlock), args, smem, stream);
+    /* recorded whether or not the launch succeeded: the next call waits on this event and it must not be left unrecorded */
+    cudaEventRecord(ctx->ind_kernel_event, stream);
     if (e != cudaSuccess) return fail(ctx, GINT_ERR_CUDA, "cudaLaunchKernel(indirect)", e);
     return GINT_OK;
 }
@@ -1170,14 +1199,18 @@ int gint_execute_indirect_static(gint_ctx *ctx, const uint64_t *handles, int n_p
     if ((int)smem > ctx->max_smem_optin) return fail(ctx, GINT_ERR_TOO_LARGE, "a program of this batch is too long for indirect mode (shared memory)");
 
     DeviceGuard guard(ctx->device);
-    void *scratch = nullptr;
-    int rc = static_scratch_for_device(ctx, &scratch);  // first call on a device: set-up (synchronises the device)
-    if (rc != GINT_OK) return rc;
     cudaStream_t stream = (cudaStream_t)cuda_stream;
+    int rc = refuse_capture(ctx, stream, "gint_execute_indirect_static");
+    if (rc != GINT_OK) return rc;
+    /* Held from set-up to the kernel launch: the host image is shared, and the uploads and the launch of one call must not be
+     * interleaved with another thread's. */
+    std::lock_guard<std::mutex> lk(g_static_mu);
+    void *scratch = nullptr;
+    rc = static_scratch_for_device(ctx, &scratch);  // first call on a device: resolves the array's device address
+    if (rc != GINT_OK) return rc;
     const StaticScratch *d = reinterpret_cast<const StaticScratch *>(scratch);
     cudaError_t e;
     {
-        std::lock_guard<std::mutex> lk(g_static_mu);
         StaticScratch *h = reinterpret_cast<StaticScratch *>(g_static_host);
         for (int i = 0; i < n_programs; i++) {
             h->ti[i] = progs[i]->ti;
@@ -1190,7 +1223,7 @@ int gint_execute_indirect_static(gint_ctx *ctx, const uint64_t *handles, int n_p
             h->table[i].reserved = 0;
         }
         /* Two copies of exactly the used parts. The source is ordinary (pageable) host memory: the runtime stages it and
-         * returns once the host image may be reused, which is why the lock can be dropped after these calls. */
+         * returns once the host image may be reused by the next call. */
         e = cudaMemcpyAsync(scratch, h, (size_t)n_programs * sizeof(gint_tensor_info), cudaMemcpyHostToDevice, stream);
         if (e == cudaSuccess)
             e = cudaMemcpyAsync((char *)scratch + offsetof(StaticScratch, table), h->table, (size_t)grid_dim * sizeof(IndirectEntry),

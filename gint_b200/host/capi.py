@@ -43,7 +43,7 @@ class BytecodeStatsC(ctypes.Structure):
 
 class LaunchInfoC(ctypes.Structure):
     _fields_ = [(n, c_int32) for n in ("pool_size", "tiles_per_warp", "warps_per_block", "grid_blocks", "smem_bytes",
-                                       "regs_per_thread", "blocks_per_sm", "num_sms", "staged_row_tensors")] + \
+                                       "regs_per_thread", "blocks_per_sm", "num_sms", "early_loads")] + \
                [("reserved", c_int32 * 7)]
 
 

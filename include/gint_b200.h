@@ -65,7 +65,7 @@ typedef struct gint_bytecode_stats {
     int32_t reserved;
 } gint_bytecode_stats;
 
-/* How a program will be / was launched; for tests, benchmarks and DESIGN notes. */
+/* How a program will be / was launched; for tests and benchmarks. */
 typedef struct gint_launch_info {
     int32_t pool_size;        /* 4, 7, 12 */
     int32_t tiles_per_warp;   /* logical programs interpreted together by one warp: 1, 2 or 4 */
@@ -75,7 +75,7 @@ typedef struct gint_launch_info {
     int32_t regs_per_thread;
     int32_t blocks_per_sm;
     int32_t num_sms;
-    int32_t staged_row_tensors; /* tile loads per logical program that are started ahead of their use (early issue) */
+    int32_t early_loads;      /* tile loads per logical program that are started ahead of their use (early issue) */
     int32_t reserved[7];
 } gint_launch_info;
 
@@ -168,8 +168,13 @@ int gint_execute_plan(gint_ctx *ctx, const gint_plan_step *steps, int n_steps, v
 
 /* One launch in which logical program i runs programs[indices[i]] with that program's own tensors.
  * base_ptrs holds n_programs rows of GINT_MAX_TENSORS addresses. Replaces CudaExecutor.execute_indirect
- * (gint/host/cuda/executor_impl.py:135-201). Uses context-owned scratch for the per-warp tables; may grow
- * it (allocation) on a call with a larger batch than any before, so warm it up before stream capture. */
+ * (gint/host/cuda/executor_impl.py:135-201). Uses context-owned scratch for the per-warp tables and may grow it
+ * (allocation) on a call with a larger batch than any before. Indirect launches of one context are serialised: a call
+ * holds a context lock while it builds and queues its tables, and its upload waits (on the GPU, through an event) for
+ * the previous indirect kernel of the context, whichever stream that ran on, so calls from several threads or streams
+ * cannot overwrite tables that are still being read. Not for stream capture: the tables are uploaded from a host image
+ * that the next call overwrites, so a stream that is being captured is refused with GINT_ERR_INVALID_ARGUMENT. Of the
+ * launch entry points only gint_execute, gint_execute_range and gint_execute_plan may be captured. */
 int gint_execute_indirect(gint_ctx *ctx, const uint64_t *handles, int n_programs, const uint64_t *base_ptrs,
                           const int32_t *indices, uint32_t grid_dim, void *cuda_stream);
 
@@ -184,8 +189,12 @@ int gint_execute_indirect(gint_ctx *ctx, const uint64_t *handles, int n_programs
  * or any other allocating routine, on the device or in a library.
  *   Limits: n_programs <= 64 and grid_dim <= 4096; anything larger is refused with GINT_ERR_TOO_LARGE (and a message in
  *     gint_last_error) before any work is queued. Use gint_execute_indirect for larger batches.
- *   Set-up: the first call on a device resolves the array's device address and clears the array once; that first call
- *     synchronises the device, so make it before any stream capture begins and outside latency-critical sections.
+ *   Set-up: the first call on a device resolves the array's device address (cudaGetSymbolAddress, which may load the
+ *     library's device code); make that first call before any stream capture begins in the process and outside
+ *     latency-critical sections. Set-up and the rest of the call run under one process-wide lock, so first calls from
+ *     several threads are safe.
+ *   Capture: like gint_execute_indirect this call uploads its tables from a host image that the next call overwrites, so
+ *     it refuses a stream that is being captured (GINT_ERR_INVALID_ARGUMENT).
  *   Sharing: every call on a device, from any context or thread, uses the same array, and the array keeps the previous
  *     call's tables until they are overwritten. Each call rewrites every entry it is going to read (nothing has to start
  *     at zero), but two of these launches that can overlap on the GPU -- different streams without an ordering between

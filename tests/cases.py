@@ -344,6 +344,75 @@ def advance_walk(x, y, REGW, WARP, STEPS):
 
 
 @bytecode
+def dtype_tiles_1d(xh, xb, xu, oh, ob, of, REGW, WARP):
+    """f16 / bf16 / u8 tiles through the 1-D layout (element = offset + lane + 32 w), with Nop and Pop2 along the way."""
+    N, = xh.shape
+    h, b, u, ohb, obb, ofb = [make_block_1d(t, N, t.strides[0], cdiv(N, 256), 256) for t in (xh, xb, xu, oh, ob, of)]
+    for i in range(0, 256, WARP * REGW):
+        nop()
+        fldg_1d_f16(i, h)
+        fldg_1d_bf16(i, b)
+        fadd()
+        dup()
+        fstg_1d_f16(i, ohb)
+        fpush(3.0)
+        fpush(4.0)
+        pop2()                 # drops both immediates
+        fldg_1d_u8(i, u)
+        fmul()
+        dup()
+        fstg_1d_bf16(i, obb)
+        fstg_1d(i, ofb)
+    halt()
+
+
+@bytecode
+def dtype_tiles_2dw(xh, xb, xu, oh, ob, of, REGW, WARP):
+    """f16 / bf16 / u8 tiles through the 2DW layout: thread = row (dim 1), width lane = column (dim 2)."""
+    T, W = xh.shape
+    h, b, u, ohb, obb, ofb = [make_block_2d(t, [T, W], [t.strides[0], t.strides[1]], [cdiv(T, WARP), 1], [WARP, 0])
+                              for t in (xh, xb, xu, oh, ob, of)]
+    for j in range(0, W, REGW):
+        fldg_2dw_f16(j, h)
+        fldg_2dw_bf16(j, b)
+        fadd()
+        dup()
+        fstg_2dw_f16(j, ohb)
+        fldg_2dw_u8(j, u)
+        fmul()
+        dup()
+        fstg_2dw_bf16(j, obb)
+        fstg_2dw(j, ofb)
+    halt()
+
+
+@bytecode
+def advance_alias(a, out, REGW, WARP):
+    """A store through a slot that AdvanceBase has moved OUTSIDE the extent its descriptor gives lands on what a later load of
+    another slot reads: the load must see the stored values, so it may not be started ahead of the store. (`out` is described
+    as 128 elements that do not overlap `a`; moved by 512 bytes it covers a[0:128].)"""
+    ab, ob = make_block_1d(a, 256, 1), make_block_1d(out, 128, 1)
+    fldg_1d(0, ab); fmulimm(2.0); adv_base(512, ob); fstg_1d(0, ob)       # a[0:128] = 2 a[0:128], through the moved `out`
+    fldg_1d(0, ab); fmulimm(3.0); adv_base(-512, ob); fstg_1d(0, ob)      # out[0:128] = 3 * (the new a[0:128])
+    fldg_1d(128, ab); fldg_1d(0, ab); fadd(); adv_base(1024, ob); fstg_1d(0, ob)   # a[128:256] += a[0:128]
+    halt()
+
+
+def narrow_special_values(n: int, g: torch.Generator):
+    """Inputs for the narrow-type cases: random values with, in front, sums that are exact ties of the f16 / bf16 roundings,
+    values beyond the f16 range, signed zeros, infinities and NaN."""
+    h = torch.randn(n, generator=g).half()
+    b = torch.randn(n, generator=g).bfloat16()
+    u = torch.randint(0, 256, (n,), generator=g, dtype=torch.int64).to(torch.uint8)
+    sp_h = torch.tensor([1.0, 1.0, 1.0, 65504.0, 65504.0, -0.0, float("inf"), float("nan"), 6.1e-5, 2.0 ** -24, 0.0, 1.0]).half()
+    sp_b = torch.tensor([2.0 ** -11, 3 * 2.0 ** -11, 2.0 ** -12, 16.0, 8.0, 0.0, 1.0, 1.0, -6.1e-5, 2.0 ** -25, float("-inf"), float("nan")]).bfloat16()
+    sp_u = torch.tensor([1, 1, 1, 1, 255, 7, 0, 3, 1, 1, 2, 0], dtype=torch.uint8)
+    k = min(n, sp_h.numel())
+    h[:k], b[:k], u[:k] = sp_h[:k], sp_b[:k], sp_u[:k]
+    return h, b, u
+
+
+@bytecode
 def special_math(x, o_sqrt, o_exp, o_log, o_trig, o_misc, REGW, WARP):
     """Transcendental opcodes (approximate on the GPU; compared with a tolerance)."""
     N, = x.shape
@@ -515,10 +584,37 @@ def build_cases() -> list[Case]:
                     _z(r, c, dtype=torch.float16), _z(r, c, dtype=torch.bfloat16), _z(r, c)]
         cases.append(Case(f"dtype_tiles_r{r}_c{c}", dtype_tiles, mk, cdiv(r, REGW), [3, 4, 5]))
 
+    # narrow types through the 1-D and 2DW layouts (partial tiles, a strided view, rounding ties, NaN / inf / overflow)
+    for n in [1, 127, 256, 1000]:
+        def mk(g, n=n):
+            h, b, u = narrow_special_values(n, g)
+            return [h, b, u, _z(n, dtype=torch.float16), _z(n, dtype=torch.bfloat16), _z(n)]
+        cases.append(Case(f"dtype_tiles_1d_n{n}", dtype_tiles_1d, mk, cdiv(n, 256), [3, 4, 5]))
+
+    def mk_1d_strided(g):
+        h, b, u = narrow_special_values(900, g)
+        return [h, b, u, _z(900, dtype=torch.float16), _z(900, dtype=torch.bfloat16), _z(900)]
+    cases.append(Case("dtype_tiles_1d_strided", dtype_tiles_1d, mk_1d_strided, cdiv(300, 256), [3, 4, 5], view=lambda ts: [t[::3] for t in ts]))
+
+    for t_, w_ in [(1, 4), (33, 6), (100, 16)]:
+        def mk(g, t_=t_, w_=w_):
+            h, b, u = narrow_special_values(t_ * w_, g)
+            return [h.view(t_, w_), b.view(t_, w_), u.view(t_, w_), _z(t_, w_, dtype=torch.float16), _z(t_, w_, dtype=torch.bfloat16), _z(t_, w_)]
+        cases.append(Case(f"dtype_tiles_2dw_t{t_}_w{w_}", dtype_tiles_2dw, mk, cdiv(t_, 32), [3, 4, 5]))
+
+    def mk_2dw_strided(g):
+        h, b, u = narrow_special_values(64 * 24, g)
+        return [h.view(64, 24), b.view(64, 24), u.view(64, 24), _z(64, 24, dtype=torch.float16), _z(64, 24, dtype=torch.bfloat16), _z(64, 24)]
+    cases.append(Case("dtype_tiles_2dw_strided", dtype_tiles_2dw, mk_2dw_strided, cdiv(64, 32), [3, 4, 5],
+                      view=lambda ts: [t[1::2, ::2] for t in ts]))
+
     def mk_adv(g):
         return [torch.randn(100, 4, generator=g), torch.full((128, 4), 7.0)]
     cases.append(Case("advance_walk", advance_walk, mk_adv, 1, [1], kwargs=dict(STEPS=4),
                       expect=lambda t: {1: torch.cat([t[0] * 2.0, torch.zeros(28, 4)])}))
+
+    cases.append(Case("advance_alias", advance_alias, lambda g: [torch.randn(384, generator=g)], 1, [0, 1],
+                      view=lambda ts: [ts[0][128:384], ts[0][0:128]]))
 
     for n in [1, 128, 777]:
         def mk(g, n=n):

@@ -94,8 +94,12 @@ class FuzzProgram(BaseExecutableProgram):
                     choices.append("regstore")
                 if depth < self.max_depth:
                     choices += ["dup", "bcast"]
+            if rng.random() < 0.05:
+                choices.append("nop")
             if depth >= 2:
                 choices += ["binary", "binary", "binary", "swap", "shuf"]
+                if depth >= 3 and rng.random() < 0.2:
+                    choices.append("pop2")
                 if depth < self.max_depth:
                     choices.append("dupx1")
                 if depth + 2 <= self.max_depth:
@@ -157,6 +161,10 @@ class FuzzProgram(BaseExecutableProgram):
                 emit(O.Dup2)
             elif kind == "swap":
                 emit(O.Swap)
+            elif kind == "nop":
+                emit(O.Nop)
+            elif kind == "pop2":
+                emit(O.Pop2)
             elif kind == "binary":
                 emit(binary[rng.integers(len(binary))])
             elif kind == "tern":

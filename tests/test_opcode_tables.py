@@ -131,3 +131,25 @@ def test_pool_geometry_of_the_named_programs():
     variant = lambda n: select_variant(np.asarray(recs[n]["bytecode"], dtype=np.int32))
     assert [variant(n) for n in ("add_n1048576", "rmsnorm_r16384_n4096", "bmm4x4_b4194304", "inv4x4_b4194304",
                                  "graph_fused_r65536_n1024")] == ["s7", "s7", "s7", "l12", "s7"]
+
+
+def test_every_opcode_is_executed_by_a_parity_case():
+    """All 106 opcodes of the format appear in the programs that the GPU parity tests run against the oracle (the case list
+    plus the random programs), so no handler goes untested."""
+    import torch
+    from cases import build_cases, to_interfaces
+    from fuzz import FuzzProgram
+    seen = set()
+    for case in build_cases():
+        host = case.make(torch.Generator().manual_seed(42))
+        if case.view:
+            host = case.view(host)
+        pd = case.program.get_program(*to_interfaces(host), **case.kwargs)
+        seen.update(int(op) for op in np.asarray(pd.program).reshape(-1, 2)[:, 0])
+    for seed in range(24):     # the parameters of test_gpu_parity.py::test_random_programs_bit_exact
+        depth, regs = [(3, 1), (4, 0), (6, 1), (7, 4), (8, 4), (4, 8), (5, 7), (2, 2)][seed % 8]
+        for family in ("float", "int"):
+            pd = FuzzProgram(seed, family, depth, regs, length=60 + 7 * seed, rows=33, cols=36).get_program()
+            seen.update(int(op) for op in np.asarray(pd.program).reshape(-1, 2)[:, 0])
+    missing = sorted(set(range(opcodes.N_OPCODES)) - seen)
+    assert not missing, [opcodes.NAMES[m] for m in missing]

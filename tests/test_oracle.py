@@ -199,6 +199,51 @@ def test_dtype_tiles_expectation(r, c):
     assert torch.equal(t[5], prod)
 
 
+NARROW = [c.name for c in CASES if c.name.startswith(("dtype_tiles_1d", "dtype_tiles_2dw"))]
+
+
+@pytest.mark.parametrize("name", NARROW)
+def test_narrow_type_tiles_expectation(name):
+    """1-D and 2DW f16 / bf16 / u8 loads and f16 / bf16 stores against an independent torch expression: widening is exact,
+    narrowing is round-to-nearest-even (ties, overflow to inf, NaN stays NaN), and Nop / Pop2 leave the values alone."""
+    case = next(k for k in CASES if k.name == name)
+    t = run_case_on_oracle(case)
+    h = t[0].float() + t[1].float()
+    prod = h * t[2].float()
+    for got, want in ((t[3], h.half()), (t[4], prod.bfloat16()), (t[5], prod)):
+        assert got.shape == want.shape
+        nan = torch.isnan(want.float())
+        assert torch.equal(torch.isnan(got.float()), nan)
+        assert torch.equal(got.float()[~nan], want.float()[~nan])
+        # signed zeros too
+        assert torch.equal(torch.signbit(got.float()[~nan]), torch.signbit(want.float()[~nan]))
+
+
+def test_narrowing_ties_go_to_even():
+    """Known answers for the special values in front of the narrow-type inputs."""
+    case = next(k for k in CASES if k.name == "dtype_tiles_1d_n127")
+    t = run_case_on_oracle(case)
+    oh = t[3].float()
+    assert oh[0] == 1.0                      # 1 + 2^-11 is halfway between 1 and 1 + 2^-10: even mantissa wins
+    assert oh[1] == 1.0 + 2.0 ** -9          # 1 + 3 * 2^-11 is halfway between 1 + 2^-10 and 1 + 2^-9
+    assert oh[2] == 1.0                      # 1 + 2^-12 is below the tie
+    assert oh[3] == float("inf")             # 65504 + 16 is the tie between 65504 (odd mantissa) and 2^16: even wins, which overflows
+    assert oh[4] == 65504.0                  # 65504 + 8 is below that tie
+    assert torch.isnan(oh[7]) and torch.isnan(oh[11]) and oh[6] == float("inf") and oh[10] == float("-inf")
+
+
+def test_advance_alias_expectation():
+    """Stores through a moved slot are seen by the loads that follow them in program order."""
+    case = next(k for k in CASES if k.name == "advance_alias")
+    g = torch.Generator().manual_seed(42)
+    orig = case.make(g)[0].clone()
+    t = run_case_on_oracle(case)
+    a0, a1 = orig[128:256], orig[256:384]
+    assert torch.equal(t[0][:128], 2 * a0)
+    assert torch.equal(t[1], 3 * (2 * a0))
+    assert torch.equal(t[0][128:], a1 + 2 * a0)
+
+
 def test_special_math_close_to_libm():
     case = next(c for c in CASES if c.name == "special_math_n777")
     t = run_case_on_oracle(case)
