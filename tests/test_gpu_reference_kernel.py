@@ -57,6 +57,13 @@ def test_case_matches_reference_kernel(case):
     torch.cuda.synchronize()
     approx = (not case.exact) or case.name.startswith(APPROX)
     for i in case.outputs:
+        if case.name.startswith("int_mix") and i == 3:
+            # IDiv / IRem by zero: undefined in the reference (LLVM sdiv / srem, arith_int.py:42-51); this build defines them
+            # (quotient -1, remainder = dividend). Compared where the divisor is not zero.
+            keep = host[1].view(torch.int32) != 0
+            assert keep.sum() > 0
+            assert bits_equal(ours[i].cpu()[keep], theirs[i].cpu()[keep]), f"{case.name} output {i}: " + mismatch_report(ours[i].cpu()[keep], theirs[i].cpu()[keep])
+            continue
         if approx:
             torch.testing.assert_close(ours[i].float().cpu(), theirs[i].float().cpu(), rtol=max(case.rtol, 2e-5), atol=max(case.atol, 2e-5))
         else:
