@@ -29,7 +29,14 @@ CSRC = os.path.join(PKG_DIR, "csrc")
 KERNELS = os.path.join(CSRC, "kernels")
 OBJ_DIR = os.path.join(CSRC, "build")
 LIB_PATH = os.path.join(PKG_DIR, "libgint_b200.so")
-N_OPS = 142          # GINT_N_DISPATCH: the 106 opcodes of the format + the internal ones
+def _dispatch_count() -> int:
+    """GINT_N_DISPATCH of csrc/gint_opcodes.h: the 106 opcodes of the format + the internal ones + the fused handlers."""
+    import re
+    with open(os.path.join(CSRC, "gint_opcodes.h")) as f:
+        return int(re.search(r"#define GINT_N_DISPATCH (\d+)", f.read()).group(1))
+
+
+N_OPS = _dispatch_count()
 N_KEYS = 9 * N_OPS   # (GINT_MAX_STACK + 1) * GINT_N_DISPATCH
 
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
@@ -58,14 +65,14 @@ def _run(cmd: list[str], what: str) -> str:
 
 
 def _newest_header() -> float:
-    hdrs = glob.glob(os.path.join(CSRC, "*.h")) + glob.glob(os.path.join(CSRC, "*.cuh")) + \
+    hdrs = glob.glob(os.path.join(CSRC, "*.h")) + glob.glob(os.path.join(CSRC, "*.cuh")) + glob.glob(os.path.join(CSRC, "hot_handlers.json")) + \
         glob.glob(os.path.join(PKG_DIR, "..", "include", "*.h")) + [os.path.join(PKG_DIR, "ptx_dispatch.py"), __file__]
     return max(os.path.getmtime(h) for h in hdrs)
 
 
-def _build_kernel(src: str, extra: list[str], jump_table: bool) -> tuple[str, str]:
+def _build_kernel(src: str, extra: list[str], jump_table: bool, cluster: bool = True) -> tuple[str, str]:
     """CUDA C++ -> PTX -> (jump-table rewrite) -> cubin -> object with the cubin as a byte array."""
-    from . import ptx_dispatch
+    from . import hot_handlers, ptx_dispatch
     stem = os.path.basename(src)[:-3]                       # gint_direct_p4_k1
     sym = stem.replace("gint_", "gint_cubin_").replace("_p", "_").replace("_k", "_")   # gint_cubin_direct_4_1
     ptx, cubin, obj = (os.path.join(OBJ_DIR, stem + ext) for ext in (".ptx", ".cubin", ".o"))
@@ -73,10 +80,10 @@ def _build_kernel(src: str, extra: list[str], jump_table: bool) -> tuple[str, st
     _run([_nvcc(), "-arch=compute_100a", "-ptx"] + COMMON + extra + [src, "-o", ptx], f"nvcc -ptx {stem}")
     log = ""
     if jump_table:
-        text, stats = ptx_dispatch.rewrite(open(ptx).read(), N_KEYS, N_OPS)
+        text, stats = ptx_dispatch.rewrite(open(ptx).read(), N_KEYS, N_OPS, cluster=cluster, hot=hot_handlers.load())
         with open(ptx, "w") as f:
             f.write(text)
-        log += f"jump table: {stats['cases']} cases over {stats['keys']} keys\n"
+        log += f"jump table: {stats['cases']} cases over {stats['keys']} keys, {stats['clustered']} small handlers clustered\n"
     t1 = time.time()
     # -fmad=false again: ptxas would otherwise contract the adjacent mul.rn.f32x2 / add.rn.f32x2 of a fused handler into an fma
     log += _run([_nvcc(), "-arch=sm_100a", "-cubin", "-lineinfo", "-fmad=false", "-Xptxas", "-v", ptx, "-o", cubin], f"ptxas {stem}")
@@ -90,11 +97,11 @@ def _build_kernel(src: str, extra: list[str], jump_table: bool) -> tuple[str, st
 
 
 def build(force: bool = False, jobs: int | None = None, verbose: bool = False, extra_flags: list[str] | None = None,
-          jump_table: bool = True) -> str:
+          jump_table: bool = True, cluster: bool = True) -> str:
     os.makedirs(OBJ_DIR, exist_ok=True)
     extra = list(extra_flags or [])
     stamp = os.path.join(OBJ_DIR, "flags.txt")
-    flags_now = " ".join(extra) + f" jt={jump_table}"
+    flags_now = " ".join(extra) + f" jt={jump_table} cluster={cluster}"
     if not os.path.exists(stamp) or open(stamp).read() != flags_now:
         force = True
     hdr_time = _newest_header()
@@ -111,7 +118,7 @@ def build(force: bool = False, jobs: int | None = None, verbose: bool = False, e
     objs.append(capi_obj)
     capi_todo = force or not os.path.exists(capi_obj) or os.path.getmtime(capi_obj) < max(os.path.getmtime(capi_src), hdr_time)
     with concurrent.futures.ThreadPoolExecutor(max_workers=jobs or os.cpu_count() or 4) as ex:
-        futs = [ex.submit(_build_kernel, s, extra, jump_table) for s in todo]
+        futs = [ex.submit(_build_kernel, s, extra, jump_table, cluster) for s in todo]
         if capi_todo:
             futs.append(ex.submit(lambda: ("gint_capi", _run([_nvcc()] + ARCH + COMMON + ["-Xcompiler", "-fPIC", "-c", capi_src, "-o", capi_obj],
                                                               "nvcc gint_capi"))))
@@ -134,10 +141,11 @@ def main() -> None:
     ap.add_argument("--force", action="store_true")
     ap.add_argument("--jobs", type=int, default=None)
     ap.add_argument("--no-jump-table", action="store_true", help="keep nvcc's compare-tree dispatch (for A/B measurements)")
+    ap.add_argument("--no-cluster", action="store_true", help="leave the small handlers where the compiler put them (for A/B measurements)")
     ap.add_argument("-D", dest="defines", action="append", default=[])
     opts = ap.parse_args()
     path = build(force=opts.force, jobs=opts.jobs, verbose=True, extra_flags=[f"-D{d}" for d in opts.defines],
-                 jump_table=not opts.no_jump_table)
+                 jump_table=not opts.no_jump_table, cluster=not opts.no_cluster)
     print(path)
 
 

@@ -31,11 +31,13 @@ using gint::LaunchArgs;
 namespace {
 
 struct OpEffect { int8_t min_depth, net; };
-const OpEffect kEffects[GINT_N_OPCODES] = {
+const OpEffect kEffects[GINT_FUSED_FIRST] = {     // the format's opcodes, then the internal ones (numbered consecutively)
 #define GINT_X_EFF(name, num, md, net) {md, net},
     GINT_OPCODE_LIST(GINT_X_EFF)
+    GINT_INTERNAL_OPCODE_LIST(GINT_X_EFF)
 #undef GINT_X_EFF
 };
+static_assert(sizeof(kEffects) / sizeof(kEffects[0]) == GINT_FUSED_FIRST, "internal opcodes must be numbered consecutively up to the fused handlers");
 
 bool is_tensor_op(int op)
 {
@@ -128,15 +130,13 @@ constexpr int OP_CARRIER_UNUSED = -2; // the same, for a member that reads no op
 int net_effect(int op)
 {
     if (op == OP_CARRIER || op == OP_CARRIER_UNUSED) return 0;
-    if (op < GINT_N_OPCODES) return kEffects[op].net;
     if (op >= GINT_FUSED_FIRST) {
         int net = 0;
         const FusedDef &f = kFused[op - GINT_FUSED_FIRST];
         for (int j = 0; j < f.len; j++) net += net_effect(f.ops[j]);
         return net;
     }
-    if (op == OP_StoreGlobal1DF32Fast) return -1;
-    return (op == OP_PfTake || op == OP_PfTakeIssue1D || op == OP_PfTakeIssue1DFast || op == OP_LoadGlobal1DF32Fast || op == OP_LoadStagedRows) ? 1 : 0;
+    return kEffects[op].net;
 }
 
 /* Replace known instruction sequences by fused handlers (gint_fused.h): greedy, longest match first. The absorbed
@@ -201,7 +201,7 @@ bool writes_tensor(int op)
 {
     return op == OP_StoreGlobal1DF32 || op == OP_StoreGlobal1DF16 || op == OP_StoreGlobal1DBF16 || op == OP_StoreGlobal1DF32Indirect ||
            op == OP_StoreGlobal2DTF32 || op == OP_StoreGlobal2DTF16 || op == OP_StoreGlobal2DTBF16 || op == OP_StoreGlobal2DWF32 ||
-           op == OP_StoreGlobal2DWF16 || op == OP_StoreGlobal2DWBF16 || op == OP_StoreGlobal1DF32Fast;
+           op == OP_StoreGlobal2DWF16 || op == OP_StoreGlobal2DWBF16 || op == OP_StoreGlobal1DF32Fast || op == OP_StoreGlobal2DWF32Fast;
 }
 
 /*
@@ -411,6 +411,61 @@ uint32_t apply_row_staging(std::vector<Insn> *prog, const gint_tensor_info &ti, 
     return staged;
 }
 
+/*
+ * Fast row accesses: the 2DW counterpart of apply_fast_accesses. A LoadGlobal2DWF32 / StoreGlobal2DWF32 becomes its Fast form
+ * (one unmasked 128-bit access per lane) when, for every logical program of the grid, all 32 rows of the tile exist, the four
+ * columns exist, and the first byte is 16-byte aligned given a 16-byte aligned base pointer: unit column stride, row stride
+ * and every per-program offset a multiple of 4 elements, column offset a multiple of 4. Slots that the program moves
+ * (AdvanceBase / AdvanceBlock2D) are left alone. Returns the mask of slots relied on (base alignment is checked per launch).
+ */
+uint32_t apply_fast_rows(std::vector<Insn> *prog, const gint_tensor_info &ti, int n_tensors)
+{
+    bool ok[GINT_MAX_TENSORS];
+    int64_t min_cols[GINT_MAX_TENSORS];
+    for (int t = 0; t < GINT_MAX_TENSORS; t++) {
+        ok[t] = false;
+        min_cols[t] = 0;
+        if (t >= n_tensors) continue;
+        const int64_t rows = ti.block_shape_stride_1[t][0], row_stride = ti.block_shape_stride_1[t][1];
+        const int64_t cols = ti.block_shape_stride_2[t][0], col_stride = ti.block_shape_stride_2[t][1];
+        const int64_t gd1 = (uint32_t)ti.block_grid_dims[t][0], gd2 = (uint32_t)ti.block_grid_dims[t][1];
+        const int64_t gs1 = ti.block_grid_steps[t][0], gs2 = ti.block_grid_steps[t][1];
+        bool good = ti.elm_size[t] == 4 && col_stride == 1 && row_stride >= 0 && (row_stride % 4) == 0 && gd1 >= 1 && gd2 >= 1 && gs1 >= 0 && gs2 >= 0 &&
+                    rows - (gd1 - 1) * gs1 >= 32 && (int64_t)31 * row_stride + cols < (1ll << 29);
+        if (good && gd1 != 1 && (gs1 * row_stride) % 4 != 0) good = false;
+        if (good && gd2 != 1 && (gs2 * col_stride) % 4 != 0) good = false;
+        for (int j = 0; good && j < 4; j++)
+            if (ti.batch_shape[t][j] != 1 && ti.batch_strides[t][j] % 4 != 0) good = false;
+        ok[t] = good;
+        min_cols[t] = cols - (gd2 - 1) * gs2;
+    }
+    for (const Insn &in : *prog)
+        if (in.op == OP_AdvanceBlock2D || in.op == OP_AdvanceBase) ok[in.operand & 7u] = false;
+    uint32_t used = 0;
+    for (Insn &in : *prog) {
+        if (in.op != OP_LoadGlobal2DWF32 && in.op != OP_StoreGlobal2DWF32) continue;
+        const int slot = (int)(in.operand & 15u);
+        const int64_t j0 = (int64_t)(in.operand >> 4);
+        if (slot >= n_tensors || slot >= 8 || !ok[slot] || (j0 & 3) != 0 || j0 + 4 > min_cols[slot] || j0 * 4 >= (1 << 26)) continue;
+        in.op = in.op == OP_LoadGlobal2DWF32 ? OP_LoadGlobal2DWF32Fast : OP_StoreGlobal2DWF32Fast;
+        in.operand = ((uint32_t)slot << 29) | (uint32_t)(j0 * 4);
+        used |= 1u << slot;
+    }
+    return used;
+}
+
+/*
+ * DupBroadcastW k -> Bcast_k: the lane index is a constant of the program, so it moves from the operand word into the opcode
+ * and the handler needs no run-time select (gint_opcodes.h). Same value in the same slot; the index was clamped to 0..3 by
+ * normalise().
+ */
+void lower_lane_moves(std::vector<Insn> *prog, int pool_size)
+{
+    if (pool_size >= 12) return;   // the 12-slot kernels carry no Bcast_k handlers (register budget, see op_valid)
+    for (Insn &in : *prog)
+        if (in.op == OP_DupBroadcastW) in = Insn{OP_Bcast_0 + (int)(in.operand & 3u), 0u};
+}
+
 /* Conservative byte extent a program can touch from a tensor's base pointer; 0 = unknown (negative strides). */
 uint64_t tensor_extent_bytes(const gint_tensor_info &ti, int t)
 {
@@ -431,6 +486,7 @@ struct Variant {
     const void *fn;   // cudaKernel_t of the loaded cubin, usable wherever the runtime takes a kernel function
     int regs;
     bool ok;
+    int resident_warps;   // warps of this kernel the whole device holds when a block needs only its minimum of shared memory
 };
 
 /* The embedded cubins are loaded once per process (a cudaLibrary_t is not tied to a device or context). */
@@ -475,6 +531,16 @@ int load_images()
     return usable;
 }
 
+struct Geometry {
+    Variant *v;
+    uint32_t smem;
+    uint32_t code_smem;
+    int blocks_per_sm;
+    uint32_t grid;
+};
+
+struct PlanMemo { bool valid; uint32_t count; int opt_k, opt_blocks; Geometry g; };
+
 struct Program {
     bool live = false;
     uint2 *code_dev = nullptr;
@@ -496,6 +562,11 @@ struct Program {
     int ring_slots = gint::kRingSlotsShallow;   // depth of the ring of early-issued loads (early-issue stream)
     uint32_t row_area_bytes = 0; // shared memory per tile for staged row blocks (early-issue stream only)
     uint64_t extent[GINT_MAX_TENSORS] = {};
+    /* host copies of the two streams when they are short enough to travel inside the kernel parameters */
+    uint2 code_inline[gint::kInlineCodeSlots];
+    uint2 early_inline[gint::kInlineCodeSlots];
+    PlanMemo memo[2] = {};      // last launch plan of the plain stream [0] and of the early-issue stream [1]
+    std::mutex memo_mu;
 };
 
 /* Which bytes of each tensor one logical program reads: the union of its tile loads along the contiguous dimension.
@@ -541,13 +612,14 @@ struct gint_ctx {
     std::mutex mu;
     std::vector<Program *> programs;
     std::vector<Variant> direct;
-    Variant indirect{12, 1, nullptr, 0, false};
+    Variant indirect{12, 1, nullptr, 0, false, 0};
     std::string last_error;
     int opt_tiles_per_warp = 0;
     int opt_max_blocks = 0;
     int opt_prefetch = 0;
     int opt_early_issue = 1;
     int opt_fuse = 1;           // applies to programs created afterwards
+    int opt_lower = 1;          // DupBroadcastW -> Bcast_k (lower_lane_moves); applies to programs created afterwards
     /* scratch for indirect launches */
     void *ind_dev = nullptr;
     void *ind_host = nullptr;
@@ -598,45 +670,75 @@ Variant *find_variant(gint_ctx *ctx, int P, int K)
     return nullptr;
 }
 
-struct Geometry {
-    Variant *v;
-    uint32_t smem;
-    uint32_t code_smem;
-    int blocks_per_sm;
-    uint32_t grid;
+
+/* What a launch runs: one of the program's two streams. The ring of early-issued loads and the staged row blocks exist only
+ * in the early-issue stream. */
+struct StreamView {
+    uint32_t n_slots;
+    uint32_t ring_bytes;       // shared memory per tile for the ring of early-issued loads
+    uint32_t row_area_bytes;   // shared memory per tile for staged row blocks
+    bool early;
 };
 
-/* the ring of early-issued loads exists only in streams that have such loads (n_early is zeroed in the launch's view of
- * the program when the plain stream runs) */
-uint32_t ring_bytes_per_tile(const Program *p) { return p->n_early > 0 ? (uint32_t)p->ring_slots * 512u : 0u; }
-
-uint32_t direct_smem(const Program *p, int K, uint32_t *code_smem)
+StreamView stream_view(const Program *p, bool early)
 {
-    const uint32_t cs = (p->n_slots * 8u + 127u) & ~127u;
-    *code_smem = cs;
-    return cs + gint::kTensorInfoSmemBytes + (uint32_t)(gint::kWarpsPerBlock * K) * (uint32_t)sizeof(gint::TileInfo) +
-           (uint32_t)(gint::kWarpsPerBlock * K) * (ring_bytes_per_tile(p) + p->row_area_bytes);
+    StreamView v;
+    v.early = early;
+    v.n_slots = early ? p->early_slots : p->n_slots;
+    v.ring_bytes = early && p->n_early > 0 ? (uint32_t)p->ring_slots * 512u : 0u;
+    v.row_area_bytes = early ? p->row_area_bytes : 0u;
+    return v;
 }
 
-int plan_direct(gint_ctx *ctx, const Program *p, uint32_t count, Geometry *g)
+uint32_t direct_smem(const StreamView &v, int K, uint32_t *code_smem)
+{
+    const uint32_t cs = (v.n_slots * 8u + 127u) & ~127u;
+    *code_smem = cs;
+    return cs + gint::kTensorInfoSmemBytes + (uint32_t)(gint::kWarpsPerBlock * K) * (uint32_t)sizeof(gint::TileInfo) +
+           (uint32_t)(gint::kWarpsPerBlock * K) * (v.ring_bytes + v.row_area_bytes);
+}
+
+/* Blocks needed to give every group of K logical programs a warp. */
+uint64_t blocks_for(uint32_t count, int K)
+{
+    const uint64_t groups = ((uint64_t)count + (uint64_t)K - 1) / (uint64_t)K;
+    return (groups + gint::kWarpsPerBlock - 1) / gint::kWarpsPerBlock;
+}
+
+int plan_direct(gint_ctx *ctx, const Program *p, const StreamView &sv, uint32_t count, Geometry *g)
 {
     const int P = p->st.pool_size;
     const int ks[3] = {4, 2, 1};
+    /* upper bound on K: the option if set; else 2 (measured: 4 tiles per warp lose more to the lower occupancy of the
+     * 96-register kernels than they gain from amortised dispatch), and 1 for programs that are bound by memory instructions
+     * rather than by dispatch: those in which at least 2 of 5 instructions access memory (measured on RMSNorm rows: load/store
+     * issue is not amortised by more tiles per warp) and those in which at least 1 of 5 instructions is a load that is not
+     * issued early (measured on the batched 4x4 product: its latency is hidden only by more resident warps, which the
+     * narrower kernel gives) */
+    int k_max = ctx->opt_tiles_per_warp ? ctx->opt_tiles_per_warp : p->prefer_narrow ? 1 : 2;
+    /* A short program whose whole grid is gone after at most two rounds of the resident warps is bound by latency, not
+     * throughput: what it waits for is a fixed per-block cost (block start, program staging, descriptor decode) and one or
+     * two memory round trips per warp. Fewer, fatter blocks are then faster as long as every SM still gets two of them
+     * (measured on a+b over 2^20 elements, device time: 7.1 / 6.3 / 5.9 us at 1 / 2 / 4 tiles per warp). */
+    bool latency_bound = false;
+    if (!ctx->opt_tiles_per_warp && sv.n_slots <= (uint32_t)gint::kInlineCodeSlots) {
+        Variant *v1 = find_variant(ctx, P, 1);
+        if (v1 && v1->resident_warps > 0 && (uint64_t)count <= 2ull * (uint64_t)v1->resident_warps) {
+            latency_bound = true;
+            k_max = 1;
+            for (int K : ks)
+                if (find_variant(ctx, P, K) && blocks_for(count, K) >= 2ull * (uint64_t)ctx->num_sms) { k_max = K; break; }
+        }
+    }
     Geometry best{};
     bool have = false;
     for (int K : ks) {
-        /* upper bound on K: the option if set; else 2 (measured: 4 tiles per warp lose more to the lower occupancy of
-         * the 96-register kernels than they gain from amortised dispatch), and 1 for programs that are bound by memory
-         * instructions rather than by dispatch: those in which at least 2 of 5 instructions access memory (measured on
-         * RMSNorm rows: load/store issue is not amortised by more tiles per warp) and those in which at least 1 of 5
-         * instructions is a load that is not issued early (measured on the batched 4x4 product: its latency is hidden only
-         * by more resident warps, which the narrower kernel gives) */
-        if (K > (ctx->opt_tiles_per_warp ? ctx->opt_tiles_per_warp : p->prefer_narrow ? 1 : 2)) continue;
+        if (K > k_max) continue;
         Variant *v = find_variant(ctx, P, K);
         if (!v) continue;
         Geometry c{};
         c.v = v;
-        c.smem = direct_smem(p, K, &c.code_smem);
+        c.smem = direct_smem(sv, K, &c.code_smem);
         if ((int)c.smem > ctx->max_smem_optin) continue;
         if (c.smem > 48u * 1024u) {
             cudaError_t e = cudaFuncSetAttribute(v->fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)c.smem);
@@ -651,15 +753,14 @@ int plan_direct(gint_ctx *ctx, const Program *p, uint32_t count, Geometry *g)
          * lose to exposed latency. Rows of 4 KB (the conductor graph) stay below that bound at full occupancy. */
         while (bps > 4 && (uint64_t)p->reread_bytes * (uint64_t)(K * gint::kWarpsPerBlock) * (uint64_t)ctx->num_sms * (uint64_t)bps > 50000000ull) bps--;
         c.blocks_per_sm = bps;
-        const uint64_t groups = ((uint64_t)count + (uint64_t)K - 1) / (uint64_t)K;
-        uint64_t blocks_needed = (groups + gint::kWarpsPerBlock - 1) / gint::kWarpsPerBlock;
+        const uint64_t blocks_needed = blocks_for(count, K);
         uint64_t resident = (uint64_t)bps * (uint64_t)ctx->num_sms;
         if (ctx->opt_max_blocks > 0 && (uint64_t)ctx->opt_max_blocks < resident) resident = (uint64_t)ctx->opt_max_blocks;
         c.grid = (uint32_t)(blocks_needed < resident ? blocks_needed : resident);
         if (c.grid == 0) c.grid = 1;
         if (!have) { best = c; have = true; }
         /* take the widest K that still fills the machine with at least one group per resident warp */
-        if (blocks_needed >= resident || ctx->opt_tiles_per_warp) { best = c; break; }
+        if (blocks_needed >= resident || ctx->opt_tiles_per_warp || latency_bound) { best = c; break; }
         best = c;  // fewer groups than warps: prefer the narrower variant (more warps busy)
     }
     if (!have) return fail(ctx, GINT_ERR_TOO_LARGE, "no kernel variant fits this program (shared memory)");
@@ -681,6 +782,7 @@ int launch_direct(gint_ctx *ctx, uint64_t handle, const uint64_t *base_ptrs, int
      * addresses, one of the tensors those stores write. */
     bool early = ctx->opt_early_issue && p->early_dev != nullptr;
     for (int t = 0; early && t < n_tensors; t++) {
+        if (!p->alias_slots[t]) continue;
         for (int b = 0; early && b < n_tensors; b++) {
             if (!((p->alias_slots[t] >> b) & 1u)) continue;
             const uint64_t a0 = base_ptrs[t], a1 = a0 + p->extent[t], b0 = base_ptrs[b], b1 = b0 + p->extent[b];
@@ -689,38 +791,39 @@ int launch_direct(gint_ctx *ctx, uint64_t handle, const uint64_t *base_ptrs, int
     }
     for (int t = 0; early && t < n_tensors; t++)
         if (((p->fast_slots >> t) & 1u) && (base_ptrs[t] & 15u) != 0) early = false;   // fast accesses need aligned bases
-    Program view = *p;   // geometry depends on the stream length
-    if (early) view.n_slots = p->early_slots;
-    else { view.row_area_bytes = 0; view.n_early = 0; }
+    const StreamView sv = stream_view(p, early);   // geometry depends on the stream
     Geometry g;
     {
-        /* the calling thread's last plan is reused while nothing it depends on changes: saves the occupancy query */
-        struct Memo { gint_ctx *ctx; uint64_t uid; uint32_t count, n_slots; int opt_k, opt_blocks; bool early; Geometry g; };
-        static thread_local Memo memo = {nullptr, 0, 0, 0, 0, 0, false, {}};
-        if (memo.ctx == ctx && memo.uid == p->uid && memo.count == count && memo.n_slots == view.n_slots &&
-            memo.opt_k == ctx->opt_tiles_per_warp && memo.opt_blocks == ctx->opt_max_blocks && memo.early == early) {
-            g = memo.g;
+        /* each program remembers its last plan per stream: a launch that repeats the previous one's size skips the occupancy
+         * queries (several microseconds), also when the caller alternates between programs */
+        PlanMemo &m = p->memo[early ? 1 : 0];
+        std::lock_guard<std::mutex> lk(p->memo_mu);
+        if (m.valid && m.count == count && m.opt_k == ctx->opt_tiles_per_warp && m.opt_blocks == ctx->opt_max_blocks) {
+            g = m.g;
         } else {
-            int rc = plan_direct(ctx, &view, count, &g);
+            int rc = plan_direct(ctx, p, sv, count, &g);
             if (rc != GINT_OK) return rc;
-            memo = Memo{ctx, p->uid, count, view.n_slots, ctx->opt_tiles_per_warp, ctx->opt_max_blocks, early, g};
+            m = PlanMemo{true, count, ctx->opt_tiles_per_warp, ctx->opt_max_blocks, g};
         }
     }
     LaunchArgs a;
-    a.code = early ? p->early_dev : p->code_dev;
-    a.n_slots = view.n_slots;
+    const bool inline_code = sv.n_slots <= (uint32_t)gint::kInlineCodeSlots;
+    a.code = inline_code ? nullptr : (early ? p->early_dev : p->code_dev);
+    a.n_slots = sv.n_slots;
     a.n_tensors = (uint32_t)p->n_tensors;
     a.first = first;
     a.end = first + count;
     a.code_smem_bytes = g.code_smem;
     a.prefetch_mask = ctx->opt_prefetch ? p->prefetch_mask : 0u;
     a.zero = 0;
-    a.row_area_bytes = view.row_area_bytes;
-    a.ring_bytes = ring_bytes_per_tile(&view);
+    a.row_area_bytes = sv.row_area_bytes;
+    a.ring_bytes = sv.ring_bytes;
     a.reserved = 0;
-    for (int t = 0; t < GINT_MAX_TENSORS; t++) a.fp[t] = p->fp[t];
+    if (a.prefetch_mask)
+        for (int t = 0; t < GINT_MAX_TENSORS; t++) a.fp[t] = p->fp[t];
     a.ti = p->ti;
     for (int i = 0; i < n_tensors; i++) a.ti.base_ptr[i] = (int64_t)base_ptrs[i];
+    if (inline_code) memcpy(a.inline_code, early ? p->early_inline : p->code_inline, sizeof(a.inline_code));
     void *args[1] = {&a};
     cudaError_t e = cudaLaunchKernel(g.v->fn, dim3(g.grid), dim3(gint::kThreadsPerBlock), args, g.smem, (cudaStream_t)stream);
     if (e != cudaSuccess) return fail(ctx, GINT_ERR_CUDA, "cudaLaunchKernel", e);
@@ -853,14 +956,21 @@ int gint_create(int device, gint_ctx **out)
     for (auto &im : g_images) {
         if (!im.loaded) continue;
         if (im.K == 0) ctx->indirect.fn = (const void *)im.kernel;
-        else ctx->direct.push_back(Variant{im.P, im.K, (const void *)im.kernel, 0, false});
+        else ctx->direct.push_back(Variant{im.P, im.K, (const void *)im.kernel, 0, false, 0});
     }
     int usable = 0;
     for (auto &v : ctx->direct) {
         cudaFuncAttributes attr;
         cudaError_t e = cudaFuncGetAttributes(&attr, v.fn);
-        if (e == cudaSuccess) { v.regs = attr.numRegs; v.ok = true; usable++; }
-        else cudaGetLastError();
+        if (e == cudaSuccess) {
+            v.regs = attr.numRegs;
+            v.ok = true;
+            usable++;
+            int bps = 0;
+            if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&bps, v.fn, gint::kThreadsPerBlock, 2048) == cudaSuccess)
+                v.resident_warps = bps * ctx->num_sms * gint::kWarpsPerBlock;
+            else cudaGetLastError();
+        } else cudaGetLastError();
     }
     if (ctx->indirect.fn) {
         cudaFuncAttributes attr;
@@ -907,6 +1017,9 @@ int gint_program_create(gint_ctx *ctx, const int32_t *code, int n_words, const g
         std::vector<Insn> plain;
         int rc = normalise(code, n_words, n_tensors, &plain);
         if (rc != GINT_OK) return fail(ctx, rc, gint_status_string(rc));
+        gint_bytecode_stats st0;
+        analyze(code, n_words, &st0);
+        if (ctx->opt_lower) lower_lane_moves(&plain, st0.pool_size);
         if (ctx->opt_fuse) fuse_sequences(&plain);
         emit_stream(plain, &pre);
     }
@@ -935,7 +1048,13 @@ int gint_program_create(gint_ctx *ctx, const int32_t *code, int n_words, const g
             staged = apply_row_staging(&ei.prog, p->ti, n_tensors, &row_area, ei.alias_slots);
             for (const Insn &in : ei.prog) n_staged_loads += in.op == OP_LoadStagedRows;
         }
-        bool usable = ei.n_early > 0 || staged != 0;
+        /* fast row accesses are tried on a copy: they count only if the early stream is used at all */
+        uint32_t fast_rows = 0;
+        {
+            std::vector<Insn> probe = ei.prog;
+            fast_rows = apply_fast_rows(&probe, p->ti, n_tensors);
+        }
+        bool usable = ei.n_early > 0 || staged != 0 || fast_rows != 0;
         /* A slot that the program moves (AdvanceBase / AdvanceBlock2D) reaches beyond the extent its descriptor gives, so
          * the launch-time overlap check cannot bound it: a program that pairs such a slot with a moved load keeps the
          * stream as written. */
@@ -950,8 +1069,9 @@ int gint_program_create(gint_ctx *ctx, const int32_t *code, int n_words, const g
                 if ((ei.alias_slots[t] >> b) & 1u) { if (tensor_extent_bytes(p->ti, b) == 0 || ((advanced >> b) & 1u)) usable = false; }
         }
         if (usable) {
-            p->fast_slots = apply_fast_accesses(&ei.prog, p->ti, n_tensors) | staged;
+            p->fast_slots = apply_fast_accesses(&ei.prog, p->ti, n_tensors) | apply_fast_rows(&ei.prog, p->ti, n_tensors) | staged;
             p->row_area_bytes = row_area;
+            if (ctx->opt_lower) lower_lane_moves(&ei.prog, p->st.pool_size);
             if (ctx->opt_fuse) fuse_sequences(&ei.prog);
             emit_stream(ei.prog, &early);
             p->n_early = ei.n_early;
@@ -980,6 +1100,11 @@ int gint_program_create(gint_ctx *ctx, const int32_t *code, int n_words, const g
         const int n_insns = (int)prog.size(), n_direct = n_loads - (usable ? ei.n_early + n_staged_loads : 0);
         p->prefer_narrow = 5 * n_mem >= 2 * n_insns || 5 * n_direct >= n_insns;
     }
+    p->early_slots = (uint32_t)early.size();
+    for (int i = 0; i < gint::kInlineCodeSlots; i++) {
+        p->code_inline[i] = (size_t)i < pre.size() ? pre[(size_t)i] : make_uint2(0u, OP_Halt);
+        p->early_inline[i] = (size_t)i < early.size() ? early[(size_t)i] : make_uint2(0u, OP_Halt);
+    }
     {
         DeviceGuard guard(ctx->device);
         cudaError_t e = cudaMalloc(&p->code_dev, pre.size() * sizeof(uint2));
@@ -995,7 +1120,6 @@ int gint_program_create(gint_ctx *ctx, const int32_t *code, int n_words, const g
                 delete p;
                 return fail(ctx, GINT_ERR_OUT_OF_MEMORY, "cudaMalloc/cudaMemcpy(early-issue program)", e);
             }
-            p->early_slots = (uint32_t)early.size();
         }
     }
     p->live = true;
@@ -1030,7 +1154,8 @@ int gint_program_launch_info(gint_ctx *ctx, uint64_t handle, uint32_t grid_dim, 
     if (!p) return fail(ctx, GINT_ERR_BAD_HANDLE, "unknown program handle");
     DeviceGuard guard(ctx->device);
     Geometry g;
-    int rc = plan_direct(ctx, p, grid_dim ? grid_dim : 1, &g);
+    const StreamView sv = stream_view(p, ctx->opt_early_issue && p->early_dev != nullptr);
+    int rc = plan_direct(ctx, p, sv, grid_dim ? grid_dim : 1, &g);
     if (rc != GINT_OK) return rc;
     memset(out, 0, sizeof(*out));
     out->pool_size = g.v->P;
@@ -1269,10 +1394,23 @@ int gint_debug_transform(const int32_t *code, int n_words, const gint_tensor_inf
             gint_tensor_info t0 = *ti;
             uint32_t row_area = 0, staged = 0;
             if (ei.n_early == 0) staged = apply_row_staging(&prog, t0, n_tensors, &row_area, ei.alias_slots);
-            if (ei.n_early > 0 || staged) apply_fast_accesses(&prog, t0, n_tensors);
+            uint32_t rows_fast = 0;
+            {
+                std::vector<Insn> probe = prog;
+                rows_fast = apply_fast_rows(&probe, t0, n_tensors);
+            }
+            if (ei.n_early > 0 || staged || rows_fast) {
+                apply_fast_accesses(&prog, t0, n_tensors);
+                apply_fast_rows(&prog, t0, n_tensors);
+            }
         }
     }
-    if (fuse) fuse_sequences(&prog);
+    if (fuse) {
+        gint_bytecode_stats st0;
+        analyze(code, n_words, &st0);
+        lower_lane_moves(&prog, st0.pool_size);
+        fuse_sequences(&prog);
+    }
     if ((int)prog.size() > max_insns) return GINT_ERR_INVALID_ARGUMENT;
     for (size_t i = 0; i < prog.size(); i++) {
         if (out_ops) out_ops[i] = prog[i].op == OP_CARRIER_UNUSED ? OP_CARRIER : prog[i].op;
@@ -1303,6 +1441,10 @@ int gint_set_option(gint_ctx *ctx, const char *name, int value)
     }
     if (strcmp(name, "fuse") == 0) {
         ctx->opt_fuse = value != 0;
+        return GINT_OK;
+    }
+    if (strcmp(name, "lower") == 0) {
+        ctx->opt_lower = value != 0;
         return GINT_OK;
     }
     if (strcmp(name, "early_issue") == 0) {

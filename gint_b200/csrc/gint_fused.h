@@ -9,7 +9,7 @@
  * in the same order on the same slots; only the dispatches in between disappear.
  *
  * The sequences below are the idioms of the gint frontend and conductor lowerings: the chunk bodies of row reductions and
- * of scale-and-store loops, SiLU, the width-lane combine after a warp reduction, and the inner step of the 4x4 matmul.
+ * of scale-and-store loops, SiLU, and the inner step and row end of the 4x4 matmul.
  * 1-D loads appear in the two flavours the early-issue transformation (gint_capi.cu) produces for provably full, aligned
  * tiles before fusion runs: taken from the ring while the next one is started, and taken without a successor.
  *
@@ -23,7 +23,7 @@
 
 #include "gint_opcodes.h"
 
-#define GINT_FUSED_FIRST 116
+#define GINT_FUSED_FIRST 122
 
 /* one entry per load flavour L for the 1-D idioms */
 #define GINT_FUSED_1D(X, base, L)                                                        \
@@ -36,29 +36,33 @@
     X(base + 6, 3, L, OP_FAdd, OP_StoreGlobal1DF32Fast)
 
 #define GINT_FUSED_LIST(X)                                                               \
-    GINT_FUSED_1D(X, 116, OP_PfTakeIssue1DFast)                                          \
-    GINT_FUSED_1D(X, 123, OP_PfTake)                                                     \
-    X(130, 4, OP_DupBroadcastW, OP_LoadGlobal2DWF32, OP_FMul, OP_Swap)   /* bmm inner step */ \
-    X(131, 5, OP_Dup, OP_FNeg, OP_FExp, OP_FAddImm, OP_FRDiv)            /* SiLU      */ \
-    X(132, 3, OP_Dup, OP_FPermW, OP_FAdd)                                /* width combine */ \
-    X(133, 5, OP_Pop, OP_FAdd, OP_FAdd, OP_FAdd, OP_StoreGlobal2DWF32)   /* bmm row end */ \
-    X(134, 2, OP_FMul, OP_FAdd)                                                          \
-    X(135, 2, OP_FMul, OP_StoreGlobal1DF32Fast)                                          \
+    GINT_FUSED_1D(X, GINT_FUSED_FIRST + 0, OP_PfTakeIssue1DFast)                         \
+    GINT_FUSED_1D(X, GINT_FUSED_FIRST + 7, OP_PfTake)                                    \
+    X(GINT_FUSED_FIRST + 14, 5, OP_Dup, OP_FNeg, OP_FExp, OP_FAddImm, OP_FRDiv)          /* SiLU      */ \
+    X(GINT_FUSED_FIRST + 15, 5, OP_Pop, OP_FAdd, OP_FAdd, OP_FAdd, OP_StoreGlobal2DWF32)   /* bmm row end */ \
+    X(GINT_FUSED_FIRST + 16, 5, OP_Pop, OP_FAdd, OP_FAdd, OP_FAdd, OP_StoreGlobal2DWF32Fast) \
+    X(GINT_FUSED_FIRST + 17, 2, OP_FMul, OP_FAdd)                                        \
+    X(GINT_FUSED_FIRST + 18, 2, OP_FMul, OP_StoreGlobal1DF32Fast)                        \
     /* whole chunk bodies: two reduction steps; scale by s and by w, store; the same without the store; SiLU, add, store */ \
-    X(136, 8, OP_PfTakeIssue1DFast, OP_Dup, OP_FMul, OP_FAdd, OP_PfTakeIssue1DFast, OP_Dup, OP_FMul, OP_FAdd) \
-    X(137, 7, OP_Dup, OP_PfTakeIssue1DFast, OP_Swap, OP_FMul, OP_PfTakeIssue1DFast, OP_FMul, OP_StoreGlobal1DF32Fast) \
-    X(138, 6, OP_Dup, OP_PfTakeIssue1DFast, OP_Swap, OP_FMul, OP_PfTakeIssue1DFast, OP_FMul) \
-    X(139, 8, OP_Dup, OP_FNeg, OP_FExp, OP_FAddImm, OP_FRDiv, OP_PfTakeIssue1DFast, OP_FAdd, OP_StoreGlobal1DF32Fast) \
-    X(140, 4, OP_PfTakeIssue1DFast, OP_FAdd, OP_PfTakeIssue1DFast, OP_FAdd)                \
-    X(141, 4, OP_DupBroadcastW, OP_LoadStagedRows, OP_FMul, OP_Swap)     /* bmm inner step, staged rows */
+    X(GINT_FUSED_FIRST + 19, 8, OP_PfTakeIssue1DFast, OP_Dup, OP_FMul, OP_FAdd, OP_PfTakeIssue1DFast, OP_Dup, OP_FMul, OP_FAdd) \
+    X(GINT_FUSED_FIRST + 20, 7, OP_Dup, OP_PfTakeIssue1DFast, OP_Swap, OP_FMul, OP_PfTakeIssue1DFast, OP_FMul, OP_StoreGlobal1DF32Fast) \
+    X(GINT_FUSED_FIRST + 21, 6, OP_Dup, OP_PfTakeIssue1DFast, OP_Swap, OP_FMul, OP_PfTakeIssue1DFast, OP_FMul) \
+    X(GINT_FUSED_FIRST + 22, 8, OP_Dup, OP_FNeg, OP_FExp, OP_FAddImm, OP_FRDiv, OP_PfTakeIssue1DFast, OP_FAdd, OP_StoreGlobal1DF32Fast) \
+    X(GINT_FUSED_FIRST + 23, 4, OP_PfTakeIssue1DFast, OP_FAdd, OP_PfTakeIssue1DFast, OP_FAdd)                \
+    /* inner step of the 4x4 product over staged rows, one per broadcast lane */         \
+    X(GINT_FUSED_FIRST + 24, 4, OP_Bcast_0, OP_LoadStagedRows, OP_FMul, OP_Swap)         \
+    X(GINT_FUSED_FIRST + 25, 4, OP_Bcast_1, OP_LoadStagedRows, OP_FMul, OP_Swap)         \
+    X(GINT_FUSED_FIRST + 26, 4, OP_Bcast_2, OP_LoadStagedRows, OP_FMul, OP_Swap)         \
+    X(GINT_FUSED_FIRST + 27, 4, OP_Bcast_3, OP_LoadStagedRows, OP_FMul, OP_Swap)
 
-#define GINT_N_FUSED 26
-#define GINT_N_DISPATCH_ALL (GINT_FUSED_FIRST + GINT_N_FUSED)   /* 142 */
+#define GINT_N_FUSED 28
+#define GINT_N_DISPATCH_ALL (GINT_FUSED_FIRST + GINT_N_FUSED)   /* 150 */
 #define GINT_MAX_FUSED_LEN 8
 
 /* does the instruction read its operand word? (fused handlers fetch operands only for those that do) */
 #define GINT_OP_USES_OPERAND(op)                                                                                           \
     (((op) >= OP_LoadImm && (op) <= OP_LoadGlobal1DU8) || (op) == OP_FApprox || ((op) >= OP_LoadGlobal1DF32Indirect && (op) <= OP_DupBroadcastW) || \
-     (op) == OP_FPermW || (op) == OP_FShuf2 || (op) == OP_PfIssue1D || (op) == OP_PfTakeIssue1D || (op) == OP_PfSkip || ((op) >= OP_LoadGlobal1DF32Fast && (op) <= OP_LoadStagedRows))
+     (op) == OP_FPermW || (op) == OP_FShuf2 || (op) == OP_PfIssue1D || (op) == OP_PfTakeIssue1D || (op) == OP_PfSkip || ((op) >= OP_LoadGlobal1DF32Fast && (op) <= OP_LoadStagedRows) || \
+     (op) == OP_LoadGlobal2DWF32Fast || (op) == OP_StoreGlobal2DWF32Fast)
 
 #endif /* GINT_FUSED_H */

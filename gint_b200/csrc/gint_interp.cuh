@@ -380,6 +380,14 @@ template <int P, int K> __device__ __forceinline__ void pool_declare()
     asm volatile(".reg .b64 %%gs<%0>;" ::"n"(2 * P * K));
 }
 
+/* A packed pair assembled from two lanes of a slot chosen by immediate operands (Bcast_k, gint_opcodes.h): the four lanes of the
+ * source slot are named a0..a3 inside a PTX scope -- register moves only, no selects. */
+template <int DST, int SRC_LO, int SRC_HI, int I, int J> __device__ __forceinline__ void r_pick()
+{
+    asm volatile("{\n\t.reg .b32 a<4>;\n\tmov.b64 {a0, a1}, %%gs%1;\n\tmov.b64 {a2, a3}, %%gs%2;\n\tmov.b64 %%gs%0, {a%3, a%4};\n\t}"
+                 ::"n"(DST), "n"(SRC_LO), "n"(SRC_HI), "n"(I), "n"(J));
+}
+
 template <int I> __device__ __forceinline__ void r_get(float &x, float &y)
 {
     asm volatile("mov.b64 {%0, %1}, %%gs%2;" : "=f"(x), "=f"(y) : "n"(I));
@@ -467,7 +475,44 @@ struct Ctx {
     uint32_t ring_mask; // bytes of the warp's ring of early-issued loads (4 or 8 slots of K x 512 bytes) minus 1
     uint32_t rows;     // shared-memory address of this warp's staged row blocks (tile 0); tile k is rows_stride bytes further
     uint32_t rows_stride;
+    const LaunchArgs *args;   // the launch parameters (direct mode), for the kernels that derive the four values above on demand
 };
+
+/* The widest kernels (12 slots x 2 tiles = 96 pool registers) have about a dozen registers left for everything else, and the
+ * handlers with the most temporaries (runtime lane selects) spilled. They do not keep hidden / ring_mask / rows / rows_stride
+ * in registers between handlers: the few handlers that need them recompute them from the launch parameters (constant bank)
+ * and the warp index. */
+template <int P, int K> __host__ __device__ constexpr bool lean_ctx() { return P * K >= 24; }
+
+/* shared-memory address of the first byte after the block's tile descriptors (see geval_direct_body for the layout) */
+template <int K> __device__ __forceinline__ uint32_t cx_after_tiles(const Ctx &cx, uint32_t warp)
+{
+    return (uint32_t)__cvta_generic_to_shared(cx.tiles) + ((uint32_t)kWarpsPerBlock - warp) * (uint32_t)(K * sizeof(TileInfo));
+}
+template <int P, int K> __device__ __forceinline__ uint32_t cx_ring_mask(const Ctx &cx)
+{
+    if constexpr (lean_ctx<P, K>()) return (uint32_t)K * cx.args->ring_bytes - 1u;
+    else return cx.ring_mask;
+}
+template <int P, int K> __device__ __forceinline__ uint32_t cx_rows_stride(const Ctx &cx)
+{
+    if constexpr (lean_ctx<P, K>()) return cx.args->row_area_bytes;
+    else return cx.rows_stride;
+}
+template <int P, int K> __device__ __forceinline__ uint32_t cx_hidden(const Ctx &cx)
+{
+    if constexpr (lean_ctx<P, K>()) {
+        const uint32_t warp = threadIdx.x >> 5;
+        return cx_after_tiles<K>(cx, warp) + warp * (uint32_t)K * cx.args->ring_bytes + (uint32_t)cx.lane * 4u;
+    } else return cx.hidden;
+}
+template <int P, int K> __device__ __forceinline__ uint32_t cx_rows(const Ctx &cx)
+{
+    if constexpr (lean_ctx<P, K>()) {
+        const uint32_t warp = threadIdx.x >> 5;
+        return cx_after_tiles<K>(cx, warp) + (uint32_t)(kWarpsPerBlock * K) * cx.args->ring_bytes + warp * (uint32_t)K * cx.args->row_area_bytes;
+    } else return cx.rows;
+}
 
 template <int OP> struct OpInfo;
 #define GINT_X_INFO(name, num, md, net) \
@@ -537,6 +582,9 @@ template <int OP, int SP, int P> __host__ __device__ constexpr bool op_valid()
         if (SP > limit || SP < OpInfo<OP>::min_depth) return false;
         if (SP + OpInfo<OP>::net_effect > limit) return false;
         if (OP == OP_DupX2 && SP + 1 > limit) return false;
+        /* The 12-slot kernels have no Bcast_k handlers (the host keeps DupBroadcastW there): with them the two-tile kernel no
+         * longer fits its 128 registers and the assembler moves pool registers to local memory, which every program pays for. */
+        if (OP >= OP_Bcast_0 && OP <= OP_Bcast_3 && P >= 12) return false;
         if (OP >= OP_FLoadReg0 && OP <= OP_FLoadReg7 && (P - 1 - (OP - OP_FLoadReg0)) < 0) return false;
         if (OP >= OP_FStoreReg0 && OP <= OP_FStoreReg7 && (P - 1 - (OP - OP_FStoreReg0)) < 0) return false;
         return true;
@@ -774,6 +822,11 @@ __device__ __forceinline__ void exec_tile(const uint32_t operand, const Ctx &cx)
         const float o[4] = {sel4(v1, operand), sel4(v1, operand >> 8), sel4(v2, operand >> 16), sel4(v2, operand >> 24)};
         slot_write<K, T - 1, KI>(o);
     }
+    /* ---- DupBroadcastW with the lane index built into the opcode (see gint_opcodes.h) ---- */
+    else if constexpr (OP >= OP_Bcast_0 && OP <= OP_Bcast_3) {
+        r_pick<LO(SP), LO(T), HI(T), (OP - OP_Bcast_0), (OP - OP_Bcast_0)>();
+        r_mov<HI(SP), LO(SP)>();
+    }
     /* ---- virtual registers: reg n = pool[P-1-n] (state.py:38-41, reg.py:7-59) ---- */
     else if constexpr (OP >= OP_FLoadReg0 && OP <= OP_FLoadReg7) {
         slot_mov<K, SP, P - 1 - (OP - OP_FLoadReg0), KI>();
@@ -809,6 +862,17 @@ __device__ __forceinline__ void exec_tile(const uint32_t operand, const Ctx &cx)
                      "mov.b64 {t0, t1}, %%gs%0;\n\tmov.b64 {t2, t3}, %%gs%1;\n\t"
                      "st.global.b32 [%2], t0;\n\tst.global.b32 [%2+128], t1;\n\tst.global.b32 [%2+256], t2;\n\tst.global.b32 [%2+384], t3;\n\t}"
                      ::"n"(LO(T)), "n"(HI(T)), "l"(p) : "memory");
+    } else if constexpr (OP == OP_LoadGlobal2DWF32Fast || OP == OP_StoreGlobal2DWF32Fast) {
+        /* a 2DW row access that the host proved full, unmasked and 16-byte aligned for every logical program: lane = row,
+         * four consecutive floats. Operand as for the 1-D fast accesses: {8 * slot in bits 26..31, byte offset of the column};
+         * the row stride comes from the tile descriptor. */
+        const TileInfo *ti = cx.tiles + KI;
+        const int stride1 = *reinterpret_cast<const int *>(reinterpret_cast<const char *>(ti->s1) + (operand >> 26) + 4);
+        char *p = fast_tile_address(ti, operand) + (long long)(cx.lane * stride1) * 4;
+        if constexpr (OP == OP_LoadGlobal2DWF32Fast)
+            asm volatile("ld.global.v2.b64 {%%gs%0, %%gs%1}, [%2];" ::"n"(LO(SP)), "n"(HI(SP)), "l"(p) : "memory");
+        else
+            asm volatile("st.global.v2.b64 [%2], {%%gs%0, %%gs%1};" ::"n"(LO(T)), "n"(HI(T)), "l"(p) : "memory");
     } else if constexpr (MemOp<OP>::is) {
         float v[4];
         if constexpr (MemOp<OP>::store) {
@@ -850,7 +914,7 @@ __device__ __forceinline__ void exec_all(const uint32_t operand, const Ctx &cx, 
         const uint32_t lq = (operand >> 3) & 3u, area = (operand >> 8) & 0xFFFFu;
         auto one = [&](int ki) {
             const char *src = reinterpret_cast<const char *>(cx.tiles[ki].ptr[operand & 7u]) + cx.lane * 16;
-            const uint32_t dst = cx.rows + (uint32_t)ki * cx.rows_stride + area;
+            const uint32_t dst = cx_rows<P, K>(cx) + (uint32_t)ki * cx_rows_stride<P, K>(cx) + area;
             for (uint32_t i = 0; i < (1u << lq); i++) {
                 const uint32_t c = i * 32u + (uint32_t)cx.lane, m = c >> lq, r = c & ((1u << lq) - 1u);
                 asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + staged_row_position(m, r, lq) * 16u), "l"(src + i * 512u) : "memory");
@@ -863,8 +927,9 @@ __device__ __forceinline__ void exec_all(const uint32_t operand, const Ctx &cx, 
         const uint32_t lq = operand & 3u, part = (operand >> 2) & 3u, area = (operand >> 8) & 0xFFFFu;
         asm volatile("cp.async.wait_group 0;" ::: "memory");
         __syncwarp();
-        const uint32_t at = cx.rows + area + staged_row_position((uint32_t)cx.lane, part, lq) * 16u;
-        (take_rows<K, SP, KI>(at + (uint32_t)KI * cx.rows_stride), ...);
+        const uint32_t at = cx_rows<P, K>(cx) + area + staged_row_position((uint32_t)cx.lane, part, lq) * 16u;
+        const uint32_t rows_stride = cx_rows_stride<P, K>(cx);
+        (take_rows<K, SP, KI>(at + (uint32_t)KI * rows_stride), ...);
     } else if constexpr ((OP >= OP_PfTake && OP <= OP_PfSkip) || OP == OP_PfIssue1DFast || OP == OP_PfTakeIssue1DFast) {
         /* Early-issued loads. One cp.async group per load (all K tiles together). When load n is taken, the D-1 loads
          * after it are in flight, so "all but the newest D-1 groups have landed" is exactly "load n has landed"; a plain
@@ -872,12 +937,13 @@ __device__ __forceinline__ void exec_all(const uint32_t operand, const Ctx &cx, 
         constexpr bool take = OP == OP_PfTake || OP == OP_PfTakeIssue1D || OP == OP_PfTakeIssue1DFast;
         uint32_t ring;
         asm volatile("mov.b32 %0, %%gring;" : "=r"(ring));
-        const uint32_t slot = cx.hidden + ring;
+        const uint32_t slot = cx_hidden<P, K>(cx) + ring;
+        const uint32_t ring_mask = cx_ring_mask<P, K>(cx);
         /* the ring has D = 4 or 8 slots, chosen per program by the host (long rows gain from the deeper one); the wait
          * count is an immediate of the instruction, hence the (warp-uniform) branch */
         if constexpr (OP == OP_PfTake) asm volatile("cp.async.wait_group 0;" ::: "memory");
         else if constexpr (take) {
-            if (cx.ring_mask & (uint32_t)(K * 2048)) asm volatile("cp.async.wait_group 7;" ::: "memory");
+            if (ring_mask & (uint32_t)(K * 2048)) asm volatile("cp.async.wait_group 7;" ::: "memory");
             else asm volatile("cp.async.wait_group 3;" ::: "memory");
         }
         if constexpr (take) {
@@ -887,8 +953,8 @@ __device__ __forceinline__ void exec_all(const uint32_t operand, const Ctx &cx, 
         if constexpr (OP == OP_PfIssue1D || OP == OP_PfTakeIssue1D) (tile_issue<K, KI>(cx.tiles + KI, operand, cx, slot), ...);
         if constexpr (OP == OP_PfIssue1DFast || OP == OP_PfTakeIssue1DFast) (tile_issue_fast<K, KI>(cx.tiles + KI, operand, cx, slot), ...);
         if constexpr (OP != OP_PfTake && OP != OP_PfSkip) asm volatile("cp.async.commit_group;" ::: "memory");
-        if constexpr (OP == OP_PfSkip) asm volatile("mad.lo.u32 %%gring, %0, %1, %%gring;\n\tand.b32 %%gring, %%gring, %2;" ::"r"(operand), "n"(K * 512), "r"(cx.ring_mask));
-        else asm volatile("add.u32 %%gring, %%gring, %0;\n\tand.b32 %%gring, %%gring, %1;" ::"n"(K * 512), "r"(cx.ring_mask));
+        if constexpr (OP == OP_PfSkip) asm volatile("mad.lo.u32 %%gring, %0, %1, %%gring;\n\tand.b32 %%gring, %%gring, %2;" ::"r"(operand), "n"(K * 512), "r"(ring_mask));
+        else asm volatile("add.u32 %%gring, %%gring, %0;\n\tand.b32 %%gring, %%gring, %1;" ::"n"(K * 512), "r"(ring_mask));
     } else {
         if constexpr (OP == OP_AdvanceBlock2D || OP == OP_AdvanceBase) __syncwarp();
         (exec_tile<OP, SP, P, K, KI>(operand, cx), ...);
@@ -1148,7 +1214,13 @@ __device__ __forceinline__ void geval_direct_body(const LaunchArgs &a)
     gint_tensor_info *ti_s = reinterpret_cast<gint_tensor_info *>(smem + a.code_smem_bytes);
     TileInfo *tiles_s = reinterpret_cast<TileInfo *>(smem + a.code_smem_bytes + kTensorInfoSmemBytes);
 
-    for (uint32_t i = threadIdx.x; i < a.n_slots; i += kThreadsPerBlock) code_s[i] = a.code[i];
+    /* a short program travels inside the parameter block (a.code == nullptr): staging it costs no global-memory round trip,
+     * which is most of what a launch of a few instructions per tile would otherwise wait for before its first load */
+    if (a.code == nullptr) {
+        if (threadIdx.x < a.n_slots) code_s[threadIdx.x] = a.inline_code[threadIdx.x];
+    } else {
+        for (uint32_t i = threadIdx.x; i < a.n_slots; i += kThreadsPerBlock) code_s[i] = a.code[i];
+    }
     {
         const int *src = reinterpret_cast<const int *>(&a.ti);
         int *dst = reinterpret_cast<int *>(ti_s);
@@ -1160,7 +1232,8 @@ __device__ __forceinline__ void geval_direct_body(const LaunchArgs &a)
     Ctx cx;
     cx.tiles = tiles_s + warp * K;
     cx.lane = lane;
-    {   // after the tile descriptors: the ring of early-issued loads (ring_bytes per tile), then the staged row blocks
+    cx.args = &a;
+    if constexpr (!lean_ctx<P, K>()) {   // after the tile descriptors: the ring of early-issued loads (ring_bytes per tile), then the staged row blocks
         unsigned char *after = reinterpret_cast<unsigned char *>(tiles_s + kWarpsPerBlock * K);
         cx.hidden = (uint32_t)__cvta_generic_to_shared(after + (size_t)(warp * K) * a.ring_bytes + lane * 4);
         cx.rows = (uint32_t)__cvta_generic_to_shared(after + (size_t)(kWarpsPerBlock * K) * a.ring_bytes + (size_t)(warp * K) * a.row_area_bytes);
@@ -1198,6 +1271,7 @@ __device__ __forceinline__ void geval_indirect_body(const IndirectArgs &a)
     cx.rows = 0;
     cx.rows_stride = 0;
     cx.ring_mask = 0;
+    cx.args = nullptr;
     for (uint32_t g = blockIdx.x * kWarpsPerBlock + warp; g < a.grid_dim; g += gridDim.x * kWarpsPerBlock) {
         const IndirectEntry e = a.table[g];
         __syncwarp();  // every lane is done with the previous program's code and descriptors

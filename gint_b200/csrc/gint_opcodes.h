@@ -138,12 +138,27 @@
  *   LoadStagedRows   the row load, served from that copy
  * (a row load by itself is a 16-byte access per lane at the row stride: 16 L1 wavefronts per warp where 4 would do)
  */
+/*
+ * DupBroadcastW with the lane index built into the opcode (no operand is read at run time). The format's DupBroadcastW carries
+ * its lane index in the operand word, so a handler has to select the value among four at run time; the index is a constant
+ * of the program, and with it in the opcode the handler is two register moves per tile:
+ *   Bcast_k    push (T[k], T[k], T[k], T[k])
+ * (The same was tried for FPermW and FShuf2, split into two steps of 16 index pairs each: four moves per tile instead of a
+ * dozen selects, but a program with many different permutations then jumps between several times as many distinct handlers,
+ * and the instruction cache misses cost more than the selects had -- the 4x4 inverse ran 2.2 times slower.)
+ */
+/* ... and for a tensor whose 2DW rows the host can prove full, 16-byte aligned and never masked, for every logical program
+ * (given a 16-byte aligned base pointer, checked at every launch):
+ *   LoadGlobal2DWF32Fast / StoreGlobal2DWF32Fast   one 128-bit access per lane, no shape, mask or alignment handling
+ */
 #define GINT_INTERNAL_OPCODE_LIST(X) \
     X(PfTake, 106, 0, 1) X(PfIssue1D, 107, 0, 0) X(PfTakeIssue1D, 108, 0, 1) X(PfSkip, 109, 0, 0) \
     X(LoadGlobal1DF32Fast, 110, 0, 1) X(StoreGlobal1DF32Fast, 111, 1, -1) X(PfIssue1DFast, 112, 0, 0) X(PfTakeIssue1DFast, 113, 0, 1) \
-    X(StageRows, 114, 0, 0) X(LoadStagedRows, 115, 0, 1)
-#define GINT_N_DISPATCH 142   /* opcodes the kernels dispatch on: the 106 of the format, the 8 above and the fused
-                                 handlers of gint_fused.h */
+    X(StageRows, 114, 0, 0) X(LoadStagedRows, 115, 0, 1) \
+    X(Bcast_0, 116, 1, 1) X(Bcast_1, 117, 1, 1) X(Bcast_2, 118, 1, 1) X(Bcast_3, 119, 1, 1) \
+    X(LoadGlobal2DWF32Fast, 120, 0, 1) X(StoreGlobal2DWF32Fast, 121, 1, -1)
+#define GINT_N_DISPATCH 150   /* opcodes the kernels dispatch on: the 106 of the format, the 16 internal ones above and the
+                                 fused handlers of gint_fused.h */
 
 enum gint_opcode {
 #define GINT_X_ENUM(name, num, md, net) OP_##name = num,

@@ -24,8 +24,11 @@ constexpr int kRingSlotsShallow = 4, kRingSlotsDeep = 8;
 
 /* Minimum resident blocks per SM requested from the compiler (caps registers per thread): the pool itself takes 4*P*K
  * registers; addresses and interpreter state take about 40 more. */
+#ifndef GINT_MIN_BLOCKS_WIDE
+#define GINT_MIN_BLOCKS_WIDE 4   /* for the widest pool (12 slots x 2 tiles = 96 pool registers) */
+#endif
 #ifndef GINT_MIN_BLOCKS
-#define GINT_MIN_BLOCKS(P, K) ((P) * (K) <= 7 ? 8 : (P) * (K) <= 8 ? 7 : (P) * (K) <= 16 ? 5 : 4)
+#define GINT_MIN_BLOCKS(P, K) ((P) * (K) <= 7 ? 8 : (P) * (K) <= 8 ? 7 : (P) * (K) <= 16 ? 5 : GINT_MIN_BLOCKS_WIDE)
 #endif
 
 /* Per logical program, decoded once into shared memory (the reference's BlockTensorInfo,
@@ -48,8 +51,10 @@ struct Footprint {
     int32_t reserved;
 };
 
+constexpr int kInlineCodeSlots = 24;   // stream entries that fit into the parameter block (programs of up to ~20 instructions)
+
 struct LaunchArgs {
-    const uint2 *code;        // pre-decoded {key, operand}; n_slots entries, padded with Halt
+    const uint2 *code;        // pre-decoded {operand, next opcode} entries; n_slots of them, padded with Halt; nullptr: inline_code
     uint32_t n_slots;         // entries staged into shared memory (even, so the copy is a 16-byte multiple)
     uint32_t n_tensors;
     uint32_t first;           // first logical program of this launch
@@ -62,6 +67,7 @@ struct LaunchArgs {
     uint32_t reserved;
     Footprint fp[GINT_MAX_TENSORS];
     gint_tensor_info ti;      // descriptor block, base pointers patched per call: travels as a kernel parameter
+    uint2 inline_code[kInlineCodeSlots];   // the program itself when it has at most kInlineCodeSlots entries (code == nullptr)
 };
 
 struct IndirectEntry {

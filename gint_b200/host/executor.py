@@ -470,9 +470,12 @@ class Plan:
 
     def __init__(self, owner: "B200Executor", ctx, steps, slots) -> None:
         self._owner, self._ctx, self._steps, self._slots = owner, ctx, steps, slots
+        self._n = len(steps)
+        self._n_launches = sum(1 for s in steps if s.grid_dim)
+        self._call = owner._lib.gint_execute_plan
 
     def __len__(self) -> int:
-        return len(self._steps)
+        return self._n
 
     def set_arg(self, step: int, arg_index: int, tensor) -> None:
         """Point argument ``arg_index`` of step ``step`` at another tensor of the same shape and strides."""
@@ -482,12 +485,12 @@ class Plan:
                 self._steps[step].base_ptrs[j] = ptr
 
     def run(self, cuda_stream: int = 0) -> None:
-        if len(self._steps) == 0:
+        if self._n == 0:
             return
-        rc = self._owner._lib.gint_execute_plan(self._ctx, self._steps, len(self._steps), cuda_stream)
+        rc = self._call(self._ctx, self._steps, self._n, cuda_stream)
         if rc != 0:
             self._owner._check(self._ctx, rc, "gint_execute_plan")
-        self._owner.launches += sum(1 for s in self._steps if s.grid_dim)
+        self._owner.launches += self._n_launches
 
 
 executor: Optional[BaseExecutor] = None

@@ -3,7 +3,7 @@
 The bytecode format is the contract with the unchanged gint frontend and conductor: a stream of
 int32 pairs ``[opcode, operand]`` terminated by opcode 0 (``gint/kernel/interpreter/main.py:61-168``
 for the numbering, ``gint/host/analyzer.py:24-135`` for the stack effects). The numbers below are
-checked against a dump of the reference's own tables in ``tests/golden/opcodes.json``.
+checked against a dump of the reference's own tables in ``gint_b200/data/opcodes.json``.
 
 The same table exists three times in this repository on purpose, each written independently and
 cross-checked by tests: here (host Python), in ``gint_b200/csrc/gint_opcodes.h`` (the C-ABI library's

@@ -1,6 +1,6 @@
 """Ready-made programs: bytecode streams recorded from the gint frontend / conductor, wrapped as executables.
 
-``tests/golden/programs.json`` holds int32 bytecode streams and tensor descriptors that were produced by running
+``gint_b200/data/programs.json`` holds int32 bytecode streams and tensor descriptors that were produced by running
 the reference's own frontend, small-matrix programs and torch.compile backend (see ``tests/golden/make_golden.py``).
 ``RecordedProgram`` turns one record into a ``BaseExecutableProgram`` so it runs through the normal executor path,
 exactly as the conductor's compiled subgraphs do (``gint/conductor/compiler.py:300-328``).
@@ -16,7 +16,7 @@ import numpy
 
 from .host.executor import BaseExecutableProgram, ProgramData, ProgramTensorInfo
 
-DEFAULT_GOLDEN = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "tests", "golden", "programs.json")
+DEFAULT_GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "data", "programs.json")
 
 
 @lru_cache(maxsize=4)

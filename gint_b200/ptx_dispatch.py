@@ -36,7 +36,69 @@ class PtxDispatchError(RuntimeError):
     pass
 
 
-def rewrite(ptx: str, n_keys: int, n_ops: int = 142) -> tuple[str, dict]:
+SMALL_HANDLER_INSNS = 64
+
+
+def cluster_small_handlers(lines: list[str], limit: int = SMALL_HANDLER_INSNS, order=None, always=None) -> tuple[list[str], int]:
+    """Move every small single-block handler next to the others, ahead of the large ones.
+
+    The compiler emits handlers in key order, so the few-instruction handlers a program actually runs (moves, arithmetic,
+    register loads and stores, lane permutes) lie scattered between tile accesses and inlined math routines of several
+    kilobytes each: the hot code of a program is a few hundred instructions spread over megabytes, every jump lands on a
+    different cache line and the lines fetched after it belong to cold handlers. A handler that is ONE basic block -- label,
+    GINT_TARGET marker, straight-line code, its own ``brx.idx`` (or ``ret``) -- can be moved freely: control only ever enters
+    it through a jump table and leaves it through its terminator. Such blocks of at most ``limit`` instructions are cut out
+    and re-emitted together, in key order (stack depth, then opcode), right after the entry dispatch. Everything else stays
+    where it was. Returns (lines, number of handlers moved)."""
+    def is_code(t: str) -> bool:
+        t = t.strip()
+        return bool(t) and not t.startswith("//") and not t.startswith(".") and t not in ("{", "}") and not t.endswith(":")
+
+    entry = next((i for i, t in enumerate(lines) if t.lstrip().startswith("brx.idx.uni") and i > 0 and "$gint_targets" in t), None)
+    if entry is None:
+        return lines, 0
+    label_at = [i for i, t in enumerate(lines) if _LABEL.match(t.strip())]
+    moved: list[tuple[int, int, int]] = []     # (key, start line, end line exclusive)
+    for n, start in enumerate(label_at):
+        end = label_at[n + 1] if n + 1 < len(label_at) else None
+        if end is None or start < entry:
+            continue
+        body = lines[start + 1:end]
+        key = next((m.group(1) for t in body if (m := _TARGET.match(t))), None)
+        if key is None or key == "default":
+            continue
+        code = [t.strip() for t in body if is_code(t)]
+        if not code or (len(code) > limit and not (always and int(key) in always)):
+            continue
+        if not (code[-1].startswith("brx.idx.uni") or code[-1].startswith("ret;")):
+            continue                                          # falls through or ends otherwise: leave it
+        if any(_CONTROL.match(t) for t in code[:-1]):
+            continue                                          # internal control flow
+        # nothing may fall through INTO the block: the last code line before its label must be an unconditional transfer
+        j = start - 1
+        while j >= 0 and not is_code(lines[j]):
+            j -= 1
+        prev = lines[j].strip() if j >= 0 else ""
+        if not (prev.startswith("brx.idx.uni") or prev.startswith("ret;") or re.match(r"^bra(\.uni)?\s", prev)):
+            continue
+        moved.append((int(key), start, end))
+    if not moved:
+        return lines, 0
+    cut = set()
+    for _, a, b in moved:
+        cut.update(range(a, b))
+    out: list[str] = []
+    for i, t in enumerate(lines):
+        if i in cut:
+            continue
+        out.append(t)
+        if i == entry:
+            for _, a, b in sorted(moved, key=(lambda m: order(m[0])) if order else None):
+                out.extend(lines[a:b])
+    return out, len(moved)
+
+
+def rewrite(ptx: str, n_keys: int, n_ops: int = 142, cluster: bool = True, hot: set | None = None) -> tuple[str, dict]:
     """Return (rewritten PTX, stats). ``n_keys`` is the size of the dispatch key space."""
     lines = ptx.split("\n")
     # depth -1 stands for "all": the non-threaded form, one table over every (depth, opcode) key
@@ -131,4 +193,13 @@ def rewrite(ptx: str, n_keys: int, n_ops: int = 142) -> tuple[str, dict]:
                 out.extend(table_decl(depth))
         if i in insert_after:
             out.append(insert_after[i])
-    return "\n".join(out), {"cases": len(numeric), "keys": n_keys, "sites": len(sites), "tables": len(used_depths)}
+    n_moved = 0
+    if cluster and threaded:
+        # profile-guided order: the handlers that recorded programs run (gint_b200/hot_handlers.py) first, next to each
+        # other, then the other small ones; within each group by stack depth and opcode
+        hot_keys = {d * n_ops + o for d, o in (hot or ())}
+
+        def order(key: int):
+            return (0 if key in hot_keys else 1, key)
+        out, n_moved = cluster_small_handlers(out, order=order)
+    return "\n".join(out), {"cases": len(numeric), "keys": n_keys, "sites": len(sites), "tables": len(used_depths), "clustered": n_moved}

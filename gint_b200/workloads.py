@@ -44,13 +44,22 @@ class Workload:
     algorithmic_bytes: int = 0
     rtol: float = 1e-5
     atol: float = 1e-6
+    _args_cache: Optional[tuple] = field(default=None, repr=False, compare=False)
 
     def run(self, executor, stream: int = 0) -> None:
-        from .host.executor import _convert_arg
         if self.pre is not None:
             self.pre(self.tensors)
-        for st in self.steps:
-            executor.execute(st.program, [_convert_arg(self.tensors[r]) for r in st.roles], st.grid_dim, cuda_stream=stream)
+        for st, args in zip(self.steps, self._interfaces()):
+            executor.execute(st.program, args, st.grid_dim, cuda_stream=stream)
+
+    def _interfaces(self):
+        """The steps' arguments as TensorInterfaces, converted once (a caller that launches the same tensors again and again
+        keeps the converted form; the conductor's compiled graphs do the same with their skeletons)."""
+        from .host.executor import _convert_arg
+        key = tuple(t.data_ptr() for t in self.tensors.values())
+        if self._args_cache is None or self._args_cache[0] != key:
+            self._args_cache = (key, [[_convert_arg(self.tensors[r]) for r in st.roles] for st in self.steps])
+        return self._args_cache[1]
 
     def plan(self, executor):
         """The bytecode steps as one reusable launch plan (``B200Executor.build_plan``); ``pre`` stays with the caller."""

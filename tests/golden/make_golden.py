@@ -1,5 +1,5 @@
 #!/usr/bin/env python
-"""Regenerate the golden fixtures in this directory from the reference implementation.
+"""Regenerate the recorded fixtures in ``gint_b200/data/`` from the reference implementation.
 
 Run in a container that has the reference checkout (CPU only, no GPU needed):
 
@@ -31,6 +31,7 @@ import numpy as np
 import torch
 
 HERE = os.path.dirname(os.path.abspath(__file__))
+DATA = os.path.join(os.path.dirname(os.path.dirname(HERE)), "gint_b200", "data")   # package data: the library, the bench and the tests read it there
 
 
 def _info_to_dict(t):
@@ -98,7 +99,7 @@ def main():
     # ------------------------------------------------------------------ opcodes.json
     opcodes = {cls.__name__: int(op) for cls, op in kmain.INSNS.items()}
     effects = {str(k): [int(a), int(b)] for k, (a, b) in analyzer._EFFECTS.items()}
-    with open(os.path.join(HERE, "opcodes.json"), "w") as fo:
+    with open(os.path.join(DATA, "opcodes.json"), "w") as fo:
         json.dump(dict(
             opcodes=opcodes, stack_effects=effects,
             variants={k: list(v) for k, v in kmain.VARIANTS.items()},
@@ -281,7 +282,7 @@ def main():
         call["arg_strides"] = dict(x=list(x.stride()), y=list(y.stride()), w=list(w.stride()))
         programs[f"rmsnorm_bf16_b{bb}_t{t}_nh{nh}_h{h}"] = call
 
-    with open(os.path.join(HERE, "programs.json"), "w") as fo:
+    with open(os.path.join(DATA, "programs.json"), "w") as fo:
         json.dump(programs, fo, separators=(",", ":"), sort_keys=True)
     for k, v in programs.items():
         print(f"{k:40s} insns={len(v['bytecode']) // 2:5d} tensors={len(v['infos'])} grid={v['grid_dim']} roles={v['arg_roles']}")

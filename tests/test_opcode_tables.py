@@ -1,6 +1,6 @@
 """The bytecode format contract: opcode numbers, stack effects and program analysis agree with the reference.
 
-Golden data: tests/golden/opcodes.json is a dump of the reference's own INSNS / _EFFECTS / VARIANTS tables
+Golden data: gint_b200/data/opcodes.json is a dump of the reference's own INSNS / _EFFECTS / VARIANTS tables
 (gint/kernel/interpreter/main.py:34-38,61-168; gint/host/analyzer.py:24-135), made by tests/golden/make_golden.py.
 The analysis cases restate the reference's tests/test_analyzer.py:10-83.
 """
@@ -17,7 +17,7 @@ from gint_b200.host import frontend as fe
 from gint_b200.programs import load_records
 from oracle import oracle
 
-GOLDEN = os.path.join(os.path.dirname(__file__), "golden", "opcodes.json")
+GOLDEN = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "gint_b200", "data", "opcodes.json")
 
 
 @pytest.fixture(scope="module")
@@ -50,7 +50,7 @@ def test_c_header_table_matches_python():
     import re
     rows = re.findall(r"X\((\w+), (\d+), (-?\d+), (-?\d+)\)", open(path).read())
     internal = [r for r in rows if int(r[1]) >= opcodes.N_OPCODES]   # the kernels' internal opcodes sit above the format's 106
-    assert all(r[0].startswith("Pf") or r[0].endswith("Fast") or r[0].endswith("Rows") for r in internal)
+    assert all(r[0].startswith(("Pf", "Bcast_")) or r[0].endswith("Fast") or r[0].endswith("Rows") for r in internal)
     assert sorted(int(r[1]) for r in internal) == list(range(opcodes.N_OPCODES, opcodes.N_OPCODES + len(internal)))
     rows = [r for r in rows if int(r[1]) < opcodes.N_OPCODES]
     assert len(rows) == opcodes.N_OPCODES

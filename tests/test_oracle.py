@@ -2,7 +2,7 @@
 
 1. Known-answer tests the reference keeps for this path: packed immediates -> [1,2,3,4] / [16,32,48,64], int32 add,
    gather and scatter exact (reference tests/test_frontend.py:166-208,245-291).
-2. Bytecode streams produced by the reference's own frontend / conductor (tests/golden/programs.json), executed by the
+2. Bytecode streams produced by the reference's own frontend / conductor (gint_b200/data/programs.json), executed by the
    oracle and compared with the torch-eager expressions the reference's tests use.
 3. Operand order and lane mapping of every opcode family against independent numpy/torch expectations.
 """

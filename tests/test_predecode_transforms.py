@@ -14,6 +14,7 @@ from gint_b200.host.utils import fill_tensor_info
 from gint_b200.programs import load_records, recorded
 
 PF_TAKE, PF_ISSUE_1D, PF_TAKE_ISSUE_1D, PF_SKIP, LOAD_1D_FAST, STORE_1D_FAST, PF_ISSUE_1D_FAST, PF_TAKE_ISSUE_1D_FAST, STAGE_ROWS, LOAD_STAGED_ROWS = range(106, 116)
+BCAST, LOAD_2DW_FAST, STORE_2DW_FAST = 116, 120, 121   # Bcast_0..3
 
 
 def fused_table():
@@ -82,9 +83,11 @@ def undo(prog, table):
             assert op != -1
             flat.append((op, operand))
             i += 1
+    # 1b. DupBroadcastW with a built-in lane index -> the format's instruction with an operand
+    flat = [(O.DupBroadcastW, op - BCAST) if BCAST <= op < BCAST + 4 else (op, operand) for op, operand in flat]
     # 2. fast accesses -> the generic opcodes they specialise
     generic = {LOAD_1D_FAST: O.LoadGlobal1DF32, STORE_1D_FAST: O.StoreGlobal1DF32, PF_ISSUE_1D_FAST: PF_ISSUE_1D,
-               PF_TAKE_ISSUE_1D_FAST: PF_TAKE_ISSUE_1D}
+               PF_TAKE_ISSUE_1D_FAST: PF_TAKE_ISSUE_1D, LOAD_2DW_FAST: O.LoadGlobal2DWF32, STORE_2DW_FAST: O.StoreGlobal2DWF32}
     # (their operand is {8 * slot in bits 26..31, byte offset of the tile in bits 0..25})
     flat = [(generic[op], ((operand & 0x03FFFFFF) // 4) << 4 | operand >> 29) if op in generic else (op, operand) for op, operand in flat]
     # staged row blocks: the copy at the program start disappears, the row loads get their tensor slot and column back
@@ -152,7 +155,7 @@ def test_named_programs_get_the_expected_shape():
     assert dispatches < 130
     takes = (PF_TAKE_ISSUE_1D, PF_TAKE_ISSUE_1D_FAST, PF_TAKE)
     assert sum(sum(m in takes for m in (table[op] if op in table else [op])) for op, _ in both) == 96
-    assert dispatches < 70     # two reduction steps, or a whole scale-and-store chunk, per dispatch
+    assert dispatches < 80     # two reduction steps, or a whole scale-and-store chunk, per dispatch
     # every tile of this program is full, unit-stride and 16-byte aligned: only the fast forms remain
     members = [m for op, _ in both for m in (table[op] if op in table else [op])]
     assert PF_TAKE_ISSUE_1D not in members and PF_ISSUE_1D not in members and O.StoreGlobal1DF32 not in members
