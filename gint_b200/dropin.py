@@ -23,17 +23,23 @@ from .host.executor import B200Executor
 _installed: dict = {}
 
 
-def install(package_path: Optional[str] = None):
+def install(package_path: Optional[str] = None, accelerate_conductor: bool = False):
     """Make the B200 executor the executor of the importable ``gint`` package and return it.
 
     ``package_path``: a directory to put in front of ``sys.path`` first (the folder that contains ``gint/``), for a gint
     that is not installed into the environment. Calling ``install`` again returns the executor already installed.
+    ``accelerate_conductor``: also route the launches of graphs compiled by ``gint.conductor`` from now on through
+    ``gint_execute_plan`` (``gint_b200/conductor_fastpath.py``: one library call per run of consecutive subgraphs instead of a
+    Python-level ``execute`` per subgraph; the conductor's source is not touched).
     """
     if package_path and package_path not in sys.path:
         sys.path.insert(0, package_path)
     gx = importlib.import_module("gint.host.executor")
     cur = getattr(gx, "executor", None)
     if cur is not None and isinstance(cur, B200Executor):
+        if accelerate_conductor:
+            from . import conductor_fastpath
+            conductor_fastpath.patch_conductor(cur)
         return cur
     cls = _installed.get(id(gx.BaseExecutor))
     if cls is None:
@@ -42,11 +48,16 @@ def install(package_path: Optional[str] = None):
         _installed[id(gx.BaseExecutor)] = cls
     _installed["previous"] = cur
     gx.executor = cls()
+    if accelerate_conductor:
+        from . import conductor_fastpath
+        conductor_fastpath.patch_conductor(gx.executor)
     return gx.executor
 
 
 def uninstall() -> None:
     """Put back whatever executor gint had before ``install`` (None: gint picks its own on next use)."""
+    from . import conductor_fastpath
+    conductor_fastpath.unpatch_conductor()
     gx = sys.modules.get("gint.host.executor")
     if gx is not None and isinstance(getattr(gx, "executor", None), B200Executor):
         gx.executor = _installed.get("previous")

@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Run the reference's own unittest modules, unmodified, with the B200 executor installed (or with the reference's own).
 
-    python tests/ref_suite_runner.py --executor b200|reference [--json out.json] tests.test_frontend tests.test_bmm4x4 ...
+    python tests/ref_suite_runner.py --executor b200|b200_plan|reference [--json out.json] tests.test_frontend tests.test_bmm4x4 ...
 
 Child process of ``tests/test_gpu_reference_suite.py``: the reference package and its ``tests`` package are imported from
 ``baseline/_ref`` (installed by ``baseline/build_ref.py``), ``gint_b200.install()`` swaps the executor in through the reference's
@@ -53,7 +53,8 @@ class _Collect(unittest.TextTestResult):
 
 def main() -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--executor", choices=["b200", "reference"], default="b200")
+    ap.add_argument("--executor", choices=["b200", "b200_plan", "reference"], default="b200",
+                    help="b200_plan: also launch conductor-compiled graphs through gint_execute_plan (gint_b200/conductor_fastpath.py)")
     ap.add_argument("--json", default=None)
     ap.add_argument("modules", nargs="+")
     o = ap.parse_args()
@@ -65,9 +66,9 @@ def main() -> int:
     torch.cuda.init()
     torch.zeros(1, device="cuda")          # the reference asks for an existing CUDA context (gint/host/cuda/driver.py:84-95)
     loaded = None
-    if o.executor == "b200":
+    if o.executor in ("b200", "b200_plan"):
         import gint_b200
-        ex = gint_b200.install()
+        ex = gint_b200.install(accelerate_conductor=(o.executor == "b200_plan"))
         loaded = type(ex).__mro__[1].__name__
     suite = unittest.TestSuite()
     loader = unittest.TestLoader()

@@ -60,3 +60,18 @@ def test_reference_module_passes_on_b200_executor(module):
     ran = sum(1 for o in res["outcomes"].values() if o["outcome"] == "ok")
     assert ran > 0, f"{module}: nothing ran ({res['outcomes']})"
     assert res["launches"] and res["launches"] > 0, "no kernel of this library was launched"
+
+
+CONDUCTOR_MODULES = [m for m in MODULES if "conductor" in m or "compile" in m]
+
+
+@pytest.mark.parametrize("module", CONDUCTOR_MODULES)
+def test_reference_conductor_module_passes_with_plan_fast_path(module):
+    """The same torch.compile test modules with the conductor's per-subgraph Python launches replaced by gint_execute_plan
+    calls (``gint_b200.install(accelerate_conductor=True)``): every case must still pass."""
+    res = run_module(module, executor="b200_plan")
+    assert res["executor_class"] == "B200DropInExecutor"
+    bad = {tid: o for tid, o in res["outcomes"].items() if o["outcome"] not in ("ok", "skip")}
+    assert not bad, json.dumps(bad, indent=1)
+    assert sum(1 for o in res["outcomes"].values() if o["outcome"] == "ok") > 0
+    assert res["launches"] and res["launches"] > 0

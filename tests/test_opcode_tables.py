@@ -153,3 +153,14 @@ def test_every_opcode_is_executed_by_a_parity_case():
             seen.update(int(op) for op in np.asarray(pd.program).reshape(-1, 2)[:, 0])
     missing = sorted(set(range(opcodes.N_OPCODES)) - seen)
     assert not missing, [opcodes.NAMES[m] for m in missing]
+
+
+def test_hot_handler_table_is_current():
+    """gint_b200/csrc/hot_handlers.json (the profile behind the kernels' code layout) equals a fresh derivation from the
+    recorded programs with the library as built: it has to be regenerated when opcode numbers or the pre-decoder change."""
+    import json
+    from gint_b200 import hot_handlers
+    with open(hot_handlers.TABLE) as f:
+        committed = json.load(f)
+    assert committed == hot_handlers.derive(), "run `python -m gint_b200.hot_handlers` and rebuild"
+    assert len(hot_handlers.load()) == len(committed["keys"]) > 100
