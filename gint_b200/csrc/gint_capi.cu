@@ -494,7 +494,7 @@ struct KernelImage {
     const unsigned char *begin;
     const unsigned char *end;
     const char *name;
-    int P, K;          // K == 0: indirect kernel
+    int P, K;          // K == 0: indirect kernel; K == -1: checked kernel
     cudaLibrary_t lib;
     cudaKernel_t kernel;
     bool loaded;
@@ -506,6 +506,9 @@ KernelImage g_images[] = {
 #undef GINT_X_IMG
 #define GINT_X_IMG(P) {gint_cubin_indirect_##P, gint_cubin_indirect_##P##_end, "gint_geval_indirect_" #P, P, 0, nullptr, nullptr, false},
     GINT_INDIRECT_VARIANTS(GINT_X_IMG)
+#undef GINT_X_IMG
+#define GINT_X_IMG(P) {gint_cubin_checked_##P, gint_cubin_checked_##P##_end, "gint_geval_checked_" #P, P, -1, nullptr, nullptr, false},
+    GINT_CHECKED_VARIANTS(GINT_X_IMG)
 #undef GINT_X_IMG
 };
 std::mutex g_images_mu;
@@ -613,6 +616,8 @@ struct gint_ctx {
     std::vector<Program *> programs;
     std::vector<Variant> direct;
     Variant indirect{12, 1, nullptr, 0, false, 0};
+    Variant checked{12, 1, nullptr, 0, false, 0};
+    gint_device_status *status_dev = nullptr;   // status word of the checked launches (allocated on first use)
     std::string last_error;
     int opt_tiles_per_warp = 0;
     int opt_max_blocks = 0;
@@ -956,6 +961,7 @@ int gint_create(int device, gint_ctx **out)
     for (auto &im : g_images) {
         if (!im.loaded) continue;
         if (im.K == 0) ctx->indirect.fn = (const void *)im.kernel;
+        else if (im.K < 0) ctx->checked.fn = (const void *)im.kernel;
         else ctx->direct.push_back(Variant{im.P, im.K, (const void *)im.kernel, 0, false, 0});
     }
     int usable = 0;
@@ -975,6 +981,11 @@ int gint_create(int device, gint_ctx **out)
     if (ctx->indirect.fn) {
         cudaFuncAttributes attr;
         if (cudaFuncGetAttributes(&attr, ctx->indirect.fn) == cudaSuccess) { ctx->indirect.regs = attr.numRegs; ctx->indirect.ok = true; }
+        else cudaGetLastError();
+    }
+    if (ctx->checked.fn) {
+        cudaFuncAttributes attr;
+        if (cudaFuncGetAttributes(&attr, ctx->checked.fn) == cudaSuccess) { ctx->checked.regs = attr.numRegs; ctx->checked.ok = true; }
         else cudaGetLastError();
     }
     if (usable == 0) {
@@ -997,6 +1008,7 @@ void gint_destroy(gint_ctx *ctx)
                 delete p;
             }
         }
+        if (ctx->status_dev) cudaFree(ctx->status_dev);
         if (ctx->ind_dev) cudaFree(ctx->ind_dev);
         if (ctx->ind_host) cudaFreeHost(ctx->ind_host);
         if (ctx->ind_event) cudaEventDestroy(ctx->ind_event);
@@ -1179,6 +1191,78 @@ int gint_execute_range(gint_ctx *ctx, uint64_t handle, const uint64_t *base_ptrs
                        void *cuda_stream)
 {
     return launch_direct(ctx, handle, base_ptrs, n_tensors, first, count, cuda_stream);
+}
+
+int gint_execute_checked(gint_ctx *ctx, uint64_t handle, const uint64_t *base_ptrs, const uint64_t *lo, const uint64_t *hi, int n_tensors,
+                         uint32_t grid_dim, void *cuda_stream)
+{
+    if (!ctx || ((!base_ptrs || !lo || !hi) && n_tensors > 0)) return fail(ctx, GINT_ERR_INVALID_ARGUMENT, "null argument");
+    Program *p = lookup(ctx, handle);
+    if (!p) return fail(ctx, GINT_ERR_BAD_HANDLE, "unknown program handle");
+    if (n_tensors != p->n_tensors) return fail(ctx, GINT_ERR_ARG_COUNT, "number of arguments does not match the program");
+    if (!ctx->checked.ok) return fail(ctx, GINT_ERR_NO_DEVICE, "checked kernel image not usable on this device");
+    if (grid_dim == 0) return GINT_OK;
+    DeviceGuard guard(ctx->device);
+    cudaStream_t stream = (cudaStream_t)cuda_stream;
+    {
+        int rc = refuse_capture(ctx, stream, "gint_execute_checked");
+        if (rc != GINT_OK) return rc;
+    }
+    {
+        std::lock_guard<std::mutex> lk(ctx->mu);
+        if (!ctx->status_dev) {
+            cudaError_t e = cudaMalloc(&ctx->status_dev, sizeof(gint_device_status));
+            if (e == cudaSuccess) e = cudaMemset(ctx->status_dev, 0, sizeof(gint_device_status));
+            if (e != cudaSuccess) { ctx->status_dev = nullptr; return fail(ctx, GINT_ERR_OUT_OF_MEMORY, "cudaMalloc(device status)", e); }
+        }
+    }
+    const StreamView sv = stream_view(p, false);      // the program as written
+    uint32_t code_smem = 0;
+    const uint32_t smem = direct_smem(sv, 1, &code_smem);
+    if ((int)smem > ctx->max_smem_optin) return fail(ctx, GINT_ERR_TOO_LARGE, "program too long for the checked kernel (shared memory)");
+    cudaError_t e;
+    if (smem > 48u * 1024u) {
+        e = cudaFuncSetAttribute(ctx->checked.fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return fail(ctx, GINT_ERR_CUDA, "cudaFuncSetAttribute(checked)", e);
+    }
+    int bps = 0;
+    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&bps, ctx->checked.fn, gint::kThreadsPerBlock, smem);
+    if (e != cudaSuccess || bps < 1) return fail(ctx, GINT_ERR_CUDA, "occupancy query (checked)", e);
+    uint64_t blocks = blocks_for(grid_dim, 1);
+    const uint64_t resident = (uint64_t)bps * (uint64_t)ctx->num_sms;
+    if (blocks > resident) blocks = resident;
+    LaunchArgs a;
+    memset(&a, 0, sizeof(a));
+    a.code = p->code_dev;
+    a.n_slots = sv.n_slots;
+    a.n_tensors = (uint32_t)p->n_tensors;
+    a.first = 0;
+    a.end = grid_dim;
+    a.code_smem_bytes = code_smem;
+    a.ti = p->ti;
+    for (int i = 0; i < n_tensors; i++) {
+        a.ti.base_ptr[i] = (int64_t)base_ptrs[i];
+        a.chk_lo[i] = lo[i];
+        a.chk_hi[i] = hi[i];
+    }
+    a.chk_status = ctx->status_dev;
+    void *args[1] = {&a};
+    e = cudaLaunchKernel(ctx->checked.fn, dim3((unsigned)blocks), dim3(gint::kThreadsPerBlock), args, smem, stream);
+    if (e != cudaSuccess) return fail(ctx, GINT_ERR_CUDA, "cudaLaunchKernel(checked)", e);
+    return GINT_OK;
+}
+
+int gint_device_status_read(gint_ctx *ctx, gint_device_status *out, int clear)
+{
+    if (!ctx || !out) return fail(ctx, GINT_ERR_INVALID_ARGUMENT, "null argument");
+    memset(out, 0, sizeof(*out));
+    if (!ctx->status_dev) return GINT_OK;     // no checked launch so far
+    DeviceGuard guard(ctx->device);
+    cudaError_t e = cudaDeviceSynchronize();
+    if (e == cudaSuccess) e = cudaMemcpy(out, ctx->status_dev, sizeof(*out), cudaMemcpyDeviceToHost);
+    if (e == cudaSuccess && clear) e = cudaMemset(ctx->status_dev, 0, sizeof(*out));
+    if (e != cudaSuccess) return fail(ctx, GINT_ERR_CUDA, "reading the device status", e);
+    return GINT_OK;
 }
 
 int gint_execute_plan(gint_ctx *ctx, const gint_plan_step *steps, int n_steps, void *cuda_stream)

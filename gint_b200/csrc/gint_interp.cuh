@@ -38,18 +38,64 @@
 
 /* GINT_GUARD: debugging aid for changes to the dispatch machinery. Every handler decrements an instruction budget (the
  * number of stream entries) and the interpreter returns when it runs out, so a mis-wired jump table cannot spin forever. */
+#ifdef GINT_CHECKED
+#define GINT_GUARD 1
+#define GINT_GUARD_TRIPPED gint::chk_record(GINT_DEVICE_INSTRUCTION_BUDGET, -1, 0ull)
+#else
+#define GINT_GUARD_TRIPPED
+#endif
 #ifdef GINT_GUARD
 #define GINT_GUARD_STEP                                                                                               \
     {                                                                                                                 \
         uint32_t left;                                                                                                \
         asm volatile("sub.u32 %%gbudget, %%gbudget, 1; mov.u32 %0, %%gbudget;" : "=r"(left));                         \
-        if ((int)left < 0) return;                                                                                    \
+        if ((int)left < 0) { GINT_GUARD_TRIPPED; return; }                                                            \
     }
 #else
 #define GINT_GUARD_STEP
 #endif
 
 namespace gint {
+
+/* ------------------------------------------------------------------------------------------------ */
+/* checked build (GINT_CHECKED): every global-memory access of a program is compared with the byte range its tensor was
+ * declared to occupy; an access outside it is NOT performed and the first such event is recorded in a status word that the
+ * host reads (gint_device_status in gint_b200.h). Compiled into one extra kernel (kernels/gint_checked_p12.cu); in the
+ * ordinary kernels GINT_CHK is the constant true and leaves no trace in the code.                                    */
+#ifdef GINT_CHECKED
+struct CheckState {
+    u64 lo[GINT_MAX_TENSORS], hi[GINT_MAX_TENSORS];   // declared byte range [lo, hi) of every tensor slot
+    gint_device_status *status;
+    uint32_t code_base;                               // shared-memory address of the staged program
+    uint32_t logical[kWarpsPerBlock];                 // first logical program of the group each warp is interpreting
+};
+static __shared__ CheckState g_chk;
+
+__device__ __forceinline__ void chk_record(int code, int slot, u64 address)
+{
+    gint_device_status *st = g_chk.status;
+    if (atomicCAS(&st->code, 0, code) == 0) {
+        uint32_t gc;
+        asm volatile("mov.b32 %0, %%gc;" : "=r"(gc));
+        st->slot = slot;
+        st->address = address;
+        st->logical_program = g_chk.logical[threadIdx.x >> 5];
+        st->instruction = (gc - g_chk.code_base) / 8u - 3u;   // %gc points three entries past the instruction in progress
+        st->lane = threadIdx.x & 31;
+    }
+    atomicAdd(&st->count, 1u);
+}
+__device__ __forceinline__ bool chk_access(int slot, const void *p, int bytes, bool store)
+{
+    const u64 a = reinterpret_cast<u64>(p);
+    if (a >= g_chk.lo[slot] && a + (u64)bytes <= g_chk.hi[slot]) return true;
+    chk_record(store ? GINT_DEVICE_STORE_OUT_OF_RANGE : GINT_DEVICE_LOAD_OUT_OF_RANGE, slot, a);
+    return false;
+}
+#define GINT_CHK(slot, p, bytes, store) gint::chk_access((slot), (p), (bytes), (store))
+#else
+#define GINT_CHK(slot, p, bytes, store) true
+#endif
 
 /* ------------------------------------------------------------------------------------------------ */
 /* packed f32x2 helpers                                                                              */
@@ -242,13 +288,15 @@ __device__ __forceinline__ void tile_rw(const TileInfo *ti, uint32_t operand, in
                 if (off + 128 <= s1.x) {
 #pragma unroll
                     for (int w = 0; w < 4; w++) {
-                        if constexpr (STORE) p[32 * w] = v[w];
-                        else v[w] = p[32 * w];
+                        if (GINT_CHK(arg, p + 32 * w, 4, STORE)) {
+                            if constexpr (STORE) p[32 * w] = v[w];
+                            else v[w] = p[32 * w];
+                        } else if constexpr (!STORE) v[w] = 0.0f;
                     }
                 } else {
 #pragma unroll
                     for (int w = 0; w < 4; w++) {
-                        const bool ok = e + 32 * w < s1.x;
+                        const bool ok = e + 32 * w < s1.x && GINT_CHK(arg, p + 32 * w, 4, STORE);
                         if constexpr (STORE) { if (ok) p[32 * w] = v[w]; }
                         else v[w] = ok ? p[32 * w] : 0.0f;
                     }
@@ -260,7 +308,7 @@ __device__ __forceinline__ void tile_rw(const TileInfo *ti, uint32_t operand, in
         const long long pstep = (long long)(s1.y * 32) * ESZ;
 #pragma unroll
         for (int w = 0; w < 4; w++) {
-            const bool ok = e + 32 * w < s1.x;
+            const bool ok = e + 32 * w < s1.x && GINT_CHK(arg, p, ESZ, STORE);
             if constexpr (STORE) { if (ok) store_elem<DT>(p, v[w]); }
             else v[w] = ok ? load_elem<DT>(p) : 0.0f;
             p += pstep;
@@ -275,11 +323,12 @@ __device__ __forceinline__ void tile_rw(const TileInfo *ti, uint32_t operand, in
             // one 128-bit access per thread: rows of 4 consecutive floats, 16-byte aligned
             if ((ti->flags[arg] & kVecRows) && (j0 & 3) == 0 && j0 + 4 <= s2.x) {
                 float4 *p = reinterpret_cast<float4 *>(base + (long long)(t * s1.y + j0) * 4);
+                const bool vok = tok && GINT_CHK(arg, p, 16, STORE);
                 if constexpr (STORE) {
-                    if (tok) *p = make_float4(v[0], v[1], v[2], v[3]);
+                    if (vok) *p = make_float4(v[0], v[1], v[2], v[3]);
                 } else {
                     float4 r = make_float4(0.f, 0.f, 0.f, 0.f);
-                    if (tok) r = *p;
+                    if (vok) r = *p;
                     v[0] = r.x; v[1] = r.y; v[2] = r.z; v[3] = r.w;
                 }
                 return;
@@ -289,7 +338,7 @@ __device__ __forceinline__ void tile_rw(const TileInfo *ti, uint32_t operand, in
         const long long pstep = (long long)s2.y * ESZ;
 #pragma unroll
         for (int w = 0; w < 4; w++) {
-            const bool ok = tok && (j0 + w < s2.x);
+            const bool ok = tok && (j0 + w < s2.x) && GINT_CHK(arg, p, ESZ, STORE);
             if constexpr (STORE) { if (ok) store_elem<DT>(p, v[w]); }
             else v[w] = ok ? load_elem<DT>(p) : 0.0f;
             p += pstep;
@@ -308,8 +357,8 @@ __device__ __forceinline__ void tile_indirect(const TileInfo *ti, uint32_t opera
 #pragma unroll
     for (int w = 0; w < 4; w++) {
         const int i = __float_as_int(idx[w]);
-        const bool ok = i < s1.x;
         float *p = reinterpret_cast<float *>(base + (long long)(i * s1.y) * 4);
+        const bool ok = i < s1.x && GINT_CHK(arg, p, 4, STORE);
         if constexpr (STORE) { if (ok) *p = v[w]; }
         else v[w] = ok ? *p : 0.0f;
     }
@@ -521,7 +570,7 @@ GINT_OPCODE_LIST(GINT_X_INFO)
 GINT_INTERNAL_OPCODE_LIST(GINT_X_INFO)
 #undef GINT_X_INFO
 
-template <int OP, int SP, int P> __host__ __device__ constexpr bool op_valid();
+template <int OP, int SP, int P, int K_ = 1> __host__ __device__ constexpr bool op_valid();
 
 /* Fused handlers (gint_fused.h): a sequence's stack effect and validity follow from its members. */
 template <int... OPS> struct Seq {
@@ -552,17 +601,17 @@ static_assert(GINT_FUSED_FIRST + GINT_N_FUSED == GINT_N_DISPATCH, "gint_fused.h 
 template <typename S> struct SeqInfo;
 template <> struct SeqInfo<Seq<>> {
     static constexpr int net = 0, min_depth = 0;
-    template <int SP, int P> static constexpr bool valid() { return true; }
+    template <int SP, int P, int K_> static constexpr bool valid() { return true; }
 };
 template <int OP0, int... REST> struct SeqInfo<Seq<OP0, REST...>> {
     using Tail = SeqInfo<Seq<REST...>>;
     static constexpr int net = OpInfo<OP0>::net_effect + Tail::net;
     static constexpr int tail_need = Tail::min_depth - OpInfo<OP0>::net_effect;
     static constexpr int min_depth = OpInfo<OP0>::min_depth > tail_need ? OpInfo<OP0>::min_depth : tail_need;
-    template <int SP, int P> static constexpr bool valid()
+    template <int SP, int P, int K_> static constexpr bool valid()
     {
-        if constexpr (!op_valid<OP0, SP, P>()) return false;
-        else return Tail::template valid<SP + OpInfo<OP0>::net_effect, P>();
+        if constexpr (!op_valid<OP0, SP, P, K_>()) return false;
+        else return Tail::template valid<SP + OpInfo<OP0>::net_effect, P, K_>();
     }
 };
 #define GINT_X_FINFO(num, len, ...)                                                                        \
@@ -573,18 +622,20 @@ template <int OP0, int... REST> struct SeqInfo<Seq<OP0, REST...>> {
 GINT_FUSED_LIST(GINT_X_FINFO)
 #undef GINT_X_FINFO
 
-template <int OP, int SP, int P> __host__ __device__ constexpr bool op_valid()
+template <int OP, int SP, int P, int K_> __host__ __device__ constexpr bool op_valid()
 {
     if constexpr (OP >= GINT_FUSED_FIRST) {
-        return SP >= 0 && SeqInfo<typename FusedSeq<OP>::type>::template valid<SP, P>();
+        return SP >= 0 && SeqInfo<typename FusedSeq<OP>::type>::template valid<SP, P, K_>();
     } else {
         constexpr int limit = P < GINT_MAX_STACK ? P : GINT_MAX_STACK;
         if (SP > limit || SP < OpInfo<OP>::min_depth) return false;
         if (SP + OpInfo<OP>::net_effect > limit) return false;
         if (OP == OP_DupX2 && SP + 1 > limit) return false;
-        /* The 12-slot kernels have no Bcast_k handlers (the host keeps DupBroadcastW there): with them the two-tile kernel no
-         * longer fits its 128 registers and the assembler moves pool registers to local memory, which every program pays for. */
-        if (OP >= OP_Bcast_0 && OP <= OP_Bcast_3 && P >= 12) return false;
+        /* The 12-slot two-tile kernel has no Bcast_k handlers (the host keeps DupBroadcastW in programs that need 12 slots):
+         * with them it no longer fits its 128 registers and the assembler moves pool registers to local memory, which every
+         * program pays for. The one-tile 12-slot kernels (direct, indirect, checked) keep them: they also run the streams of
+         * programs with smaller pools, in which DupBroadcastW has become Bcast_k. */
+        if (OP >= OP_Bcast_0 && OP <= OP_Bcast_3 && P * K_ >= 24) return false;
         if (OP >= OP_FLoadReg0 && OP <= OP_FLoadReg7 && (P - 1 - (OP - OP_FLoadReg0)) < 0) return false;
         if (OP >= OP_FStoreReg0 && OP <= OP_FStoreReg7 && (P - 1 - (OP - OP_FStoreReg0)) < 0) return false;
         return true;
@@ -1088,7 +1139,7 @@ __device__ __forceinline__ void run_fused(const Ctx &cx, uint32_t &next_opcode)
     {
         uint32_t left;
         asm volatile("sub.u32 %%gbudget, %%gbudget, %1; mov.u32 %0, %%gbudget;" : "=r"(left) : "n"(S::n));
-        if ((int)left < 0) return;
+        if ((int)left < 0) { GINT_GUARD_TRIPPED; return; }
     }
 #endif
     SeqRun<S, SP, P, K, 0>::run(cx, ops);
@@ -1114,7 +1165,7 @@ __device__ __forceinline__ void interpret(const uint2 *code, uint32_t n_entries,
         switch (key) {
 #define GINT_CASE_SP(num, spv)                                                                          \
     case (spv) * GINT_N_DISPATCH + (num):                                                                \
-        if constexpr (op_valid<num, spv, P>()) {                                                        \
+        if constexpr (op_valid<num, spv, P, K>()) {                                                     \
             asm volatile("// GINT_TARGET %0;" ::"n"((spv) * GINT_N_DISPATCH + (num)));                   \
             if constexpr ((num) == OP_Halt) return;                                                     \
             else {                                                                                      \
@@ -1146,6 +1197,9 @@ __device__ __forceinline__ void interpret(const uint2 *code, uint32_t n_entries,
 #undef GINT_CASE_SP
         default:
             asm volatile("// GINT_TARGET default;");
+#ifdef GINT_CHECKED
+            chk_record(GINT_DEVICE_BAD_DISPATCH, -1, (u64)key);
+#endif
             return;
         }
     }
@@ -1203,7 +1257,7 @@ static __device__ __noinline__ void stage_for_warp(uint2 *code_s, const uint2 *c
 
 /* Direct mode: every logical program runs the same bytecode. Persistent blocks of kWarpsPerBlock warps;
  * shared memory = [program | descriptor block | kWarpsPerBlock x K TileInfo | kWarpsPerBlock x load staging]. */
-template <int P, int K>
+template <int P, int K, bool THREADED = true>
 __device__ __forceinline__ void geval_direct_body(const LaunchArgs &a)
 {
     extern __shared__ __align__(16) unsigned char smem[];
@@ -1226,6 +1280,16 @@ __device__ __forceinline__ void geval_direct_body(const LaunchArgs &a)
         int *dst = reinterpret_cast<int *>(ti_s);
         for (uint32_t i = threadIdx.x; i < sizeof(gint_tensor_info) / 4; i += kThreadsPerBlock) dst[i] = src[i];
     }
+#ifdef GINT_CHECKED
+    if (threadIdx.x < GINT_MAX_TENSORS) {
+        g_chk.lo[threadIdx.x] = a.chk_lo[threadIdx.x];
+        g_chk.hi[threadIdx.x] = a.chk_hi[threadIdx.x];
+    }
+    if (threadIdx.x == 0) {
+        g_chk.status = reinterpret_cast<gint_device_status *>(a.chk_status);
+        g_chk.code_base = (uint32_t)__cvta_generic_to_shared(code_s);
+    }
+#endif
     __syncthreads();
 
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -1246,7 +1310,16 @@ __device__ __forceinline__ void geval_direct_body(const LaunchArgs &a)
         __syncwarp();  // every lane is done with the previous group's tile descriptors
         decode_tiles<K>(ti_s, (int)a.n_tensors, a.first + g * (uint32_t)K, a.end, cx.tiles, lane);
         if (a.prefetch_mask) prefetch_footprints<K>(a, cx.tiles, lane);
-        interpret<P, K, true, true>(code_s, a.n_slots, cx);
+#ifdef GINT_CHECKED
+        if (lane == 0) g_chk.logical[warp] = a.first + g * (uint32_t)K;
+        __syncwarp();
+#endif
+#ifdef GINT_CHECKED
+        /* the instruction budget: a stream entry stands for at most GINT_MAX_FUSED_LEN instructions (a fused handler) */
+        interpret<P, K, true, THREADED>(code_s, a.n_slots * (uint32_t)GINT_MAX_FUSED_LEN, cx);
+#else
+        interpret<P, K, true, THREADED>(code_s, a.n_slots, cx);
+#endif
     }
 }
 
@@ -1289,6 +1362,13 @@ __device__ __forceinline__ void geval_indirect_body(const IndirectArgs &a)
         gint_geval_indirect_##P(const __grid_constant__ gint::IndirectArgs a)                                   \
     {                                                                                                           \
         gint::geval_indirect_body<P>(a);                                                                        \
+    }
+/* The checked kernel: direct mode, one tile per warp, dispatch through a single jump table (compiles in seconds). */
+#define GINT_DEFINE_CHECKED_KERNEL(P)                                                                           \
+    extern "C" __global__ void __launch_bounds__(gint::kThreadsPerBlock, 4)                                      \
+        gint_geval_checked_##P(const __grid_constant__ gint::LaunchArgs a)                                       \
+    {                                                                                                           \
+        gint::geval_direct_body<P, 1, false>(a);                                                                \
     }
 #define GINT_DEFINE_DIRECT_KERNEL(P, K)                                                                         \
     extern "C" __global__ void __launch_bounds__(gint::kThreadsPerBlock, GINT_MIN_BLOCKS(P, K))                  \

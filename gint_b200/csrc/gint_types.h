@@ -68,6 +68,9 @@ struct LaunchArgs {
     Footprint fp[GINT_MAX_TENSORS];
     gint_tensor_info ti;      // descriptor block, base pointers patched per call: travels as a kernel parameter
     uint2 inline_code[kInlineCodeSlots];   // the program itself when it has at most kInlineCodeSlots entries (code == nullptr)
+    /* checked launches only (gint_execute_checked): declared byte range [lo, hi) of every tensor and the status word */
+    u64 chk_lo[GINT_MAX_TENSORS], chk_hi[GINT_MAX_TENSORS];
+    void *chk_status;
 };
 
 struct IndirectEntry {

@@ -14,6 +14,7 @@ extern "C" {
 
 #define GINT_DIRECT_VARIANTS(X) X(4, 1) X(4, 2) X(4, 4) X(7, 1) X(7, 2) X(12, 1) X(12, 2)
 #define GINT_INDIRECT_VARIANTS(X) X(12)
+#define GINT_CHECKED_VARIANTS(X) X(12)
 
 #define GINT_X_DECL(P, K)                                        \
     extern const unsigned char gint_cubin_direct_##P##_##K[];     \
@@ -24,6 +25,11 @@ GINT_DIRECT_VARIANTS(GINT_X_DECL)
     extern const unsigned char gint_cubin_indirect_##P[];   \
     extern const unsigned char gint_cubin_indirect_##P##_end[];
 GINT_INDIRECT_VARIANTS(GINT_X_DECL)
+#undef GINT_X_DECL
+#define GINT_X_DECL(P)                                    \
+    extern const unsigned char gint_cubin_checked_##P[];   \
+    extern const unsigned char gint_cubin_checked_##P##_end[];
+GINT_CHECKED_VARIANTS(GINT_X_DECL)
 #undef GINT_X_DECL
 
 #ifdef __cplusplus

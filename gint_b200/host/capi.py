@@ -60,6 +60,15 @@ GINT_ERR_NO_DEVICE = -9
 GINT_ERR_TOO_LARGE = -10
 GINT_ERR_OUT_OF_MEMORY = -11
 
+class DeviceStatusC(ctypes.Structure):
+    """gint_device_status"""
+    _fields_ = [("code", c_int32), ("slot", c_int32), ("logical_program", c_uint32), ("instruction", c_uint32), ("address", c_uint64),
+                ("lane", c_uint32), ("count", c_uint32)]
+
+
+DEVICE_CODES = {0: "ok", 1: "load out of range", 2: "store out of range", 3: "instruction budget exhausted", 4: "bad dispatch"}
+
+
 class PlanStepC(ctypes.Structure):
     """gint_plan_step"""
     _fields_ = [("handle", c_uint64), ("base_ptrs", c_uint64 * 8), ("n_tensors", c_int32), ("grid_dim", c_uint32)]
@@ -83,6 +92,8 @@ SIGNATURES = {
     "gint_execute": (c_int, [c_void_p, c_uint64, POINTER(c_uint64), c_int, c_uint32, c_void_p]),
     "gint_execute_range": (c_int, [c_void_p, c_uint64, POINTER(c_uint64), c_int, c_uint32, c_uint32, c_void_p]),
     "gint_execute_plan": (c_int, [c_void_p, POINTER(PlanStepC), c_int, c_void_p]),
+    "gint_execute_checked": (c_int, [c_void_p, c_uint64, POINTER(c_uint64), POINTER(c_uint64), POINTER(c_uint64), c_int, c_uint32, c_void_p]),
+    "gint_device_status_read": (c_int, [c_void_p, POINTER(DeviceStatusC), c_int]),
     "gint_execute_indirect": (c_int, [c_void_p, POINTER(c_uint64), c_int, POINTER(c_uint64), POINTER(c_int32), c_uint32, c_void_p]),
     "gint_execute_indirect_static": (c_int, [c_void_p, POINTER(c_uint64), c_int, POINTER(c_uint64), POINTER(c_int32), c_uint32, c_void_p]),
     "gint_set_option": (c_int, [c_void_p, c_char_p, c_int]),

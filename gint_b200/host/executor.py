@@ -269,6 +269,38 @@ class B200Executor(BaseExecutor):
             self._check(ctx, rc, "gint_execute")
         self.launches += 1
 
+    def execute_checked(self, program: BaseExecutableProgram, args: Sequence[TensorInterface], grid_dim: int, cuda_stream: int = 0,
+                        **extra_kwargs):
+        """``execute`` on the bounds-checking kernel (``gint_execute_checked``): every access is compared with the byte range
+        of the tensor VIEW that was passed (base pointer, shape and strides of its ``TensorInterface``); an access outside it
+        is skipped and recorded. Read the outcome with ``device_status()``. For developing programs and descriptors; slow."""
+        ctx, line = self._cacheline(program, args, extra_kwargs)
+        n = line.n
+        ptrs, lo, hi = line.ptrs, (ctypes.c_uint64 * MAX_N_TENSORS)(), (ctypes.c_uint64 * MAX_N_TENSORS)()
+        for i, a in enumerate(line.indices):
+            t = args[a]
+            ptrs[i] = t.base_ptr
+            below = sum(min(0, (s - 1) * st) for s, st in zip(t.shape, t.strides) if s > 0)
+            above = sum(max(0, (s - 1) * st) for s, st in zip(t.shape, t.strides) if s > 0)
+            empty = any(s == 0 for s in t.shape)
+            lo[i] = t.base_ptr + below * t.elm_size
+            hi[i] = lo[i] if empty else t.base_ptr + (above + 1) * t.elm_size
+        rc = self._lib.gint_execute_checked(ctx, line.handle, ptrs, lo, hi, n, grid_dim, cuda_stream)
+        if rc != 0:
+            self._check(ctx, rc, "gint_execute_checked")
+        self.launches += 1
+
+    def device_status(self, clear: bool = True, device: Optional[int] = None) -> dict:
+        """What the checked launches on ``device`` found so far (waits for the device): ``code`` 0 means nothing; otherwise
+        the first event's kind, tensor slot, logical program, instruction index, address and lane, and the event count."""
+        _, ctx = self._ctx(device)
+        st = capi.DeviceStatusC()
+        rc = self._lib.gint_device_status_read(ctx, ctypes.byref(st), 1 if clear else 0)
+        self._check(ctx, rc, "gint_device_status_read")
+        out = {name: getattr(st, name) for name, _ in capi.DeviceStatusC._fields_}
+        out["what"] = capi.DEVICE_CODES.get(st.code, "unknown")
+        return out
+
     def execute_range(self, program: BaseExecutableProgram, args: Sequence[TensorInterface], first: int, count: int,
                       cuda_stream: int = 0, **extra_kwargs):
         """Run logical programs ``[first, first + count)`` of the program's grid (multi-GPU sharding primitive)."""

@@ -79,6 +79,25 @@ typedef struct gint_launch_info {
     int32_t reserved[7];
 } gint_launch_info;
 
+/* What a checked launch (gint_execute_checked) found; all zero = nothing. The FIRST event is described, `count` counts all. */
+typedef enum gint_device_code {
+    GINT_DEVICE_OK = 0,
+    GINT_DEVICE_LOAD_OUT_OF_RANGE = 1,    /* a tile load or gather outside the tensor's declared byte range: skipped, value 0 */
+    GINT_DEVICE_STORE_OUT_OF_RANGE = 2,   /* a tile store or scatter outside it: skipped */
+    GINT_DEVICE_INSTRUCTION_BUDGET = 3,   /* more instructions executed than the program holds (a dispatch error): stopped */
+    GINT_DEVICE_BAD_DISPATCH = 4          /* no handler for an (opcode, stack depth) pair; `address` holds the key: stopped */
+} gint_device_code;
+
+typedef struct gint_device_status {
+    int32_t code;             /* gint_device_code of the first event */
+    int32_t slot;             /* tensor slot of the access, -1 if not applicable */
+    uint32_t logical_program; /* logical program (warp tile) in which it happened */
+    uint32_t instruction;     /* index of the instruction in the bytecode stream */
+    uint64_t address;         /* the address that was refused */
+    uint32_t lane;            /* lane of the warp (0..31) */
+    uint32_t count;           /* number of events in all */
+} gint_device_status;
+
 typedef struct gint_ctx gint_ctx;
 
 /* ---- host-only helpers: no GPU needed ---------------------------------------------------------- */
@@ -149,6 +168,19 @@ int gint_execute(gint_ctx *ctx, uint64_t handle, const uint64_t *base_ptrs, int 
  * shard's byte offset). No counterpart in the reference, which is single-GPU. */
 int gint_execute_range(gint_ctx *ctx, uint64_t handle, const uint64_t *base_ptrs, int n_tensors, uint32_t first,
                        uint32_t count, void *cuda_stream);
+
+/* gint_execute with every global-memory access checked: `lo[i]` / `hi[i]` give the byte range [lo, hi) that descriptor slot i
+ * may touch (the tensor view the caller handed over). The program runs as written, on a slower kernel (one logical program
+ * per warp, no early-issued loads, no fused handlers); an access outside its tensor's range is not performed (a load yields
+ * 0) and is recorded in a status word that gint_device_status_read returns. The reference has no counterpart: an invalid
+ * program is undefined behaviour there (gint/kernel/interpreter/main.py:245-248) and the only tool is an external memory
+ * checker; this is the bounds-checking debug mode for program and descriptor development. Allocates the status word on first
+ * use; not for stream capture. */
+int gint_execute_checked(gint_ctx *ctx, uint64_t handle, const uint64_t *base_ptrs, const uint64_t *lo, const uint64_t *hi,
+                         int n_tensors, uint32_t grid_dim, void *cuda_stream);
+
+/* Wait for the device, copy the status word of the checked launches so far into *out and, if `clear` is not 0, reset it. */
+int gint_device_status_read(gint_ctx *ctx, gint_device_status *out, int clear);
 
 /* One step of a plan: a program, the device addresses of its tensors and its logical grid. */
 typedef struct gint_plan_step {

@@ -273,3 +273,18 @@ def test_launch_info_reports_geometry():
         assert info["tiles_per_warp"] in (1, 2, 4)
         assert info["num_sms"] == torch.cuda.get_device_properties(0).multi_processor_count
         assert info["grid_blocks"] >= 1 and info["regs_per_thread"] > 0 and info["smem_bytes"] > 0
+
+
+def test_indirect_launch_runs_lane_broadcasts_of_a_small_pool_program():
+    """bmm4x4 needs 7 pool slots, so its DupBroadcastW instructions are pre-decoded into their index-in-the-opcode form; the
+    indirect kernel (12 slots) must carry those handlers too. Same bits as the direct launch."""
+    import cases as C
+    ex = get_executor()
+    g = torch.Generator().manual_seed(11)
+    a, b = torch.randn(64, 16, generator=g).cuda(), torch.randn(64, 16, generator=g).cuda()
+    direct, indirect = torch.zeros(64, 16, device="cuda"), torch.zeros(64, 16, device="cuda")
+    C.bmm4x4(a, b, direct, grid_dim=2)
+    ex.execute_indirect([C.bmm4x4], [(a, b, indirect)], [0, 0])       # both warps run logical programs 0 and 1 of the same program
+    torch.cuda.synchronize()
+    assert bits_equal(indirect, direct), mismatch_report(indirect, direct)
+    torch.testing.assert_close(direct, torch.bmm(a.view(-1, 4, 4), b.view(-1, 4, 4)).reshape(-1, 16), rtol=1e-5, atol=1e-5)
