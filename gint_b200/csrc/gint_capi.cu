@@ -849,7 +849,7 @@ struct StaticScratch {
     gint::IndirectEntry table[GINT_STATIC_MAX_GRID];       // per-logical-program {code, descriptors, length}
 };
 
-/* 136 KiB that every GPU which loads this library holds until the process exits. In host code this name is only a
+/* 166 KiB that every GPU which loads this library holds until the process exits. In host code this name is only a
  * stand-in for the device object: it must never be handed to a kernel; the device address comes from
  * cudaGetSymbolAddress (static_scratch_for_device below). */
 static __device__ __align__(256) unsigned char g_static_scratch[sizeof(StaticScratch)];
@@ -1352,7 +1352,8 @@ int gint_execute_indirect(gint_ctx *ctx, const uint64_t *handles, int n_programs
         h_tab[i].code = progs[(size_t)indices[i]]->code_dev;
         h_tab[i].ti = d_ti + indices[i];
         h_tab[i].n_slots = progs[(size_t)indices[i]]->n_slots;
-        h_tab[i].reserved = 0;
+        h_tab[i].patch_slot = 0;
+        h_tab[i].patch_ptr = 0;
     }
     cudaError_t e = cudaMemcpyAsync(ctx->ind_dev, ctx->ind_host, need, cudaMemcpyHostToDevice, stream);
     if (e != cudaSuccess) return fail(ctx, GINT_ERR_CUDA, "cudaMemcpyAsync(indirect tables)", e);
@@ -1379,6 +1380,105 @@ int gint_execute_indirect(gint_ctx *ctx, const uint64_t *handles, int n_programs
     /* recorded whether or not the launch succeeded: the next call waits on this event and it must not be left unrecorded */
     cudaEventRecord(ctx->ind_kernel_event, stream);
     if (e != cudaSuccess) return fail(ctx, GINT_ERR_CUDA, "cudaLaunchKernel(indirect)", e);
+    return GINT_OK;
+}
+
+int gint_execute_batch(gint_ctx *ctx, const int32_t *codes, int n_programs, int n_words, const gint_tensor_info *ti, int n_tensors,
+                       const uint64_t *base_ptrs, int out_slot, uint64_t out_stride_bytes, int32_t *status_out, void *cuda_stream)
+{
+    if (!ctx || !codes || !ti || !base_ptrs || n_programs < 0 || n_words <= 0 || (n_words & 1)) return fail(ctx, GINT_ERR_INVALID_ARGUMENT, "null or malformed argument");
+    if (n_tensors < 1 || n_tensors > GINT_MAX_TENSORS || out_slot < 0 || out_slot >= n_tensors) return fail(ctx, GINT_ERR_INVALID_ARGUMENT, "tensor count or output slot out of range");
+    if (n_programs == 0) return GINT_OK;
+    if (!ctx->indirect.ok) return fail(ctx, GINT_ERR_NO_DEVICE, "indirect kernel image not usable on this device");
+    /* every candidate is pre-decoded into a slice of `stride` entries: its instructions, the lead entry and the tail */
+    const uint32_t stride = (uint32_t)((n_words / 2 + 4 + 1) & ~1);
+    const uint32_t code_smem = (stride * 8u + 127u) & ~127u;
+    const uint32_t smem = (uint32_t)gint::kWarpsPerBlock * ((uint32_t)sizeof(gint::TileInfo) + (uint32_t)gint::kTensorInfoSmemBytes + code_smem);
+    if ((int)smem > ctx->max_smem_optin) return fail(ctx, GINT_ERR_TOO_LARGE, "candidate programs too long for indirect mode (shared memory)");
+
+    DeviceGuard guard(ctx->device);
+    cudaStream_t stream = (cudaStream_t)cuda_stream;
+    {
+        int rc = refuse_capture(ctx, stream, "gint_execute_batch");
+        if (rc != GINT_OK) return rc;
+    }
+    std::lock_guard<std::mutex> ind_lock(ctx->ind_mu);
+    /* scratch layout: [one gint_tensor_info, padded to 640 | n_programs x IndirectEntry | n_programs x stride x uint2] */
+    const size_t ti_bytes = 640, tab_bytes = (size_t)n_programs * sizeof(IndirectEntry);
+    const size_t code_off = (ti_bytes + tab_bytes + 15) & ~(size_t)15;
+    const size_t need = code_off + (size_t)n_programs * stride * sizeof(uint2);
+    if (need > ctx->ind_bytes) {
+        if (ctx->ind_event) cudaEventSynchronize(ctx->ind_event);
+        if (ctx->ind_kernel_event) cudaEventSynchronize(ctx->ind_kernel_event);
+        if (ctx->ind_dev) { cudaFree(ctx->ind_dev); ctx->ind_dev = nullptr; }
+        if (ctx->ind_host) { cudaFreeHost(ctx->ind_host); ctx->ind_host = nullptr; }
+        ctx->ind_bytes = 0;
+        const size_t cap = need < 65536 ? 65536 : need * 2;
+        cudaError_t e = cudaMalloc(&ctx->ind_dev, cap);
+        if (e != cudaSuccess) return fail(ctx, GINT_ERR_OUT_OF_MEMORY, "cudaMalloc(batch scratch)", e);
+        e = cudaMallocHost(&ctx->ind_host, cap);
+        if (e != cudaSuccess) { cudaFree(ctx->ind_dev); ctx->ind_dev = nullptr; return fail(ctx, GINT_ERR_OUT_OF_MEMORY, "cudaMallocHost(batch scratch)", e); }
+        ctx->ind_bytes = cap;
+    }
+    if (!ctx->ind_event) {
+        cudaError_t e = cudaEventCreateWithFlags(&ctx->ind_event, cudaEventDisableTiming);
+        if (e == cudaSuccess) e = cudaEventCreateWithFlags(&ctx->ind_kernel_event, cudaEventDisableTiming);
+        if (e != cudaSuccess) return fail(ctx, GINT_ERR_CUDA, "cudaEventCreate", e);
+    } else {
+        cudaEventSynchronize(ctx->ind_event);
+        cudaError_t e = cudaStreamWaitEvent(stream, ctx->ind_kernel_event, 0);
+        if (e != cudaSuccess) return fail(ctx, GINT_ERR_CUDA, "cudaStreamWaitEvent(batch)", e);
+    }
+    gint_tensor_info *h_ti = (gint_tensor_info *)ctx->ind_host;
+    IndirectEntry *h_tab = (IndirectEntry *)((char *)ctx->ind_host + ti_bytes);
+    uint2 *h_code = (uint2 *)((char *)ctx->ind_host + code_off);
+    const char *d_base = (const char *)ctx->ind_dev;
+    *h_ti = *ti;
+    for (int t = 0; t < n_tensors; t++) h_ti->base_ptr[t] = (int64_t)base_ptrs[t];
+    std::vector<uint2> pre;
+    int n_valid = 0;
+    for (int i = 0; i < n_programs; i++) {
+        IndirectEntry &en = h_tab[i];
+        en.code = (const uint2 *)(d_base + code_off) + (size_t)i * stride;
+        en.ti = (const gint_tensor_info *)d_base;
+        en.patch_slot = (uint32_t)out_slot + 1u;
+        en.patch_ptr = base_ptrs[out_slot] + (uint64_t)i * out_stride_bytes;
+        const int rc = predecode(codes + (size_t)i * (size_t)n_words, n_words, n_tensors, &pre);
+        if (status_out) status_out[i] = rc;
+        if (rc != GINT_OK || pre.size() > stride) {
+            if (status_out && rc == GINT_OK) status_out[i] = GINT_ERR_TOO_LARGE;
+            en.n_slots = 0;                 // the warp skips this candidate; its output row is left as it is
+            continue;
+        }
+        en.n_slots = (uint32_t)pre.size();
+        memcpy(h_code + (size_t)i * stride, pre.data(), pre.size() * sizeof(uint2));
+        n_valid++;
+    }
+    cudaError_t e = cudaMemcpyAsync(ctx->ind_dev, ctx->ind_host, need, cudaMemcpyHostToDevice, stream);
+    if (e != cudaSuccess) return fail(ctx, GINT_ERR_CUDA, "cudaMemcpyAsync(batch tables)", e);
+    cudaEventRecord(ctx->ind_event, stream);
+    if (n_valid == 0) { cudaEventRecord(ctx->ind_kernel_event, stream); return GINT_OK; }
+
+    IndirectArgs a;
+    a.table = (const IndirectEntry *)(d_base + ti_bytes);
+    a.n_tensors = (uint32_t)n_tensors;
+    a.grid_dim = (uint32_t)n_programs;
+    a.code_smem_bytes = code_smem;
+    a.reserved = 0;
+    if (smem > 48u * 1024u) {
+        e = cudaFuncSetAttribute(ctx->indirect.fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return fail(ctx, GINT_ERR_CUDA, "cudaFuncSetAttribute(indirect)", e);
+    }
+    int bps = 0;
+    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&bps, ctx->indirect.fn, gint::kThreadsPerBlock, smem);
+    if (e != cudaSuccess || bps < 1) return fail(ctx, GINT_ERR_CUDA, "occupancy query (indirect)", e);
+    uint64_t blocks = ((uint64_t)n_programs + gint::kWarpsPerBlock - 1) / gint::kWarpsPerBlock;
+    const uint64_t resident = (uint64_t)bps * (uint64_t)ctx->num_sms;
+    if (blocks > resident) blocks = resident;
+    void *args[1] = {&a};
+    e = cudaLaunchKernel(ctx->indirect.fn, dim3((unsigned)blocks), dim3(gint::kThreadsPerBlock), args, smem, stream);
+    cudaEventRecord(ctx->ind_kernel_event, stream);
+    if (e != cudaSuccess) return fail(ctx, GINT_ERR_CUDA, "cudaLaunchKernel(batch)", e);
     return GINT_OK;
 }
 
@@ -1429,7 +1529,8 @@ int gint_execute_indirect_static(gint_ctx *ctx, const uint64_t *handles, int n_p
             h->table[i].code = progs[indices[i]]->code_dev;
             h->table[i].ti = d->ti + indices[i];
             h->table[i].n_slots = progs[indices[i]]->n_slots;
-            h->table[i].reserved = 0;
+            h->table[i].patch_slot = 0;
+            h->table[i].patch_ptr = 0;
         }
         /* Two copies of exactly the used parts. The source is ordinary (pageable) host memory: the runtime stages it and
          * returns once the host image may be reused by the next call. */

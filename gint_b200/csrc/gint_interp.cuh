@@ -1348,7 +1348,12 @@ __device__ __forceinline__ void geval_indirect_body(const IndirectArgs &a)
     for (uint32_t g = blockIdx.x * kWarpsPerBlock + warp; g < a.grid_dim; g += gridDim.x * kWarpsPerBlock) {
         const IndirectEntry e = a.table[g];
         __syncwarp();  // every lane is done with the previous program's code and descriptors
+        if (e.n_slots == 0) continue;   // warp-uniform: the entry belongs to the whole warp
         stage_for_warp(code_s, e.code, e.n_slots, ti_s, e.ti, lane);
+        if (e.patch_slot) {
+            if (lane == 0) ti_s->base_ptr[e.patch_slot - 1u] = (int64_t)e.patch_ptr;
+            __syncwarp();
+        }
         decode_tiles<1>(ti_s, (int)a.n_tensors, g, a.grid_dim, cx.tiles, lane);
         interpret<P, 1, true, false>(code_s, e.n_slots, cx);
     }

@@ -76,8 +76,9 @@ struct LaunchArgs {
 struct IndirectEntry {
     const uint2 *code;              // pre-decoded program of this logical program
     const gint_tensor_info *ti;     // its descriptor block in device memory
-    uint32_t n_slots;               // entries in `code`
-    uint32_t reserved;
+    uint32_t n_slots;               // entries in `code`; 0: nothing to run (an invalid candidate of a batch)
+    uint32_t patch_slot;            // 1 + tensor slot whose base pointer is replaced by patch_ptr for this logical program; 0: none
+    u64 patch_ptr;                  // (batches of candidate programs share one descriptor block and differ in one pointer)
 };
 
 

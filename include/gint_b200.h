@@ -210,9 +210,22 @@ int gint_execute_plan(gint_ctx *ctx, const gint_plan_step *steps, int n_steps, v
 int gint_execute_indirect(gint_ctx *ctx, const uint64_t *handles, int n_programs, const uint64_t *base_ptrs,
                           const int32_t *indices, uint32_t grid_dim, void *cuda_stream);
 
+/* A batch of candidate programs, one launch: candidate i (the n_words int32 words at codes + i * n_words) runs as ONE logical
+ * program over the tensors of `base_ptrs` with the descriptors of `ti`, except that the base pointer of descriptor slot
+ * `out_slot` is base_ptrs[out_slot] + i * out_stride_bytes (every candidate writes its own output row). Replaces the batch
+ * path of the reference's superoptimizer example (examples/superopt/executor.py:100-186: per candidate a 608-byte descriptor
+ * block is packed in Python, then bytecode, blocks and two pointer tables are uploaded and geval is launched with flag 1;
+ * its profile puts 55 % of the batch time into that packing loop, examples/superopt/bench/README.md:92-120): here the
+ * candidates are analysed and pre-decoded in C, ONE descriptor block is shared and the per-candidate pointer travels in the
+ * table entry. A candidate that fails the analysis (unknown opcode, stack underflow or overflow, no Halt) is skipped -- its
+ * output row is left as it is -- and its gint_status is stored in status_out[i] (0 for the others; status_out may be NULL).
+ * Shares the context's indirect scratch and its serialisation (see gint_execute_indirect); may allocate; not for capture. */
+int gint_execute_batch(gint_ctx *ctx, const int32_t *codes, int n_programs, int n_words, const gint_tensor_info *ti, int n_tensors,
+                       const uint64_t *base_ptrs, int out_slot, uint64_t out_stride_bytes, int32_t *status_out, void *cuda_stream);
+
 /* Indirect launch that allocates nothing. No counterpart in the reference (whose execute_indirect allocates and frees
  * on every call). Same arguments and same results as gint_execute_indirect, but the per-launch tables (one descriptor
- * block per program, one {program, descriptors} entry per logical program) are written into a fixed 136 KiB array that
+ * block per program, one {program, descriptors} entry per logical program) are written into a fixed 166 KiB array that
  * lives in the library's device image, not into context scratch that grows with cudaMalloc. It exists for callers that
  * are not allowed to allocate device memory when they launch: processes whose whole device-memory budget has been handed
  * to another allocator (a framework's caching pool, a partitioned inference server), control loops with a hard deadline
