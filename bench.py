@@ -121,6 +121,31 @@ def dist_setup(n_gpus: int):
     return rank, world, local
 
 
+def pin_to_gpu_numa_node(local: int):
+    """Run this rank's host threads on the CPUs next to its GPU, so that the pinned host buffers of the end-to-end leg
+    (allocated afterwards, first touch) and the copies' staging live on the GPU's own NUMA node instead of all ranks sharing
+    node 0. Returns a short description, or None when the topology cannot be read."""
+    try:
+        prop = torch.cuda.get_device_properties(local)
+        bdf = f"{prop.pci_domain_id:04x}:{prop.pci_bus_id:02x}:{prop.pci_device_id:02x}.0"
+        with open(f"/sys/bus/pci/devices/{bdf}/local_cpulist") as f:
+            text = f.read().strip()
+        cpus = set()
+        for part in text.split(","):
+            lo, _, hi = part.partition("-")
+            cpus.update(range(int(lo), int(hi or lo) + 1))
+        allowed = os.sched_getaffinity(0)
+        cpus &= allowed
+        if not cpus:
+            return None
+        os.sched_setaffinity(0, cpus)
+        with open(f"/sys/bus/pci/devices/{bdf}/numa_node") as f:
+            node = f.read().strip()
+        return f"gpu {local} ({bdf}): numa node {node}, {len(cpus)} cpus"
+    except Exception:
+        return None
+
+
 def barrier(world: int):
     torch.cuda.synchronize()
     if world > 1:
@@ -264,9 +289,13 @@ def run_program_bench(name: str, world: int, rank: int, steps: int, warmup: int,
         if impl == "reference_kernel":
             ref_harness.run_workload(wl, stream)
         else:
-            if wl.pre is not None:
-                wl.pre(wl.tensors)
-            plans[state["i"] % n_sets].run(stream)
+            plan = plans[state["i"] % n_sets]
+            if plan is None:               # gathered rows: plain executor calls
+                wl.run(ex, stream)
+            else:
+                if wl.pre is not None:
+                    wl.pre(wl.tensors)
+                plan.run(stream)
         state["i"] += 1
     for _ in range(max(3, warmup, n_sets)):   # every buffer set once at least: its program is built on first use
         step()
@@ -287,7 +316,7 @@ def run_program_bench(name: str, world: int, rank: int, steps: int, warmup: int,
                 "frac_of_measured_peak": total_bytes / (per_step_ms * 1e-3) / 1e9 / (peak_gbs * world)}, wls
     info = ex.launch_info(st.program, [wl.tensors[r] for r in st.roles], st.grid_dim)
     split = {}
-    if wl.pre is None and world == 1:
+    if wl.pre is None and world == 1 and plans[0] is not None:
         # host and device separated: the event-timed figure above includes whatever the host fails to hide
         try:
             split = {"device_us_per_launch": graph_replay_us(wls, ex, max(10, steps)),
@@ -422,6 +451,7 @@ def main():
         return 1
     rank, world, local = dist_setup(opts.gpus)
     torch.cuda.set_device(local)
+    numa = pin_to_gpu_numa_node(local) if world > 1 else None
 
     sampler = ClockSampler(local) if rank == 0 else None
     if sampler:
@@ -438,7 +468,8 @@ def main():
 
     programs = {}
     if opts.programs == "all":
-        for other in ("add", "rmsnorm", "bmm4x4", "inv4x4", "graph"):
+        # the five named programs, and the conductor graph once more with its gather folded into the fused program's loads
+        for other in ("add", "rmsnorm", "bmm4x4", "inv4x4", "graph", "graph_gathered"):
             if other == name:
                 programs[other] = res
                 continue
@@ -485,6 +516,8 @@ def main():
             line["reference_kernel_unavailable"] = ref_kernel_note
         if strong is not None:
             line["strong_scaling"] = strong
+        if numa:
+            line["host_placement"] = numa
         if not opts.no_cpu:
             gbs, desc, cores, ms, wl_cpu = cpu_reference(name, budget_s=10.0)
             line["cpu_baseline"] = {"value": gbs, "unit": "GB/s", "cores": cores, "kind": "reference", "sample": desc}

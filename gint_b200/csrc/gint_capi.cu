@@ -773,8 +773,14 @@ int plan_direct(gint_ctx *ctx, const Program *p, const StreamView &sv, uint32_t 
     return GINT_OK;
 }
 
+struct GatherArgs {
+    uint32_t mask;            // tensor slots whose innermost batch index goes through the row index
+    const long long *index;   // device pointer
+    uint64_t extent_bytes;    // bytes of the gathered tensor(s) that the index can reach, from the base pointer
+};
+
 int launch_direct(gint_ctx *ctx, uint64_t handle, const uint64_t *base_ptrs, int n_tensors, uint32_t first, uint32_t count,
-                  void *stream)
+                  void *stream, const GatherArgs *gather = nullptr)
 {
     if (!ctx || (!base_ptrs && n_tensors > 0)) return fail(ctx, GINT_ERR_INVALID_ARGUMENT, "null argument");
     Program *p = lookup(ctx, handle);
@@ -790,7 +796,9 @@ int launch_direct(gint_ctx *ctx, uint64_t handle, const uint64_t *base_ptrs, int
         if (!p->alias_slots[t]) continue;
         for (int b = 0; early && b < n_tensors; b++) {
             if (!((p->alias_slots[t] >> b) & 1u)) continue;
-            const uint64_t a0 = base_ptrs[t], a1 = a0 + p->extent[t], b0 = base_ptrs[b], b1 = b0 + p->extent[b];
+            const bool ga = gather && ((gather->mask >> t) & 1u), gb = gather && ((gather->mask >> b) & 1u);
+            const uint64_t a0 = base_ptrs[t], a1 = a0 + (ga ? gather->extent_bytes : p->extent[t]);
+            const uint64_t b0 = base_ptrs[b], b1 = b0 + (gb ? gather->extent_bytes : p->extent[b]);
             if (a0 < b1 && b0 < a1) early = false;
         }
     }
@@ -824,6 +832,10 @@ int launch_direct(gint_ctx *ctx, uint64_t handle, const uint64_t *base_ptrs, int
     a.row_area_bytes = sv.row_area_bytes;
     a.ring_bytes = sv.ring_bytes;
     a.reserved = 0;
+    a.gather_mask = gather ? gather->mask : 0u;
+    a.gather_index = gather ? gather->index : nullptr;
+    a.reserved2 = 0;
+    a.chk_status = nullptr;
     if (a.prefetch_mask)
         for (int t = 0; t < GINT_MAX_TENSORS; t++) a.fp[t] = p->fp[t];
     a.ti = p->ti;
@@ -1191,6 +1203,17 @@ int gint_execute_range(gint_ctx *ctx, uint64_t handle, const uint64_t *base_ptrs
                        void *cuda_stream)
 {
     return launch_direct(ctx, handle, base_ptrs, n_tensors, first, count, cuda_stream);
+}
+
+int gint_execute_gathered(gint_ctx *ctx, uint64_t handle, const uint64_t *base_ptrs, int n_tensors, uint32_t grid_dim, uint32_t gather_mask,
+                          const int64_t *row_index, uint64_t gathered_extent_bytes, void *cuda_stream)
+{
+    if (!ctx) return GINT_ERR_INVALID_ARGUMENT;
+    if (gather_mask == 0) return launch_direct(ctx, handle, base_ptrs, n_tensors, 0u, grid_dim, cuda_stream);
+    if (!row_index) return fail(ctx, GINT_ERR_INVALID_ARGUMENT, "gathered rows need a row index");
+    if (n_tensors < 0 || n_tensors > GINT_MAX_TENSORS || (gather_mask >> n_tensors) != 0) return fail(ctx, GINT_ERR_INVALID_ARGUMENT, "gather mask names a slot the program does not have");
+    GatherArgs ga{gather_mask, reinterpret_cast<const long long *>(row_index), gathered_extent_bytes};
+    return launch_direct(ctx, handle, base_ptrs, n_tensors, 0u, grid_dim, cuda_stream, &ga);
 }
 
 int gint_execute_checked(gint_ctx *ctx, uint64_t handle, const uint64_t *base_ptrs, const uint64_t *lo, const uint64_t *hi, int n_tensors,

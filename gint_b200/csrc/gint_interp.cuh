@@ -369,7 +369,8 @@ __device__ __forceinline__ void tile_indirect(const TileInfo *ti, uint32_t opera
 
 template <int K>
 __device__ __forceinline__ void decode_tiles(const gint_tensor_info *__restrict__ ti, int n_tensors, uint32_t first_idx,
-                                             uint32_t end_idx, TileInfo *tiles, int lane)
+                                             uint32_t end_idx, TileInfo *tiles, int lane, uint32_t gather_mask = 0u,
+                                             const long long *__restrict__ gather_index = nullptr)
 {
     const int k = lane >> 3, t = lane & 7;
     if (k < K) {
@@ -393,6 +394,15 @@ __device__ __forceinline__ void decode_tiles(const gint_tensor_info *__restrict_
 #pragma unroll
             for (int j = 0; j < 4; j++) {
                 const uint32_t sz = (uint32_t)ti->batch_shape[t][j];
+                if (j == 0 && ((gather_mask >> t) & 1u)) {
+                    /* gathered rows: the innermost batch index selects an entry of the row index, which takes its place
+                     * (tensor[index[b]] without the copy; 64-bit index values, 32-bit offset arithmetic like every other term) */
+                    const uint32_t q = sz != 1u ? r / sz : r;
+                    const uint32_t b = sz != 1u ? r - q * sz : 0u;
+                    off += (uint32_t)ti->batch_strides[t][0] * (uint32_t)gather_index[b];
+                    r = q;
+                    continue;
+                }
                 if (sz != 1u && r != 0u) {
                     const uint32_t q = r / sz;
                     off += (uint32_t)ti->batch_strides[t][j] * (r - q * sz);
@@ -1308,7 +1318,7 @@ __device__ __forceinline__ void geval_direct_body(const LaunchArgs &a)
     const uint32_t n_groups = (a.end - a.first + (uint32_t)K - 1u) / (uint32_t)K;
     for (uint32_t g = blockIdx.x * kWarpsPerBlock + warp; g < n_groups; g += gridDim.x * kWarpsPerBlock) {
         __syncwarp();  // every lane is done with the previous group's tile descriptors
-        decode_tiles<K>(ti_s, (int)a.n_tensors, a.first + g * (uint32_t)K, a.end, cx.tiles, lane);
+        decode_tiles<K>(ti_s, (int)a.n_tensors, a.first + g * (uint32_t)K, a.end, cx.tiles, lane, a.gather_mask, a.gather_index);
         if (a.prefetch_mask) prefetch_footprints<K>(a, cx.tiles, lane);
 #ifdef GINT_CHECKED
         if (lane == 0) g_chk.logical[warp] = a.first + g * (uint32_t)K;

@@ -71,6 +71,11 @@ struct LaunchArgs {
     /* checked launches only (gint_execute_checked): declared byte range [lo, hi) of every tensor and the status word */
     u64 chk_lo[GINT_MAX_TENSORS], chk_hi[GINT_MAX_TENSORS];
     void *chk_status;
+    /* gathered rows (gint_execute_gathered): for the tensor slots in gather_mask the index along the innermost batch dimension
+     * is replaced by gather_index[that index] before it is multiplied by the batch stride */
+    const long long *gather_index;
+    uint32_t gather_mask;
+    uint32_t reserved2;
 };
 
 struct IndirectEntry {

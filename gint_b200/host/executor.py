@@ -269,6 +269,26 @@ class B200Executor(BaseExecutor):
             self._check(ctx, rc, "gint_execute")
         self.launches += 1
 
+    def execute_gathered(self, program: BaseExecutableProgram, args: Sequence[TensorInterface], grid_dim: int, gathered: Sequence[int],
+                         row_index, cuda_stream: int = 0, **extra_kwargs):
+        """``execute`` in which the arguments listed in ``gathered`` (argument indices) are TABLES read through ``row_index``:
+        logical program b works on row ``row_index[b]`` of such a tensor instead of row b (its descriptor's innermost batch
+        dimension). ``row_index`` is an int64 device tensor. ``table[index]`` feeds the program without a gather kernel and an
+        intermediate copy (``gint_execute_gathered``)."""
+        ctx, line = self._cacheline(program, args, extra_kwargs)
+        ptrs = line.ptrs
+        mask, extent = 0, 0
+        for i, a in enumerate(line.indices):
+            ptrs[i] = args[a].base_ptr
+            if a in gathered:
+                mask |= 1 << i
+                t = args[a]
+                extent = max(extent, (sum((s - 1) * abs(st) for s, st in zip(t.shape, t.strides) if s > 0) + 1) * t.elm_size)
+        rc = self._lib.gint_execute_gathered(ctx, line.handle, ptrs, line.n, grid_dim, mask, ctypes.c_void_p(row_index.data_ptr()), extent, cuda_stream)
+        if rc != 0:
+            self._check(ctx, rc, "gint_execute_gathered")
+        self.launches += 1
+
     def execute_checked(self, program: BaseExecutableProgram, args: Sequence[TensorInterface], grid_dim: int, cuda_stream: int = 0,
                         **extra_kwargs):
         """``execute`` on the bounds-checking kernel (``gint_execute_checked``): every access is compared with the byte range

@@ -28,6 +28,8 @@ class Step:
     program: RecordedProgram
     roles: list[str]          # tensor role for each program argument
     grid_dim: int
+    gathered: tuple = ()      # argument positions that are tables read through `row_index` (B200Executor.execute_gathered)
+    row_index: str = ""       # role of the int64 row-index tensor
 
 
 @dataclass
@@ -50,7 +52,10 @@ class Workload:
         if self.pre is not None:
             self.pre(self.tensors)
         for st, args in zip(self.steps, self._interfaces()):
-            executor.execute(st.program, args, st.grid_dim, cuda_stream=stream)
+            if st.gathered:
+                executor.execute_gathered(st.program, args, st.grid_dim, st.gathered, self.tensors[st.row_index], cuda_stream=stream)
+            else:
+                executor.execute(st.program, args, st.grid_dim, cuda_stream=stream)
 
     def _interfaces(self):
         """The steps' arguments as TensorInterfaces, converted once (a caller that launches the same tensors again and again
@@ -62,7 +67,10 @@ class Workload:
         return self._args_cache[1]
 
     def plan(self, executor):
-        """The bytecode steps as one reusable launch plan (``B200Executor.build_plan``); ``pre`` stays with the caller."""
+        """The bytecode steps as one reusable launch plan (``B200Executor.build_plan``); ``pre`` stays with the caller. None for a
+        workload with gathered rows (plans carry plain launches only)."""
+        if any(st.gathered for st in self.steps):
+            return None
         return executor.build_plan([(st.program, [self.tensors[r] for r in st.roles], st.grid_dim) for st in self.steps])
 
     def launches_per_run(self) -> int:
@@ -105,10 +113,10 @@ def eager_graph(t, eps: float = 1e-6):
     return {"z": z, "s": z.sum(-1)}
 
 
-EAGER = {"add": eager_add, "rmsnorm": eager_rmsnorm, "bmm4x4": eager_bmm, "inv4x4": eager_inv, "graph": eager_graph}
+EAGER = {"add": eager_add, "rmsnorm": eager_rmsnorm, "bmm4x4": eager_bmm, "inv4x4": eager_inv, "graph": eager_graph, "graph_gathered": eager_graph}
 
 FULL_SIZES = {"add": (1048576, 1), "rmsnorm": (16384, 4096), "bmm4x4": (4194304, 16), "inv4x4": (4194304, 16),
-              "graph": (65536, 1024)}
+              "graph": (65536, 1024), "graph_gathered": (65536, 1024)}
 GRAPH_TABLE_ROWS = 65536   # x_full of the conductor graph; replicated on every GPU because x_full[idx] reads any row
 
 
@@ -145,7 +153,7 @@ def make_workload(name: str, leading: Optional[int] = None, inner: Optional[int]
         t = {"a": a.reshape(leading, 16).contiguous(), "c": torch.zeros(leading, 16)}
         wl = Workload("inv4x4", "configs[3]: batched 4x4 inverse", leading, 16, steps=[Step(prog, prog.arg_roles, prog.grid_dim)],
                       outputs=["c"], elements=leading * 16, algorithmic_bytes=2 * 64 * leading, rtol=1e-4, atol=1e-4)
-    elif name == "graph":
+    elif name in ("graph", "graph_gathered"):
         fused = recorded(f"graph_fused_r{leading}_n{inner}")
         rowsum = recorded(f"graph_rowsum_r{leading}_n{inner}")
         table = table_rows or (GRAPH_TABLE_ROWS if inner == 1024 and leading >= 8192 else {96: 128, 10: 16}.get(leading, leading))
@@ -165,11 +173,21 @@ def make_workload(name: str, leading: Optional[int] = None, inner: Optional[int]
                       outputs=["z", "s"], pre=gather, elements=leading * inner,
                       # as executed (3 kernels): gather R+W, fused R(g)+R(x)+W(z), sum R(z); plus idx, w, s
                       algorithmic_bytes=leading * row * 6 + leading * 8 + 4 * inner + 4 * leading)
+        if name == "graph_gathered":
+            # the same two bytecode programs, but the fused one reads x_full[idx] in place: its `g` argument is the table and
+            # logical program b works on row idx[b] (gint_execute_gathered) -- no gather kernel, no intermediate g
+            g_pos = fused.arg_roles.index("g")
+            roles = [("x_full" if r == "g" else r) for r in fused.arg_roles]
+            wl = Workload("graph_gathered", "configs[4] with the gather folded into the fused program's row loads (2 kernels)", leading, inner,
+                          steps=[Step(fused, roles, fused.grid_dim, gathered=(g_pos,), row_index="idx"), Step(rowsum, rowsum.arg_roles, rowsum.grid_dim)],
+                          outputs=["z", "s"], pre=None, elements=leading * inner,
+                          # R(x_full[idx]) + R(x_rows) + W(z); sum R(z); plus idx, w, s
+                          algorithmic_bytes=leading * row * 4 + leading * 8 + 4 * inner + 4 * leading)
     else:
         raise KeyError(name)
 
     wl.tensors = {k: v.to(dev) for k, v in t.items()}
-    if name == "graph":
+    if name in ("graph", "graph_gathered"):
         # keep x_rows a view of the table on the device as well
         wl.tensors["x_rows"] = wl.tensors["x_full"][:leading]
     return wl

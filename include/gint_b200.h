@@ -182,6 +182,17 @@ int gint_execute_checked(gint_ctx *ctx, uint64_t handle, const uint64_t *base_pt
 /* Wait for the device, copy the status word of the checked launches so far into *out and, if `clear` is not 0, reset it. */
 int gint_device_status_read(gint_ctx *ctx, gint_device_status *out, int clear);
 
+/* gint_execute with gathered rows: for every descriptor slot in `gather_mask`, the index along the tensor's INNERMOST batch
+ * dimension -- b = 0 .. batch_shape-1, normally multiplied by the batch stride -- is first looked up in the device array
+ * row_index[b] (int64). Logical program b thus works on row row_index[b] of the tensor at base_ptrs[slot]: `table[index]` is
+ * read (or written) in place, without the separate gather kernel and the intermediate copy that the reference needs for the
+ * same graph (its conductor leaves aten.index.Tensor to torch eager, gint/conductor/op_registry.py:1058-1132; the interpreter's
+ * own gather opcode, 66, picks single elements). gathered_extent_bytes = bytes of the table reachable through the index, from
+ * its base pointer (used by the launch-time overlap check in place of the descriptor's extent). Offsets are 32-bit element
+ * counts like every other descriptor term. No counterpart in the reference. Same launch properties as gint_execute. */
+int gint_execute_gathered(gint_ctx *ctx, uint64_t handle, const uint64_t *base_ptrs, int n_tensors, uint32_t grid_dim,
+                          uint32_t gather_mask, const int64_t *row_index, uint64_t gathered_extent_bytes, void *cuda_stream);
+
 /* One step of a plan: a program, the device addresses of its tensors and its logical grid. */
 typedef struct gint_plan_step {
     uint64_t handle;

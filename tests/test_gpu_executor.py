@@ -288,3 +288,22 @@ def test_indirect_launch_runs_lane_broadcasts_of_a_small_pool_program():
     torch.cuda.synchronize()
     assert bits_equal(indirect, direct), mismatch_report(indirect, direct)
     torch.testing.assert_close(direct, torch.bmm(a.view(-1, 4, 4), b.view(-1, 4, 4)).reshape(-1, 16), rtol=1e-5, atol=1e-5)
+
+
+@pytest.mark.parametrize("leading,inner", [(10, 256), (96, 1024), (8192, 1024)])
+def test_gathered_rows_equal_gather_then_launch(leading, inner):
+    """The conductor graph with x_full[idx] read in place (gint_execute_gathered) gives the bits of the three-kernel form
+    (torch gather into g, fused program, row sum), and matches torch eager."""
+    from gint_b200.workloads import EAGER, check_outputs, make_workload
+    ex = get_executor()
+    three = make_workload("graph", leading, inner, device="cuda")
+    two = make_workload("graph_gathered", leading, inner, device="cuda")
+    three.run(ex, torch.cuda.current_stream().cuda_stream)
+    launches = ex.launches
+    two.run(ex, torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    assert ex.launches - launches == 2
+    for role in two.outputs:
+        assert bits_equal(two.tensors[role], three.tensors[role]), f"{role}: " + mismatch_report(two.tensors[role], three.tensors[role])
+    assert torch.equal(two.tensors["g"], torch.zeros_like(two.tensors["g"]))      # the intermediate was never written
+    check_outputs(two, EAGER["graph"]({k: v.cpu() for k, v in two.tensors.items()}))
