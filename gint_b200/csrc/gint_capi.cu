@@ -777,6 +777,7 @@ struct GatherArgs {
     uint32_t mask;            // tensor slots whose innermost batch index goes through the row index
     const long long *index;   // device pointer
     uint64_t extent_bytes;    // bytes of the gathered tensor(s) that the index can reach, from the base pointer
+    uint32_t rows;            // rows of the gathered table
 };
 
 int launch_direct(gint_ctx *ctx, uint64_t handle, const uint64_t *base_ptrs, int n_tensors, uint32_t first, uint32_t count,
@@ -834,7 +835,7 @@ int launch_direct(gint_ctx *ctx, uint64_t handle, const uint64_t *base_ptrs, int
     a.reserved = 0;
     a.gather_mask = gather ? gather->mask : 0u;
     a.gather_index = gather ? gather->index : nullptr;
-    a.reserved2 = 0;
+    a.gather_rows = gather ? gather->rows : 0u;
     a.chk_status = nullptr;
     if (a.prefetch_mask)
         for (int t = 0; t < GINT_MAX_TENSORS; t++) a.fp[t] = p->fp[t];
@@ -1206,13 +1207,13 @@ int gint_execute_range(gint_ctx *ctx, uint64_t handle, const uint64_t *base_ptrs
 }
 
 int gint_execute_gathered(gint_ctx *ctx, uint64_t handle, const uint64_t *base_ptrs, int n_tensors, uint32_t grid_dim, uint32_t gather_mask,
-                          const int64_t *row_index, uint64_t gathered_extent_bytes, void *cuda_stream)
+                          const int64_t *row_index, uint32_t table_rows, uint64_t gathered_extent_bytes, void *cuda_stream)
 {
     if (!ctx) return GINT_ERR_INVALID_ARGUMENT;
     if (gather_mask == 0) return launch_direct(ctx, handle, base_ptrs, n_tensors, 0u, grid_dim, cuda_stream);
-    if (!row_index) return fail(ctx, GINT_ERR_INVALID_ARGUMENT, "gathered rows need a row index");
+    if (!row_index || table_rows == 0) return fail(ctx, GINT_ERR_INVALID_ARGUMENT, "gathered rows need a row index and a table with at least one row");
     if (n_tensors < 0 || n_tensors > GINT_MAX_TENSORS || (gather_mask >> n_tensors) != 0) return fail(ctx, GINT_ERR_INVALID_ARGUMENT, "gather mask names a slot the program does not have");
-    GatherArgs ga{gather_mask, reinterpret_cast<const long long *>(row_index), gathered_extent_bytes};
+    GatherArgs ga{gather_mask, reinterpret_cast<const long long *>(row_index), gathered_extent_bytes, table_rows};
     return launch_direct(ctx, handle, base_ptrs, n_tensors, 0u, grid_dim, cuda_stream, &ga);
 }
 

@@ -370,7 +370,7 @@ __device__ __forceinline__ void tile_indirect(const TileInfo *ti, uint32_t opera
 template <int K>
 __device__ __forceinline__ void decode_tiles(const gint_tensor_info *__restrict__ ti, int n_tensors, uint32_t first_idx,
                                              uint32_t end_idx, TileInfo *tiles, int lane, uint32_t gather_mask = 0u,
-                                             const long long *__restrict__ gather_index = nullptr)
+                                             const long long *__restrict__ gather_index = nullptr, uint32_t gather_rows = 0u)
 {
     const int k = lane >> 3, t = lane & 7;
     if (k < K) {
@@ -399,7 +399,12 @@ __device__ __forceinline__ void decode_tiles(const gint_tensor_info *__restrict_
                      * (tensor[index[b]] without the copy; 64-bit index values, 32-bit offset arithmetic like every other term) */
                     const uint32_t q = sz != 1u ? r / sz : r;
                     const uint32_t b = sz != 1u ? r - q * sz : 0u;
-                    off += (uint32_t)ti->batch_strides[t][0] * (uint32_t)gather_index[b];
+                    /* torch's indexing rule for a negative index (counts from the end); an index that is still out of range --
+                     * an error in torch -- is clamped to the nearest row so that no access leaves the table */
+                    long long row = gather_index[b];
+                    if (row < 0) row += (long long)gather_rows;
+                    row = row < 0 ? 0 : row >= (long long)gather_rows ? (long long)gather_rows - 1 : row;
+                    off += (uint32_t)ti->batch_strides[t][0] * (uint32_t)row;
                     r = q;
                     continue;
                 }
@@ -1318,7 +1323,7 @@ __device__ __forceinline__ void geval_direct_body(const LaunchArgs &a)
     const uint32_t n_groups = (a.end - a.first + (uint32_t)K - 1u) / (uint32_t)K;
     for (uint32_t g = blockIdx.x * kWarpsPerBlock + warp; g < n_groups; g += gridDim.x * kWarpsPerBlock) {
         __syncwarp();  // every lane is done with the previous group's tile descriptors
-        decode_tiles<K>(ti_s, (int)a.n_tensors, a.first + g * (uint32_t)K, a.end, cx.tiles, lane, a.gather_mask, a.gather_index);
+        decode_tiles<K>(ti_s, (int)a.n_tensors, a.first + g * (uint32_t)K, a.end, cx.tiles, lane, a.gather_mask, a.gather_index, a.gather_rows);
         if (a.prefetch_mask) prefetch_footprints<K>(a, cx.tiles, lane);
 #ifdef GINT_CHECKED
         if (lane == 0) g_chk.logical[warp] = a.first + g * (uint32_t)K;

@@ -75,7 +75,7 @@ struct LaunchArgs {
      * is replaced by gather_index[that index] before it is multiplied by the batch stride */
     const long long *gather_index;
     uint32_t gather_mask;
-    uint32_t reserved2;
+    uint32_t gather_rows;     // rows of the gathered table: a negative index counts from the end, anything else is clamped into range
 };
 
 struct IndirectEntry {

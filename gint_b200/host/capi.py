@@ -92,7 +92,7 @@ SIGNATURES = {
     "gint_execute": (c_int, [c_void_p, c_uint64, POINTER(c_uint64), c_int, c_uint32, c_void_p]),
     "gint_execute_range": (c_int, [c_void_p, c_uint64, POINTER(c_uint64), c_int, c_uint32, c_uint32, c_void_p]),
     "gint_execute_plan": (c_int, [c_void_p, POINTER(PlanStepC), c_int, c_void_p]),
-    "gint_execute_gathered": (c_int, [c_void_p, c_uint64, POINTER(c_uint64), c_int, c_uint32, c_uint32, c_void_p, c_uint64, c_void_p]),
+    "gint_execute_gathered": (c_int, [c_void_p, c_uint64, POINTER(c_uint64), c_int, c_uint32, c_uint32, c_void_p, c_uint32, c_uint64, c_void_p]),
     "gint_execute_batch": (c_int, [c_void_p, POINTER(c_int32), c_int, c_int, POINTER(HTensorInfo), c_int, POINTER(c_uint64), c_int, c_uint64, POINTER(c_int32), c_void_p]),
     "gint_execute_checked": (c_int, [c_void_p, c_uint64, POINTER(c_uint64), POINTER(c_uint64), POINTER(c_uint64), c_int, c_uint32, c_void_p]),
     "gint_device_status_read": (c_int, [c_void_p, POINTER(DeviceStatusC), c_int]),

@@ -277,14 +277,18 @@ class B200Executor(BaseExecutor):
         intermediate copy (``gint_execute_gathered``)."""
         ctx, line = self._cacheline(program, args, extra_kwargs)
         ptrs = line.ptrs
-        mask, extent = 0, 0
+        mask, extent, rows = 0, 0, 0
         for i, a in enumerate(line.indices):
             ptrs[i] = args[a].base_ptr
             if a in gathered:
                 mask |= 1 << i
                 t = args[a]
                 extent = max(extent, (sum((s - 1) * abs(st) for s, st in zip(t.shape, t.strides) if s > 0) + 1) * t.elm_size)
-        rc = self._lib.gint_execute_gathered(ctx, line.handle, ptrs, line.n, grid_dim, mask, ctypes.c_void_p(row_index.data_ptr()), extent, cuda_stream)
+                if rows and rows != t.shape[0]:
+                    raise ValueError("gathered tables of one launch must have the same number of rows")
+                rows = t.shape[0]
+        rc = self._lib.gint_execute_gathered(ctx, line.handle, ptrs, line.n, grid_dim, mask, ctypes.c_void_p(row_index.data_ptr()), rows, extent,
+                                             cuda_stream)
         if rc != 0:
             self._check(ctx, rc, "gint_execute_gathered")
         self.launches += 1

@@ -187,11 +187,14 @@ int gint_device_status_read(gint_ctx *ctx, gint_device_status *out, int clear);
  * row_index[b] (int64). Logical program b thus works on row row_index[b] of the tensor at base_ptrs[slot]: `table[index]` is
  * read (or written) in place, without the separate gather kernel and the intermediate copy that the reference needs for the
  * same graph (its conductor leaves aten.index.Tensor to torch eager, gint/conductor/op_registry.py:1058-1132; the interpreter's
- * own gather opcode, 66, picks single elements). gathered_extent_bytes = bytes of the table reachable through the index, from
- * its base pointer (used by the launch-time overlap check in place of the descriptor's extent). Offsets are 32-bit element
- * counts like every other descriptor term. No counterpart in the reference. Same launch properties as gint_execute. */
+ * own gather opcode, 66, picks single elements). table_rows = rows of the table: a negative index counts from the end, as in
+ * torch; an index that is still out of range (an error in torch) is clamped to the nearest row, so no access leaves the
+ * table. gathered_extent_bytes = bytes of the table from its base pointer (used by the launch-time overlap check in place
+ * of the descriptor's extent). Offsets are 32-bit element counts like every other descriptor term. No counterpart in the
+ * reference. Same launch properties as gint_execute. */
 int gint_execute_gathered(gint_ctx *ctx, uint64_t handle, const uint64_t *base_ptrs, int n_tensors, uint32_t grid_dim,
-                          uint32_t gather_mask, const int64_t *row_index, uint64_t gathered_extent_bytes, void *cuda_stream);
+                          uint32_t gather_mask, const int64_t *row_index, uint32_t table_rows, uint64_t gathered_extent_bytes,
+                          void *cuda_stream);
 
 /* One step of a plan: a program, the device addresses of its tensors and its logical grid. */
 typedef struct gint_plan_step {
