@@ -186,7 +186,7 @@ def cpu_reference(name: str, budget_s: float, steps: int = 1, warmup: int = 1):
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
     full_leading, inner = FULL_SIZES[name]
-    sample = {"add": full_leading, "rmsnorm": 2048, "bmm4x4": 524288, "inv4x4": 524288, "graph": 8192}[name]
+    sample = {"add": full_leading, "rmsnorm": 2048, "bmm4x4": 524288, "inv4x4": 524288, "graph": 8192, "graph_gathered": 8192}[name]
     wl = make_workload(name, sample, inner, device="cpu")
     fn = EAGER[name]
     for _ in range(max(1, warmup)):
@@ -262,6 +262,9 @@ def host_dispatch_us(wls, ex, stream: int, reps: int = 200) -> float:
     return dt * 1e6 / n_launch
 
 
+LEAN = False
+
+
 def run_program_bench(name: str, world: int, rank: int, steps: int, warmup: int, peak_gbs: float, impl: str = "b200"):
     """Device-resident timing of one named program at its benchmark size (sharded `world` ways). impl "reference_kernel" runs
     the same buffers through the reference's own executor and sm_100 kernels (baseline/_ref)."""
@@ -316,7 +319,7 @@ def run_program_bench(name: str, world: int, rank: int, steps: int, warmup: int,
                 "frac_of_measured_peak": total_bytes / (per_step_ms * 1e-3) / 1e9 / (peak_gbs * world)}, wls
     info = ex.launch_info(st.program, [wl.tensors[r] for r in st.roles], st.grid_dim)
     split = {}
-    if wl.pre is None and world == 1 and plans[0] is not None:
+    if wl.pre is None and world == 1 and plans[0] is not None and not LEAN:
         # host and device separated: the event-timed figure above includes whatever the host fails to hide
         try:
             split = {"device_us_per_launch": graph_replay_us(wls, ex, max(10, steps)),
@@ -413,11 +416,14 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default="rmsnorm", choices=["add", "rmsnorm", "bmm4x4", "inv4x4", "graph"])
+    ap.add_argument("--workload", default="rmsnorm", choices=["add", "rmsnorm", "bmm4x4", "inv4x4", "graph", "graph_gathered"])
     ap.add_argument("--programs", default="all", choices=["all", "none"], help="also time the other named programs")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--leading", type=int, default=0, help="override the leading dimension (a recorded size; small profiler captures)")
+    ap.add_argument("--lean", action="store_true", help="device-timed leg only: no end-to-end, reference-kernel, host/device split or CPU legs (profiler captures)")
     opts = ap.parse_args()
+    global LEAN
+    LEAN = opts.lean
     warmup = max(opts.warmup, 3)
     peak, peak_kind = measured_peak()
     metric = "achieved HBM GB/s per bytecode program (algorithmic bytes / device time)"
@@ -428,7 +434,8 @@ def main():
     leading, inner = FULL_SIZES[name]
     config = {"workload": {"add": "configs[0] a+b fp32 [1048576]", "rmsnorm": "configs[1] RMSNorm x fp32 [16384,4096], conductor-lowered bytecode (363 insns)",
                            "bmm4x4": "configs[2] batched 4x4 matmul [4194304,4,4]", "inv4x4": "configs[3] batched 4x4 inverse [4194304,4,4]",
-                           "graph": "configs[4] conductor graph x [65536,1024]"}[name],
+                           "graph": "configs[4] conductor graph x [65536,1024]",
+                           "graph_gathered": "configs[4] conductor graph x [65536,1024], gather folded into the fused program"}[name],
               "leading": leading, "inner": inner, "sharding": f"{opts.gpus} rank(s), each running its own {leading}-unit shard of a {opts.gpus * leading}-unit batch; no collective"}
 
     if opts.impl == "reference":
@@ -460,11 +467,14 @@ def main():
     clocks = sampler.stop() if sampler else None
     del wls
     torch.cuda.empty_cache()
-    e2e = run_e2e(name, world, rank, max(3, min(opts.steps, 10)), warmup)
-    torch.cuda.empty_cache()
-    e2e["unoverlapped"] = {k: v for k, v in run_e2e(name, world, rank, max(3, min(opts.steps, 10)), warmup, overlapped=False).items()
-                           if k in ("value", "ms_per_step", "api")}
-    torch.cuda.empty_cache()
+    if opts.lean:
+        e2e = None
+    else:
+        e2e = run_e2e(name, world, rank, max(3, min(opts.steps, 10)), warmup)
+        torch.cuda.empty_cache()
+        e2e["unoverlapped"] = {k: v for k, v in run_e2e(name, world, rank, max(3, min(opts.steps, 10)), warmup, overlapped=False).items()
+                               if k in ("value", "ms_per_step", "api")}
+        torch.cuda.empty_cache()
 
     programs = {}
     if opts.programs == "all":
@@ -480,7 +490,7 @@ def main():
     # the reference's own kernels (its sm_100 build of geval_s7 / geval_l12, through its unmodified executor), same buffers and
     # timing: what this library replaces, on this box
     ref_kernel_note = None
-    if world == 1:
+    if world == 1 and not opts.lean:
         try:
             from baseline import ref_harness
             if not ref_harness.available():
@@ -518,7 +528,7 @@ def main():
             line["strong_scaling"] = strong
         if numa:
             line["host_placement"] = numa
-        if not opts.no_cpu:
+        if not opts.no_cpu and not opts.lean:
             gbs, desc, cores, ms, wl_cpu = cpu_reference(name, budget_s=10.0)
             line["cpu_baseline"] = {"value": gbs, "unit": "GB/s", "cores": cores, "kind": "reference", "sample": desc}
             try:

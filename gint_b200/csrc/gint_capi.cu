@@ -1123,7 +1123,12 @@ int gint_program_create(gint_ctx *ctx, const int32_t *code, int n_words, const g
             p->reread_bytes = (uint32_t)again.size() * 512u;
         }
         const int n_insns = (int)prog.size(), n_direct = n_loads - (usable ? ei.n_early + n_staged_loads : 0);
-        p->prefer_narrow = 5 * n_mem >= 2 * n_insns || 5 * n_direct >= n_insns;
+        /* One tile per warp for programs bound by memory instructions (2 of 5 instructions access memory), and for programs
+         * with many loads that are neither issued early nor staged WHEN the wider kernel costs occupancy (pools of 7 and 12:
+         * 96 and 128 registers at two tiles against 64 and 95 at one). With the 4-slot pool two tiles per warp cost one block
+         * per SM (72 against 64 registers) and double the loads each warp keeps in flight: measured on the bf16 RMSNorm of
+         * the reference's tests (2DT tiles, no early issue), 180 us at two tiles per warp against 221 us at one. */
+        p->prefer_narrow = 5 * n_mem >= 2 * n_insns || (p->st.pool_size >= 7 && 5 * n_direct >= n_insns);
     }
     p->early_slots = (uint32_t)early.size();
     for (int i = 0; i < gint::kInlineCodeSlots; i++) {
