@@ -119,34 +119,42 @@ int normalise(const int32_t *code, int n_words, int n_tensors, std::vector<Insn>
 }
 
 struct FusedDef { int num, len; int ops[GINT_MAX_FUSED_LEN]; };
-const FusedDef kFused[GINT_N_FUSED] = {
+const FusedDef kFused[GINT_N_FUSED + GINT_N_RF_FUSED] = {   // the ordinary fused handlers, then the register-operand forms (RF streams only)
 #define GINT_X_FDEF(num, len, ...) {num, len, {__VA_ARGS__}},
     GINT_FUSED_LIST(GINT_X_FDEF)
+    GINT_RF_FUSED_LIST(GINT_X_FDEF)
 #undef GINT_X_FDEF
 };
+const FusedDef &fused_def(int op)
+{
+    return kFused[op >= GINT_RF_FUSED_FIRST ? GINT_N_FUSED + (op - GINT_RF_FUSED_FIRST) : op - GINT_FUSED_FIRST];
+}
 constexpr int OP_CARRIER = -1;        // an instruction absorbed into the fused handler before it: only its operand is used
 constexpr int OP_CARRIER_UNUSED = -2; // the same, for a member that reads no operand: it gets no stream entry
 
 int net_effect(int op)
 {
     if (op == OP_CARRIER || op == OP_CARRIER_UNUSED) return 0;
-    if (op >= GINT_FUSED_FIRST) {
+    if (GINT_IS_FUSED(op)) {
         int net = 0;
-        const FusedDef &f = kFused[op - GINT_FUSED_FIRST];
+        const FusedDef &f = fused_def(op);
         for (int j = 0; j < f.len; j++) net += net_effect(f.ops[j]);
         return net;
     }
+    if (op == OP_RLoad) return 1;
+    if (op == OP_RStore) return -1;
     return kEffects[op].net;
 }
 
 /* Replace known instruction sequences by fused handlers (gint_fused.h): greedy, longest match first. The absorbed
  * instructions stay in the stream as operand carriers. */
-void fuse_sequences(std::vector<Insn> *prog)
+void fuse_sequences(std::vector<Insn> *prog, bool rf = false)
 {
     std::vector<Insn> &p = *prog;
+    const int n_defs = rf ? GINT_N_FUSED + GINT_N_RF_FUSED : GINT_N_FUSED;   // the register-operand forms: RF streams only
     for (size_t i = 0; i < p.size();) {
         int best = -1;
-        for (int k = 0; k < GINT_N_FUSED; k++) {
+        for (int k = 0; k < n_defs; k++) {
             const FusedDef &f = kFused[k];
             if (i + (size_t)f.len > p.size() || (best >= 0 && f.len <= kFused[best].len)) continue;
             bool match = true;
@@ -467,6 +475,59 @@ void lower_lane_moves(std::vector<Insn> *prog, int pool_size)
 }
 
 /* Conservative byte extent a program can touch from a tensor's base pointer; 0 = unknown (negative strides). */
+/*
+ * Virtual registers in shared memory ("RF" streams and kernels). In the reference, and in this library's ordinary kernels, the
+ * operand stack and the eight virtual registers share one pool (register n = pool[P-1-n], gint/kernel/interpreter/state.py:
+ * 12-18, 38-41), and a program with a deep stack AND many registers needs the 12-slot pool: 96 pool registers at two tiles per
+ * warp, 16 resident warps per SM, handlers at the edge of the register budget. Such a program can run with a pool that holds
+ * only its stack if its registers live elsewhere -- in a per-warp block of shared memory -- PROVIDED the overlap of stack
+ * slots and registers in the shared pool is not observable: rf_equivalent runs the straight-line program on value numbers in
+ * both models (one pool of P slots with the overlap; stack and registers apart) and demands that every instruction reads the
+ * same value numbers in both. It also refuses a program that reads a register before writing it (the pool starts as zeros;
+ * the shared-memory registers start as whatever the previous logical program left).
+ */
+bool rf_equivalent(const std::vector<Insn> &prog, int P)
+{
+    int pool[12] = {}, stack[GINT_MAX_STACK + 1] = {}, regs[8] = {};
+    int next_id = 1, depth = 0;
+    if (P > 12) return false;
+    for (const Insn &in : prog) {
+        const int op = in.op;
+        if (op == OP_Halt) break;
+        if (op < 0 || op >= GINT_N_OPCODES) return false;
+        if (op >= OP_FLoadReg0 && op <= OP_FLoadReg7) {
+            const int n = op - OP_FLoadReg0;
+            if (P - 1 - n < 0 || regs[n] == 0 || pool[P - 1 - n] != regs[n] || depth >= P || depth >= GINT_MAX_STACK) return false;
+            pool[depth] = stack[depth] = next_id++;
+            depth++;
+            continue;
+        }
+        if (op >= OP_FStoreReg0 && op <= OP_FStoreReg7) {
+            const int n = op - OP_FStoreReg0;
+            if (P - 1 - n < 0 || depth < 1 || pool[depth - 1] != stack[depth - 1]) return false;
+            pool[P - 1 - n] = regs[n] = next_id++;
+            depth--;
+            continue;
+        }
+        const int md = kEffects[op].min_depth, post = depth + kEffects[op].net, top = post > depth ? post : depth;
+        if (depth < md || top > P || top > GINT_MAX_STACK) return false;
+        for (int j = depth - md; j < depth; j++)
+            if (pool[j] != stack[j]) return false;
+        for (int j = depth - md; j < top; j++) pool[j] = stack[j] = next_id++;
+        depth = post;
+    }
+    return true;
+}
+
+/* FLoadRegN / FStoreRegN -> RLoad / RStore with the register number in the operand (512 bytes per register and tile). */
+void rf_rewrite(std::vector<Insn> *prog)
+{
+    for (Insn &in : *prog) {
+        if (in.op >= OP_FLoadReg0 && in.op <= OP_FLoadReg7) in = Insn{OP_RLoad, (uint32_t)(in.op - OP_FLoadReg0) * 512u};
+        else if (in.op >= OP_FStoreReg0 && in.op <= OP_FStoreReg7) in = Insn{OP_RStore, (uint32_t)(in.op - OP_FStoreReg0) * 512u};
+    }
+}
+
 uint64_t tensor_extent_bytes(const gint_tensor_info &ti, int t)
 {
     int64_t elems = 1;
@@ -487,6 +548,7 @@ struct Variant {
     int regs;
     bool ok;
     int resident_warps;   // warps of this kernel the whole device holds when a block needs only its minimum of shared memory
+    bool rf = false;      // virtual registers in shared memory (pool = operand stack only)
 };
 
 /* The embedded cubins are loaded once per process (a cudaLibrary_t is not tied to a device or context). */
@@ -498,16 +560,20 @@ struct KernelImage {
     cudaLibrary_t lib;
     cudaKernel_t kernel;
     bool loaded;
+    bool rf;
 };
 
 KernelImage g_images[] = {
-#define GINT_X_IMG(P, K) {gint_cubin_direct_##P##_##K, gint_cubin_direct_##P##_##K##_end, "gint_geval_direct_" #P "_" #K, P, K, nullptr, nullptr, false},
+#define GINT_X_IMG(P, K) {gint_cubin_direct_##P##_##K, gint_cubin_direct_##P##_##K##_end, "gint_geval_direct_" #P "_" #K, P, K, nullptr, nullptr, false, false},
     GINT_DIRECT_VARIANTS(GINT_X_IMG)
 #undef GINT_X_IMG
-#define GINT_X_IMG(P) {gint_cubin_indirect_##P, gint_cubin_indirect_##P##_end, "gint_geval_indirect_" #P, P, 0, nullptr, nullptr, false},
+#define GINT_X_IMG(P, K) {gint_cubin_rf_##P##_##K, gint_cubin_rf_##P##_##K##_end, "gint_geval_rf_" #P "_" #K, P, K, nullptr, nullptr, false, true},
+    GINT_RF_VARIANTS(GINT_X_IMG)
+#undef GINT_X_IMG
+#define GINT_X_IMG(P) {gint_cubin_indirect_##P, gint_cubin_indirect_##P##_end, "gint_geval_indirect_" #P, P, 0, nullptr, nullptr, false, false},
     GINT_INDIRECT_VARIANTS(GINT_X_IMG)
 #undef GINT_X_IMG
-#define GINT_X_IMG(P) {gint_cubin_checked_##P, gint_cubin_checked_##P##_end, "gint_geval_checked_" #P, P, -1, nullptr, nullptr, false},
+#define GINT_X_IMG(P) {gint_cubin_checked_##P, gint_cubin_checked_##P##_end, "gint_geval_checked_" #P, P, -1, nullptr, nullptr, false, false},
     GINT_CHECKED_VARIANTS(GINT_X_IMG)
 #undef GINT_X_IMG
 };
@@ -568,7 +634,15 @@ struct Program {
     /* host copies of the two streams when they are short enough to travel inside the kernel parameters */
     uint2 code_inline[gint::kInlineCodeSlots];
     uint2 early_inline[gint::kInlineCodeSlots];
-    PlanMemo memo[2] = {};      // last launch plan of the plain stream [0] and of the early-issue stream [1]
+    /* the stream for the kernels with virtual registers in shared memory (nullptr: none); made from the early-issue stream if
+     * the program has a usable one (rf_from_early: the same launch conditions apply), else from the plain stream */
+    uint2 *rf_dev = nullptr;
+    uint32_t rf_slots = 0;
+    int rf_pool = 0;            // pool size of the kernel that runs it (the operand stack alone)
+    uint32_t rf_bytes = 0;      // shared memory per tile for the registers: 512 bytes per register
+    bool rf_from_early = false;
+    uint2 rf_inline[gint::kInlineCodeSlots];
+    PlanMemo memo[3] = {};      // last launch plan of the plain stream [0], of the early-issue stream [1], of the RF stream [2]
     std::mutex memo_mu;
 };
 
@@ -625,6 +699,8 @@ struct gint_ctx {
     int opt_early_issue = 1;
     int opt_fuse = 1;           // applies to programs created afterwards
     int opt_lower = 1;          // DupBroadcastW -> Bcast_k (lower_lane_moves); applies to programs created afterwards
+    int opt_rf = 1;             // launches use a program's RF stream (virtual registers in shared memory) when it has one
+    int opt_rf_create = 1;      // programs created from now on get an RF stream when they qualify
     /* scratch for indirect launches */
     void *ind_dev = nullptr;
     void *ind_host = nullptr;
@@ -668,10 +744,10 @@ Program *lookup(gint_ctx *ctx, uint64_t handle)
     return (p && p->live) ? p : nullptr;
 }
 
-Variant *find_variant(gint_ctx *ctx, int P, int K)
+Variant *find_variant(gint_ctx *ctx, int P, int K, bool rf = false)
 {
     for (auto &v : ctx->direct)
-        if (v.P == P && v.K == K && v.ok) return &v;
+        if (v.P == P && v.K == K && v.rf == rf && v.ok) return &v;
     return nullptr;
 }
 
@@ -682,16 +758,22 @@ struct StreamView {
     uint32_t n_slots;
     uint32_t ring_bytes;       // shared memory per tile for the ring of early-issued loads
     uint32_t row_area_bytes;   // shared memory per tile for staged row blocks
+    uint32_t rf_bytes;         // shared memory per tile for virtual registers (RF stream)
+    int P;                     // pool size of the kernels that run this stream
     bool early;
+    bool rf;
 };
 
-StreamView stream_view(const Program *p, bool early)
+StreamView stream_view(const Program *p, bool early, bool rf = false)
 {
     StreamView v;
     v.early = early;
-    v.n_slots = early ? p->early_slots : p->n_slots;
+    v.rf = rf;
+    v.n_slots = rf ? p->rf_slots : early ? p->early_slots : p->n_slots;
     v.ring_bytes = early && p->n_early > 0 ? (uint32_t)p->ring_slots * 512u : 0u;
     v.row_area_bytes = early ? p->row_area_bytes : 0u;
+    v.rf_bytes = rf ? p->rf_bytes : 0u;
+    v.P = rf ? p->rf_pool : p->st.pool_size;
     return v;
 }
 
@@ -700,7 +782,7 @@ uint32_t direct_smem(const StreamView &v, int K, uint32_t *code_smem)
     const uint32_t cs = (v.n_slots * 8u + 127u) & ~127u;
     *code_smem = cs;
     return cs + gint::kTensorInfoSmemBytes + (uint32_t)(gint::kWarpsPerBlock * K) * (uint32_t)sizeof(gint::TileInfo) +
-           (uint32_t)(gint::kWarpsPerBlock * K) * (v.ring_bytes + v.row_area_bytes);
+           (uint32_t)(gint::kWarpsPerBlock * K) * (v.ring_bytes + v.row_area_bytes + v.rf_bytes);
 }
 
 /* Blocks needed to give every group of K logical programs a warp. */
@@ -712,7 +794,7 @@ uint64_t blocks_for(uint32_t count, int K)
 
 int plan_direct(gint_ctx *ctx, const Program *p, const StreamView &sv, uint32_t count, Geometry *g)
 {
-    const int P = p->st.pool_size;
+    const int P = sv.P;
     const int ks[3] = {4, 2, 1};
     /* upper bound on K: the option if set; else 2 (measured: 4 tiles per warp lose more to the lower occupancy of the
      * 96-register kernels than they gain from amortised dispatch), and 1 for programs that are bound by memory instructions
@@ -727,19 +809,19 @@ int plan_direct(gint_ctx *ctx, const Program *p, const StreamView &sv, uint32_t 
      * (measured on a+b over 2^20 elements, device time: 7.1 / 6.3 / 5.9 us at 1 / 2 / 4 tiles per warp). */
     bool latency_bound = false;
     if (!ctx->opt_tiles_per_warp && sv.n_slots <= (uint32_t)gint::kInlineCodeSlots) {
-        Variant *v1 = find_variant(ctx, P, 1);
+        Variant *v1 = find_variant(ctx, P, 1, sv.rf);
         if (v1 && v1->resident_warps > 0 && (uint64_t)count <= 2ull * (uint64_t)v1->resident_warps) {
             latency_bound = true;
             k_max = 1;
             for (int K : ks)
-                if (find_variant(ctx, P, K) && blocks_for(count, K) >= 2ull * (uint64_t)ctx->num_sms) { k_max = K; break; }
+                if (find_variant(ctx, P, K, sv.rf) && blocks_for(count, K) >= 2ull * (uint64_t)ctx->num_sms) { k_max = K; break; }
         }
     }
     Geometry best{};
     bool have = false;
     for (int K : ks) {
         if (K > k_max) continue;
-        Variant *v = find_variant(ctx, P, K);
+        Variant *v = find_variant(ctx, P, K, sv.rf);
         if (!v) continue;
         Geometry c{};
         c.v = v;
@@ -805,24 +887,33 @@ int launch_direct(gint_ctx *ctx, uint64_t handle, const uint64_t *base_ptrs, int
     }
     for (int t = 0; early && t < n_tensors; t++)
         if (((p->fast_slots >> t) & 1u) && (base_ptrs[t] & 15u) != 0) early = false;   // fast accesses need aligned bases
-    const StreamView sv = stream_view(p, early);   // geometry depends on the stream
+    /* the stream with the virtual registers in shared memory, when the stream it was made from is the one this launch may use */
+    bool rf = ctx->opt_rf && p->rf_dev != nullptr && p->rf_from_early == early;
+    StreamView sv = stream_view(p, early, rf);   // geometry depends on the stream
     Geometry g;
     {
         /* each program remembers its last plan per stream: a launch that repeats the previous one's size skips the occupancy
          * queries (several microseconds), also when the caller alternates between programs */
-        PlanMemo &m = p->memo[early ? 1 : 0];
         std::lock_guard<std::mutex> lk(p->memo_mu);
-        if (m.valid && m.count == count && m.opt_k == ctx->opt_tiles_per_warp && m.opt_blocks == ctx->opt_max_blocks) {
-            g = m.g;
+        PlanMemo *m = &p->memo[rf ? 2 : early ? 1 : 0];
+        if (m->valid && m->count == count && m->opt_k == ctx->opt_tiles_per_warp && m->opt_blocks == ctx->opt_max_blocks) {
+            g = m->g;
         } else {
             int rc = plan_direct(ctx, p, sv, count, &g);
+            if (rc != GINT_OK && rf) {   // no RF kernel for this tiles-per-warp choice or this much shared memory: the ordinary kernels
+                rf = false;
+                sv = stream_view(p, early, false);
+                rc = plan_direct(ctx, p, sv, count, &g);   // (remembered under the RF stream's memo: the next launch asks there again)
+            }
             if (rc != GINT_OK) return rc;
-            m = PlanMemo{true, count, ctx->opt_tiles_per_warp, ctx->opt_max_blocks, g};
+            *m = PlanMemo{true, count, ctx->opt_tiles_per_warp, ctx->opt_max_blocks, g};
         }
+        rf = g.v->rf;
+        if (!rf && sv.rf) sv = stream_view(p, early, false);
     }
     LaunchArgs a;
     const bool inline_code = sv.n_slots <= (uint32_t)gint::kInlineCodeSlots;
-    a.code = inline_code ? nullptr : (early ? p->early_dev : p->code_dev);
+    a.code = inline_code ? nullptr : (rf ? p->rf_dev : early ? p->early_dev : p->code_dev);
     a.n_slots = sv.n_slots;
     a.n_tensors = (uint32_t)p->n_tensors;
     a.first = first;
@@ -832,7 +923,7 @@ int launch_direct(gint_ctx *ctx, uint64_t handle, const uint64_t *base_ptrs, int
     a.zero = 0;
     a.row_area_bytes = sv.row_area_bytes;
     a.ring_bytes = sv.ring_bytes;
-    a.reserved = 0;
+    a.rf_bytes = sv.rf_bytes;
     a.gather_mask = gather ? gather->mask : 0u;
     a.gather_index = gather ? gather->index : nullptr;
     a.gather_rows = gather ? gather->rows : 0u;
@@ -841,7 +932,7 @@ int launch_direct(gint_ctx *ctx, uint64_t handle, const uint64_t *base_ptrs, int
         for (int t = 0; t < GINT_MAX_TENSORS; t++) a.fp[t] = p->fp[t];
     a.ti = p->ti;
     for (int i = 0; i < n_tensors; i++) a.ti.base_ptr[i] = (int64_t)base_ptrs[i];
-    if (inline_code) memcpy(a.inline_code, early ? p->early_inline : p->code_inline, sizeof(a.inline_code));
+    if (inline_code) memcpy(a.inline_code, rf ? p->rf_inline : early ? p->early_inline : p->code_inline, sizeof(a.inline_code));
     void *args[1] = {&a};
     cudaError_t e = cudaLaunchKernel(g.v->fn, dim3(g.grid), dim3(gint::kThreadsPerBlock), args, g.smem, (cudaStream_t)stream);
     if (e != cudaSuccess) return fail(ctx, GINT_ERR_CUDA, "cudaLaunchKernel", e);
@@ -975,7 +1066,7 @@ int gint_create(int device, gint_ctx **out)
         if (!im.loaded) continue;
         if (im.K == 0) ctx->indirect.fn = (const void *)im.kernel;
         else if (im.K < 0) ctx->checked.fn = (const void *)im.kernel;
-        else ctx->direct.push_back(Variant{im.P, im.K, (const void *)im.kernel, 0, false, 0});
+        else ctx->direct.push_back(Variant{im.P, im.K, (const void *)im.kernel, 0, false, 0, im.rf});
     }
     int usable = 0;
     for (auto &v : ctx->direct) {
@@ -1018,6 +1109,7 @@ void gint_destroy(gint_ctx *ctx)
             if (p) {
                 if (p->code_dev) cudaFree(p->code_dev);
                 if (p->early_dev) cudaFree(p->early_dev);
+                if (p->rf_dev) cudaFree(p->rf_dev);
                 delete p;
             }
         }
@@ -1060,10 +1152,23 @@ int gint_program_create(gint_ctx *ctx, const int32_t *code, int n_words, const g
     if (ti) p->ti = *ti;
     for (int t = 0; t < GINT_MAX_TENSORS; t++) p->ti.base_ptr[t] = 0;
     compute_footprints(code, p->st.num_instructions, p->ti, n_tensors, p);
-    std::vector<uint2> early;
+    std::vector<uint2> early, rfs;
     {
         std::vector<Insn> prog;
         normalise(code, n_words, n_tensors, &prog);
+        /* virtual registers in shared memory: for programs that need the 12-slot pool although their stack fits 7 slots */
+        const int rf_pool = 7;
+        const bool rf_ok = ctx->opt_rf_create && p->st.pool_size == 12 && p->st.max_stack <= rf_pool && p->st.max_reg_idx >= 0 &&
+                           (find_variant(ctx, rf_pool, 1, true) || find_variant(ctx, rf_pool, 2, true)) && rf_equivalent(prog, p->st.pool_size);
+        auto make_rf = [&](std::vector<Insn> from, bool from_early) {
+            rf_rewrite(&from);
+            if (ctx->opt_lower) lower_lane_moves(&from, rf_pool);
+            if (ctx->opt_fuse) fuse_sequences(&from, true);
+            emit_stream(from, &rfs);
+            p->rf_pool = rf_pool;
+            p->rf_bytes = (uint32_t)(p->st.max_reg_idx + 1) * 512u;
+            p->rf_from_early = from_early;
+        };
         EarlyIssue ei;
         p->ring_slots = choose_ring_slots(prog);
         early_issue_transform(prog, p->ring_slots, &ei);
@@ -1096,6 +1201,7 @@ int gint_program_create(gint_ctx *ctx, const int32_t *code, int n_words, const g
         if (usable) {
             p->fast_slots = apply_fast_accesses(&ei.prog, p->ti, n_tensors) | apply_fast_rows(&ei.prog, p->ti, n_tensors) | staged;
             p->row_area_bytes = row_area;
+            if (rf_ok) make_rf(ei.prog, true);
             if (ctx->opt_lower) lower_lane_moves(&ei.prog, p->st.pool_size);
             if (ctx->opt_fuse) fuse_sequences(&ei.prog);
             emit_stream(ei.prog, &early);
@@ -1103,6 +1209,7 @@ int gint_program_create(gint_ctx *ctx, const int32_t *code, int n_words, const g
         } else {
             for (int t = 0; t < n_tensors; t++) p->alias_slots[t] = 0;
             n_staged_loads = 0;
+            if (rf_ok) make_rf(prog, false);
         }
         int n_mem = 0, n_loads = 0;
         for (const Insn &in : prog) {
@@ -1131,9 +1238,11 @@ int gint_program_create(gint_ctx *ctx, const int32_t *code, int n_words, const g
         p->prefer_narrow = 5 * n_mem >= 2 * n_insns || (p->st.pool_size >= 7 && 5 * n_direct >= n_insns);
     }
     p->early_slots = (uint32_t)early.size();
+    p->rf_slots = (uint32_t)rfs.size();
     for (int i = 0; i < gint::kInlineCodeSlots; i++) {
         p->code_inline[i] = (size_t)i < pre.size() ? pre[(size_t)i] : make_uint2(0u, OP_Halt);
         p->early_inline[i] = (size_t)i < early.size() ? early[(size_t)i] : make_uint2(0u, OP_Halt);
+        p->rf_inline[i] = (size_t)i < rfs.size() ? rfs[(size_t)i] : make_uint2(0u, OP_Halt);
     }
     {
         DeviceGuard guard(ctx->device);
@@ -1149,6 +1258,17 @@ int gint_program_create(gint_ctx *ctx, const int32_t *code, int n_words, const g
                 cudaFree(p->code_dev);
                 delete p;
                 return fail(ctx, GINT_ERR_OUT_OF_MEMORY, "cudaMalloc/cudaMemcpy(early-issue program)", e);
+            }
+        }
+        if (!rfs.empty()) {
+            e = cudaMalloc(&p->rf_dev, rfs.size() * sizeof(uint2));
+            if (e == cudaSuccess) e = cudaMemcpy(p->rf_dev, rfs.data(), rfs.size() * sizeof(uint2), cudaMemcpyHostToDevice);
+            if (e != cudaSuccess) {
+                if (p->rf_dev) cudaFree(p->rf_dev);
+                if (p->early_dev) cudaFree(p->early_dev);
+                cudaFree(p->code_dev);
+                delete p;
+                return fail(ctx, GINT_ERR_OUT_OF_MEMORY, "cudaMalloc/cudaMemcpy(register-file program)", e);
             }
         }
     }
@@ -1173,6 +1293,7 @@ int gint_program_destroy(gint_ctx *ctx, uint64_t handle)
     /* the program may still be running on some stream: cudaFree waits for the device */
     if (p->code_dev) cudaFree(p->code_dev);
     if (p->early_dev) cudaFree(p->early_dev);
+    if (p->rf_dev) cudaFree(p->rf_dev);
     delete p;
     return GINT_OK;
 }
@@ -1184,8 +1305,14 @@ int gint_program_launch_info(gint_ctx *ctx, uint64_t handle, uint32_t grid_dim, 
     if (!p) return fail(ctx, GINT_ERR_BAD_HANDLE, "unknown program handle");
     DeviceGuard guard(ctx->device);
     Geometry g;
-    const StreamView sv = stream_view(p, ctx->opt_early_issue && p->early_dev != nullptr);
+    const bool early = ctx->opt_early_issue && p->early_dev != nullptr;
+    const bool rf = ctx->opt_rf && p->rf_dev != nullptr && p->rf_from_early == early;
+    StreamView sv = stream_view(p, early, rf);
     int rc = plan_direct(ctx, p, sv, grid_dim ? grid_dim : 1, &g);
+    if (rc != GINT_OK && rf) {
+        sv = stream_view(p, early, false);
+        rc = plan_direct(ctx, p, sv, grid_dim ? grid_dim : 1, &g);
+    }
     if (rc != GINT_OK) return rc;
     memset(out, 0, sizeof(*out));
     out->pool_size = g.v->P;
@@ -1197,6 +1324,7 @@ int gint_program_launch_info(gint_ctx *ctx, uint64_t handle, uint32_t grid_dim, 
     out->blocks_per_sm = g.blocks_per_sm;
     out->num_sms = ctx->num_sms;
     out->early_loads = p->n_early;
+    out->registers_in_smem = g.v->rf ? p->st.max_reg_idx + 1 : 0;
     return GINT_OK;
 }
 
@@ -1598,7 +1726,7 @@ int gint_debug_transform(const int32_t *code, int n_words, const gint_tensor_inf
     std::vector<Insn> prog;
     int rc = normalise(code, n_words, n_tensors, &prog);
     if (rc != GINT_OK) return rc;
-    if (early_issue) {
+    if (early_issue & 1) {
         gint_bytecode_stats st;
         analyze(code, n_words, &st);
         EarlyIssue ei;
@@ -1619,7 +1747,18 @@ int gint_debug_transform(const int32_t *code, int n_words, const gint_tensor_inf
             }
         }
     }
-    if (fuse) {
+    if (early_issue & 2) {   // the stream for the kernels with virtual registers in shared memory, if the program qualifies
+        gint_bytecode_stats st0;
+        analyze(code, n_words, &st0);
+        std::vector<Insn> plain;
+        normalise(code, n_words, n_tensors, &plain);
+        if (!(st0.pool_size == 12 && st0.max_stack <= 7 && st0.max_reg_idx >= 0 && rf_equivalent(plain, st0.pool_size))) return 0;
+        rf_rewrite(&prog);
+        if (fuse) {
+            lower_lane_moves(&prog, 7);
+            fuse_sequences(&prog, true);
+        }
+    } else if (fuse) {
         gint_bytecode_stats st0;
         analyze(code, n_words, &st0);
         lower_lane_moves(&prog, st0.pool_size);
@@ -1635,14 +1774,14 @@ int gint_debug_transform(const int32_t *code, int n_words, const gint_tensor_inf
 
 int gint_debug_fused_table(int32_t *out, int max_entries)
 {
-    if (!out || max_entries < GINT_N_FUSED) return GINT_ERR_INVALID_ARGUMENT;
-    for (int k = 0; k < GINT_N_FUSED; k++) {
+    if (!out || max_entries < GINT_N_FUSED + GINT_N_RF_FUSED) return GINT_ERR_INVALID_ARGUMENT;
+    for (int k = 0; k < GINT_N_FUSED + GINT_N_RF_FUSED; k++) {
         int32_t *row = out + (size_t)k * (2 + GINT_MAX_FUSED_LEN);
         row[0] = kFused[k].num;
         row[1] = kFused[k].len;
         for (int j = 0; j < GINT_MAX_FUSED_LEN; j++) row[2 + j] = j < kFused[k].len ? kFused[k].ops[j] : -1;
     }
-    return GINT_N_FUSED;
+    return GINT_N_FUSED + GINT_N_RF_FUSED;
 }
 
 int gint_set_option(gint_ctx *ctx, const char *name, int value)
@@ -1663,6 +1802,10 @@ int gint_set_option(gint_ctx *ctx, const char *name, int value)
     }
     if (strcmp(name, "early_issue") == 0) {
         ctx->opt_early_issue = value != 0;
+        return GINT_OK;
+    }
+    if (strcmp(name, "register_file") == 0) {   // virtual registers in shared memory: programs created and launches made from now on
+        ctx->opt_rf = ctx->opt_rf_create = value != 0;
         return GINT_OK;
     }
     if (strcmp(name, "prefetch") == 0) {

@@ -583,6 +583,7 @@ template <int OP> struct OpInfo;
     template <> struct OpInfo<num> { static constexpr int min_depth = md; static constexpr int net_effect = net; };
 GINT_OPCODE_LIST(GINT_X_INFO)
 GINT_INTERNAL_OPCODE_LIST(GINT_X_INFO)
+GINT_RF_OPCODE_LIST(GINT_X_INFO)
 #undef GINT_X_INFO
 
 template <int OP, int SP, int P, int K_ = 1> __host__ __device__ constexpr bool op_valid();
@@ -610,8 +611,10 @@ template <int... OPS> struct Seq {
 template <int NUM> struct FusedSeq;
 #define GINT_X_FSEQ(num, len, ...) template <> struct FusedSeq<num> { using type = Seq<__VA_ARGS__>; static_assert(Seq<__VA_ARGS__>::n == len, "length"); };
 GINT_FUSED_LIST(GINT_X_FSEQ)
+GINT_RF_FUSED_LIST(GINT_X_FSEQ)
 #undef GINT_X_FSEQ
-static_assert(GINT_FUSED_FIRST + GINT_N_FUSED == GINT_N_DISPATCH, "gint_fused.h and gint_opcodes.h disagree");
+static_assert(GINT_FUSED_FIRST + GINT_N_FUSED == GINT_N_DISPATCH_PLAIN && GINT_RF_FUSED_FIRST + GINT_N_RF_FUSED == GINT_N_DISPATCH_RF,
+              "gint_fused.h and gint_opcodes.h disagree");
 
 template <typename S> struct SeqInfo;
 template <> struct SeqInfo<Seq<>> {
@@ -635,11 +638,15 @@ template <int OP0, int... REST> struct SeqInfo<Seq<OP0, REST...>> {
         static constexpr int net_effect = SeqInfo<Seq<__VA_ARGS__>>::net;                                  \
     };
 GINT_FUSED_LIST(GINT_X_FINFO)
+GINT_RF_FUSED_LIST(GINT_X_FINFO)
 #undef GINT_X_FINFO
 
 template <int OP, int SP, int P, int K_> __host__ __device__ constexpr bool op_valid()
 {
-    if constexpr (OP >= GINT_FUSED_FIRST) {
+    if constexpr (GINT_IS_FUSED(OP)) {
+#ifndef GINT_RF
+        if (OP >= GINT_RF_FUSED_FIRST) return false;
+#endif
         return SP >= 0 && SeqInfo<typename FusedSeq<OP>::type>::template valid<SP, P, K_>();
     } else {
         constexpr int limit = P < GINT_MAX_STACK ? P : GINT_MAX_STACK;
@@ -651,8 +658,14 @@ template <int OP, int SP, int P, int K_> __host__ __device__ constexpr bool op_v
          * program pays for. The one-tile 12-slot kernels (direct, indirect, checked) keep them: they also run the streams of
          * programs with smaller pools, in which DupBroadcastW has become Bcast_k. */
         if (OP >= OP_Bcast_0 && OP <= OP_Bcast_3 && P * K_ >= 24) return false;
+#ifdef GINT_RF
+        /* virtual registers in shared memory: the pool is the operand stack alone, registers are reached through RLoad / RStore */
+        if (OP >= OP_FLoadReg0 && OP <= OP_FStoreReg7) return false;
+#else
+        if (OP == OP_RLoad || OP == OP_RStore) return false;
         if (OP >= OP_FLoadReg0 && OP <= OP_FLoadReg7 && (P - 1 - (OP - OP_FLoadReg0)) < 0) return false;
         if (OP >= OP_FStoreReg0 && OP <= OP_FStoreReg7 && (P - 1 - (OP - OP_FStoreReg0)) < 0) return false;
+#endif
         return true;
     }
 }
@@ -899,6 +912,15 @@ __device__ __forceinline__ void exec_tile(const uint32_t operand, const Ctx &cx)
     } else if constexpr (OP >= OP_FStoreReg0 && OP <= OP_FStoreReg7) {
         slot_mov<K, P - 1 - (OP - OP_FStoreReg0), T, KI>();
     }
+    /* ---- virtual registers in shared memory (kernels built with GINT_RF): register n of tile k is the 512-byte block
+     * (n * K + k) of the warp's register area, 16 bytes per lane; %grf = address of block 0 plus 16 * lane; operand = 512 n ---- */
+    else if constexpr (OP == OP_RLoad) {
+        asm volatile("{\n\t.reg .b32 ra;\n\tmad.lo.u32 ra, %2, %3, %%grf;\n\tld.shared.v2.b64 {%%gs%0, %%gs%1}, [ra+%4];\n\t}"
+                     ::"n"(LO(SP)), "n"(HI(SP)), "r"(operand), "n"(K), "n"(KI * 512) : "memory");
+    } else if constexpr (OP == OP_RStore) {
+        asm volatile("{\n\t.reg .b32 ra;\n\tmad.lo.u32 ra, %2, %3, %%grf;\n\tst.shared.v2.b64 [ra+%4], {%%gs%0, %%gs%1};\n\t}"
+                     ::"n"(LO(T)), "n"(HI(T)), "r"(operand), "n"(K), "n"(KI * 512) : "memory");
+    }
     /* ---- warp all-reduce (reduction.py:7-30, nvptx.py:89-104): butterfly 16, 8, 4, 2, 1 per width lane ---- */
     else if constexpr (OP >= OP_WarpAllReduceSum && OP <= OP_WarpAllReduceProd) {
         float t[4];
@@ -1100,10 +1122,14 @@ template <int N> __device__ __forceinline__ void pool_clear()
  *   %gbudget     instructions left before the interpreter gives up (only with GINT_GUARD, a debugging aid)
  *   %gring       byte offset of the current slot in the warp's ring of early-issued loads
  *   %gzero       64 bits of zero that reach the kernel as a launch parameter (see fma_barrier)
+ *   %grf         shared-memory address of the warp's virtual registers plus 16 * lane (kernels built with GINT_RF)
  * so no C++ value is live from handler to handler and a handler's basic block can be entered from any other handler.
  */
 template <bool SMEM> __device__ __forceinline__ void state_declare()
 {
+#ifdef GINT_RF
+    asm volatile(".reg .b32 %%grf; // %0" ::"n"(0));
+#endif
     // (the unused "n" operand makes nvcc treat the string as a template, so that %% means %)
     if constexpr (SMEM) asm volatile(".reg .b32 %%gc; .reg .b32 %%ge<2>; .reg .b32 %%gkey; .reg .b32 %%gbudget; .reg .b32 %%gring; .reg .b64 %%gzero; // %0" ::"n"(0));
     else asm volatile(".reg .b64 %%gc; .reg .b32 %%ge<2>; .reg .b32 %%gkey; .reg .b32 %%gbudget; .reg .b32 %%gring; .reg .b64 %%gzero; // %0" ::"n"(0));
@@ -1186,7 +1212,7 @@ __device__ __forceinline__ void interpret(const uint2 *code, uint32_t n_entries,
             else {                                                                                      \
                 constexpr int next_depth = (spv) + OpInfo<num>::net_effect;                             \
                 uint32_t operand, opc;                                                                  \
-                if constexpr ((num) >= GINT_FUSED_FIRST) {                                              \
+                if constexpr (GINT_IS_FUSED(num)) {                                                     \
                     run_fused<num, spv, P, K>(cx, opc);                                                 \
                 } else {                                                                                \
                     state_advance<SMEM_CODE>(operand, opc);                                             \
@@ -1207,6 +1233,10 @@ __device__ __forceinline__ void interpret(const uint2 *code, uint32_t n_entries,
             GINT_INTERNAL_OPCODE_LIST(GINT_X_CASES)
 #define GINT_X_FCASES(num, len, ...) GINT_X_CASES(fused, num, 0, 0)
             GINT_FUSED_LIST(GINT_X_FCASES)
+#ifdef GINT_RF
+            GINT_RF_OPCODE_LIST(GINT_X_CASES)
+            GINT_RF_FUSED_LIST(GINT_X_FCASES)
+#endif
 #undef GINT_X_FCASES
 #undef GINT_X_CASES
 #undef GINT_CASE_SP
@@ -1319,6 +1349,14 @@ __device__ __forceinline__ void geval_direct_body(const LaunchArgs &a)
         cx.rows_stride = a.row_area_bytes;
         cx.ring_mask = (uint32_t)K * a.ring_bytes - 1u;
     }
+#ifdef GINT_RF
+    {   /* after the staged row blocks: the virtual registers, rf_bytes (512 per register) per tile */
+        unsigned char *after = reinterpret_cast<unsigned char *>(tiles_s + kWarpsPerBlock * K);
+        const uint32_t rf = (uint32_t)__cvta_generic_to_shared(after + (size_t)(kWarpsPerBlock * K) * (a.ring_bytes + a.row_area_bytes) +
+                                                               (size_t)(warp * K) * a.rf_bytes + lane * 16);
+        asm volatile("mov.b32 %%grf, %0;" ::"r"(rf));
+    }
+#endif
 
     const uint32_t n_groups = (a.end - a.first + (uint32_t)K - 1u) / (uint32_t)K;
     for (uint32_t g = blockIdx.x * kWarpsPerBlock + warp; g < n_groups; g += gridDim.x * kWarpsPerBlock) {
@@ -1389,6 +1427,12 @@ __device__ __forceinline__ void geval_indirect_body(const IndirectArgs &a)
         gint_geval_checked_##P(const __grid_constant__ gint::LaunchArgs a)                                       \
     {                                                                                                           \
         gint::geval_direct_body<P, 1, false>(a);                                                                \
+    }
+#define GINT_DEFINE_RF_KERNEL(P, K)                                                                             \
+    extern "C" __global__ void __launch_bounds__(gint::kThreadsPerBlock, GINT_MIN_BLOCKS(P, K))                  \
+        gint_geval_rf_##P##_##K(const __grid_constant__ gint::LaunchArgs a)                                      \
+    {                                                                                                           \
+        gint::geval_direct_body<P, K>(a);                                                                       \
     }
 #define GINT_DEFINE_DIRECT_KERNEL(P, K)                                                                         \
     extern "C" __global__ void __launch_bounds__(gint::kThreadsPerBlock, GINT_MIN_BLOCKS(P, K))                  \

@@ -151,19 +151,41 @@
  * (given a 16-byte aligned base pointer, checked at every launch):
  *   LoadGlobal2DWF32Fast / StoreGlobal2DWF32Fast   one 128-bit access per lane, no shape, mask or alignment handling
  */
+/*
+ * Virtual registers kept in shared memory (the kernels built with GINT_RF, see gint_interp.cuh). A program that needs the
+ * 12-slot pool only because of its eight virtual registers runs with a pool that holds just its operand stack; the registers
+ * live in a per-warp block of shared memory and the register number travels in the operand word, so one handler serves all
+ * eight registers and sequences such as "load register, permute, load register, multiply" can be fused whatever registers
+ * they name:
+ *   RLoad    push register (operand / 512)      -- operand = 512 * register number
+ *   RStore   pop into register (operand / 512)
+ * The host introduces them (gint_capi.cu: rf_transform) only where the reference's overlap of stack and registers in one
+ * pool cannot be observed by the program.
+ */
 #define GINT_INTERNAL_OPCODE_LIST(X) \
     X(PfTake, 106, 0, 1) X(PfIssue1D, 107, 0, 0) X(PfTakeIssue1D, 108, 0, 1) X(PfSkip, 109, 0, 0) \
     X(LoadGlobal1DF32Fast, 110, 0, 1) X(StoreGlobal1DF32Fast, 111, 1, -1) X(PfIssue1DFast, 112, 0, 0) X(PfTakeIssue1DFast, 113, 0, 1) \
     X(StageRows, 114, 0, 0) X(LoadStagedRows, 115, 0, 1) \
     X(Bcast_0, 116, 1, 1) X(Bcast_1, 117, 1, 1) X(Bcast_2, 118, 1, 1) X(Bcast_3, 119, 1, 1) \
     X(LoadGlobal2DWF32Fast, 120, 0, 1) X(StoreGlobal2DWF32Fast, 121, 1, -1)
-#define GINT_N_DISPATCH 150   /* opcodes the kernels dispatch on: the 106 of the format, the 16 internal ones above and the
-                                 fused handlers of gint_fused.h */
+/* the register-file kernels' own opcodes: numbered after the fused handlers of the ordinary kernels (gint_fused.h), so that
+ * nothing in the ordinary kernels -- numbering, dispatch keys, generated code -- depends on them */
+#define GINT_RF_OPCODE_LIST(X) X(RLoad, 150, 0, 1) X(RStore, 151, 1, -1)
+/* opcodes a kernel dispatches on: the 106 of the format, the 16 internal ones and the 28 fused handlers of gint_fused.h; in
+ * the register-file kernels also RLoad / RStore and the register-operand fused handlers */
+#define GINT_N_DISPATCH_PLAIN 150
+#define GINT_N_DISPATCH_RF 179
+#ifdef GINT_RF
+#define GINT_N_DISPATCH GINT_N_DISPATCH_RF
+#else
+#define GINT_N_DISPATCH GINT_N_DISPATCH_PLAIN
+#endif
 
 enum gint_opcode {
 #define GINT_X_ENUM(name, num, md, net) OP_##name = num,
     GINT_OPCODE_LIST(GINT_X_ENUM)
     GINT_INTERNAL_OPCODE_LIST(GINT_X_ENUM)
+    GINT_RF_OPCODE_LIST(GINT_X_ENUM)
 #undef GINT_X_ENUM
 };
 

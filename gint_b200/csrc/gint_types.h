@@ -64,7 +64,7 @@ struct LaunchArgs {
     uint32_t zero;            // always 0; a zero the assembler cannot see (fma_barrier in gint_interp.cuh)
     uint32_t row_area_bytes;  // shared-memory bytes per tile for staged row blocks (StageRows), 0 if the program has none
     uint32_t ring_bytes;      // shared-memory bytes per tile for the ring of early-issued loads, 0 if the stream has none
-    uint32_t reserved;
+    uint32_t rf_bytes;        // shared-memory bytes per tile for virtual registers (kernels built with GINT_RF; 512 per register), else 0
     Footprint fp[GINT_MAX_TENSORS];
     gint_tensor_info ti;      // descriptor block, base pointers patched per call: travels as a kernel parameter
     uint2 inline_code[kInlineCodeSlots];   // the program itself when it has at most kInlineCodeSlots entries (code == nullptr)

@@ -44,17 +44,19 @@ def derive() -> dict:
     from .programs import load_records, recorded
     lib = capi.load_library()
     fused_first = _header_int("GINT_FUSED_FIRST", "gint_fused.h")
-    n_dispatch = _header_int("GINT_N_DISPATCH", "gint_opcodes.h")
-    n_fused = n_dispatch - fused_first
-    buf = (ctypes.c_int32 * (n_fused * 10))()
-    assert lib.gint_debug_fused_table(buf, n_fused) == n_fused
+    n_dispatch = _header_int("GINT_N_DISPATCH_PLAIN", "gint_opcodes.h")
+    n_dispatch_rf = _header_int("GINT_N_DISPATCH_RF", "gint_opcodes.h")     # the register-file kernels dispatch on more opcodes
+    buf = (ctypes.c_int32 * (256 * 10))()
+    n_fused = lib.gint_debug_fused_table(buf, 256)
+    assert n_fused > 0
     members = {buf[10 * k]: [buf[10 * k + 2 + j] for j in range(buf[10 * k + 1])] for k in range(n_fused)}
     net = _effects()
 
     def net_of(op: int) -> int:
         return sum(net[m] for m in members[op]) if op in members else net[op]
 
-    keys: set[tuple[int, int]] = set()
+    keys: set[tuple[int, int]] = set()       # handlers of the ordinary streams
+    rf_keys: set[tuple[int, int]] = set()    # handlers of the streams with the virtual registers in shared memory (their own kernels)
     for name in load_records():
         if name == "execute_everything":      # refused by the library (deeper than any kernel's stack)
             continue
@@ -64,28 +66,33 @@ def derive() -> dict:
         fill_tensor_info(ti, prog.tensor_infos)
         cap = code.size + 64
         ops, operands = (ctypes.c_int32 * cap)(), (ctypes.c_uint32 * cap)()
-        for early in (0, 1):
+        for early in (0, 1, 2, 3):            # bit 0: early-issue pass; bit 1: the stream with the registers in shared memory
             n = lib.gint_debug_transform(code.ctypes.data_as(ctypes.POINTER(ctypes.c_int32)), int(code.size), ctypes.byref(ti),
                                          len(prog.tensor_infos), early, 1, ops, operands, cap)
+            if n == 0 and early & 2:          # the program does not qualify for that stream
+                continue
             assert n > 0, (name, n)
             depth = 0
             for i in range(n):
                 op = ops[i]
                 if op < 0:                    # absorbed into the fused handler before it
                     continue
-                keys.add((depth, op))
+                (rf_keys if early & 2 else keys).add((depth, op))
                 depth += net_of(op)
-    return {"n_dispatch": n_dispatch, "fused_first": fused_first, "keys": sorted([d, o] for d, o in keys)}
+    return {"n_dispatch": n_dispatch, "n_dispatch_rf": n_dispatch_rf, "fused_first": fused_first,
+            "keys": sorted([d, o] for d, o in keys), "rf_keys": sorted([d, o] for d, o in rf_keys)}
 
 
-def load() -> set[tuple[int, int]]:
-    """The committed list as a set of (depth, opcode); empty if the file is absent or was made for another numbering."""
+def load(rf: bool = False) -> set[tuple[int, int]]:
+    """The committed list as a set of (depth, opcode); empty if the file is absent or was made for another numbering.
+    ``rf``: the list for the kernels that keep the virtual registers in shared memory."""
     try:
         with open(TABLE) as f:
             t = json.load(f)
-        if t["n_dispatch"] != _header_int("GINT_N_DISPATCH", "gint_opcodes.h") or t["fused_first"] != _header_int("GINT_FUSED_FIRST", "gint_fused.h"):
+        if t["n_dispatch"] != _header_int("GINT_N_DISPATCH_PLAIN", "gint_opcodes.h") or t["fused_first"] != _header_int("GINT_FUSED_FIRST", "gint_fused.h") or \
+                t["n_dispatch_rf"] != _header_int("GINT_N_DISPATCH_RF", "gint_opcodes.h"):
             return set()
-        return {(d, o) for d, o in t["keys"]}
+        return {(d, o) for d, o in t["rf_keys" if rf else "keys"]}
     except (OSError, KeyError, ValueError):
         return set()
 
@@ -94,7 +101,7 @@ def main() -> None:
     t = derive()
     with open(TABLE, "w") as f:
         json.dump(t, f)
-    print(f"{TABLE}: {len(t['keys'])} handlers")
+    print(f"{TABLE}: {len(t['keys'])} handlers, {len(t['rf_keys'])} for the register-file kernels")
 
 
 if __name__ == "__main__":

@@ -98,8 +98,9 @@ def cluster_small_handlers(lines: list[str], limit: int = SMALL_HANDLER_INSNS, o
     return out, len(moved)
 
 
-def rewrite(ptx: str, n_keys: int, n_ops: int = 142, cluster: bool = True, hot: set | None = None) -> tuple[str, dict]:
-    """Return (rewritten PTX, stats). ``n_keys`` is the size of the dispatch key space."""
+def rewrite(ptx: str, n_keys: int, n_ops: int = 142, cluster: bool = True, hot: set | None = None, hot_any_size: bool = False) -> tuple[str, dict]:
+    """Return (rewritten PTX, stats). ``n_keys`` is the size of the dispatch key space. ``hot_any_size``: single-block handlers
+    in ``hot`` join the cluster whatever their length (kernels whose hot handlers are long fused sequences)."""
     lines = ptx.split("\n")
     # depth -1 stands for "all": the non-threaded form, one table over every (depth, opcode) key
     dispatch = [(i, m.group(1), m.group(2), -1 if m.group(3) == "all" else int(m.group(3)))
@@ -201,5 +202,5 @@ def rewrite(ptx: str, n_keys: int, n_ops: int = 142, cluster: bool = True, hot: 
 
         def order(key: int):
             return (0 if key in hot_keys else 1, key)
-        out, n_moved = cluster_small_handlers(out, order=order)
+        out, n_moved = cluster_small_handlers(out, order=order, always=hot_keys if hot_any_size else None)
     return "\n".join(out), {"cases": len(numeric), "keys": n_keys, "sites": len(sites), "tables": len(used_depths), "clustered": n_moved}

@@ -76,7 +76,8 @@ typedef struct gint_launch_info {
     int32_t blocks_per_sm;
     int32_t num_sms;
     int32_t early_loads;      /* tile loads per logical program that are started ahead of their use (early issue) */
-    int32_t reserved[7];
+    int32_t registers_in_smem; /* virtual registers kept in shared memory (the pool then holds the operand stack alone); 0: in the pool */
+    int32_t reserved[6];
 } gint_launch_info;
 
 /* What a checked launch (gint_execute_checked) found; all zero = nothing. The FIRST event is described, `count` counts all. */
@@ -122,7 +123,10 @@ int gint_predecode(const int32_t *code, int n_words, uint32_t *out_keys, int max
 /* The instruction list the kernels actually run for a program, after the optional early-issue and fusion passes (for
  * tests; no GPU needed): out_ops[i] is a format opcode, an internal opcode (>= 106) or -1 for an instruction absorbed into
  * the fused handler before it. With early_issue != 0 the descriptors in `ti` also decide which 1-D accesses become their
- * "fast" forms (provably full, aligned tiles). Returns the number of instructions (including the Halt) or < 0. */
+ * "fast" forms (provably full, aligned tiles). early_issue is a bit set: 1 = the early-issue pass, 2 = the stream for the
+ * kernels that keep the virtual registers in shared memory (FLoadRegN / FStoreRegN become RLoad / RStore with the register in
+ * the operand; returns 0 if the program does not qualify for them). Returns the number of instructions (including the Halt)
+ * or < 0. */
 int gint_debug_transform(const int32_t *code, int n_words, const gint_tensor_info *ti, int n_tensors, int early_issue, int fuse,
                          int32_t *out_ops, uint32_t *out_operands, int max_insns);
 
@@ -267,7 +271,9 @@ int gint_execute_indirect_static(gint_ctx *ctx, const uint64_t *handles, int n_p
 /* Knobs for later launches: "tiles_per_warp" (0 = automatic, else upper bound 1/2/4), "early_issue" (1 = start tile
  * loads ahead of their use when safe, default; 0 = keep loads where they are), "fuse" (1 = replace known instruction
  * sequences by fused handlers, default; applies to programs created afterwards), "prefetch" (L2 footprint prefetch,
- * default 0), "max_blocks" (cap on the persistent grid, 0 = none). */
+ * default 0), "max_blocks" (cap on the persistent grid, 0 = none), "lower" (1 = lane indices of DupBroadcastW move into the
+ * opcode, default; programs created afterwards), "register_file" (1 = programs that need the 12-slot pool only for their
+ * virtual registers keep those in shared memory and run on a kernel whose pool is the operand stack alone, default). */
 int gint_set_option(gint_ctx *ctx, const char *name, int value);
 
 #ifdef __cplusplus

@@ -473,6 +473,34 @@ def shifted_in_place(a, out, REGW, WARP):
     halt()
 
 
+@bytecode
+def register_pressure(a, b, o0, o1, REGW, WARP):
+    """Eight registers and a stack five deep: the 12-slot pool in the reference (register 7 and stack slot 4 are the same pool
+    entry there, which this program never notices), the register-file kernels here. Register loads feed permutes, shuffles and
+    products in the combinations those kernels fuse, and a few that they do not."""
+    N, = a.shape
+    ab, bb, o0b, o1b = [make_block_1d(t, N, 1, cdiv(N, 128), 128) for t in (a, b, o0, o1)]
+    fldg_1d(0, ab); fstore_reg(0)
+    fldg_1d(0, bb); fstore_reg(1)
+    for n in range(2, 8):                                     # r[n] = r[n-1] * 0.5 + r[n-2]
+        fload_reg(n - 2); fload_reg(n - 1); fmulimm(0.5); fadd(); fstore_reg(n)
+    fload_reg(7); fperm_w(1, 0, 3, 2); fload_reg(6); fperm_w(2, 3, 0, 1); fmul()      # load, permute, load, permute, multiply
+    fload_reg(5); fperm_w(3, 3, 0, 0); fload_reg(4); fmul()                           # load, permute, load, multiply
+    fload_reg(3); fload_reg(2); fperm_w(0, 2, 1, 3); fmul()                           # load, load, permute, multiply
+    fload_reg(1); fload_reg(0); fshuf2(3, 1, 2, 0)                                    # load, load, shuffle   (depth 4)
+    fload_reg(6); fmul()                                                              # load, multiply (register 7 is gone by now:
+                                                                                      # the fifth stack slot is the same pool entry)
+    fadd(); fadd(); fsub(); fstore_reg(3)                                             # depth 0
+    fload_reg(0); fload_reg(1); dup2(); fshuf2(0, 1, 0, 1); fstore_reg(4); fshuf2(2, 3, 2, 3); fstore_reg(5)
+    fload_reg(3); fload_reg(4); fload_reg(5); fload_reg(6); fload_reg(2)               # depth 5
+    fmul(); frsub(); fstore_reg(6)                                                    # multiply, reverse subtract, store
+    fmul()
+    fload_reg(6); fperm_w(2, 2, 1, 1); fadd()
+    fstg_1d(0, o0b)
+    fload_reg(3); fload_reg(5); fmul(); fload_reg(4); frsub(); fstg_1d(0, o1b)
+    halt()
+
+
 # ------------------------------------------------------------------------------------------------ case list
 
 def _z(*shape, dtype=torch.float32):
@@ -571,6 +599,11 @@ def build_cases() -> list[Case]:
         def mkp(g, n=n):
             return [torch.randn(n, generator=g), torch.randn(n, generator=g), _z(n)]
         cases.append(Case(f"permute_selectors_n{n}", permute_selectors, mkp, cdiv(n, 128), [2]))
+
+    for n in [128, 1000, 40000]:
+        def mkr(g, n=n):
+            return [torch.randn(n, generator=g), torch.randn(n, generator=g), _z(n), _z(n)]
+        cases.append(Case(f"register_pressure_n{n}", register_pressure, mkr, cdiv(n, 128), [2, 3]))
 
     for n in [1, 128, 1000]:
         def mkf(g, n=n):

@@ -265,14 +265,45 @@ def test_plan_runs_all_steps_with_one_call():
 def test_launch_info_reports_geometry():
     from gint_b200.workloads import make_workload
     ex = get_executor()
-    for name, pool in (("rmsnorm", 4), ("bmm4x4", 7), ("inv4x4", 12)):
+    # (the inverse needs 12 slots with its 8 registers in the pool; they live in shared memory instead and the pool is its stack)
+    for name, pool, smem_regs in (("rmsnorm", 4, 0), ("bmm4x4", 7, 0), ("inv4x4", 7, 8)):
         wl = make_workload(name, {"rmsnorm": 64}.get(name, 1000), {"rmsnorm": 4096}.get(name, 16), device="cuda")
         st = wl.steps[0]
         info = ex.launch_info(st.program, [wl.tensors[r] for r in st.roles], st.grid_dim)
-        assert info["pool_size"] == pool
+        assert info["pool_size"] == pool and info["registers_in_smem"] == smem_regs
         assert info["tiles_per_warp"] in (1, 2, 4)
         assert info["num_sms"] == torch.cuda.get_device_properties(0).multi_processor_count
         assert info["grid_blocks"] >= 1 and info["regs_per_thread"] > 0 and info["smem_bytes"] > 0
+
+
+@pytest.mark.parametrize("name,leading", [("inv4x4", 1000), ("inv4x4", 33), ("inv4x4", 524288)])
+def test_registers_in_shared_memory_give_the_bits_of_the_pool(name, leading):
+    """The same program on the kernel that keeps the virtual registers in shared memory (default for programs that would need
+    the 12-slot pool) and on the 12-slot pool kernel, which lays stack and registers out as the reference does."""
+    from gint_b200.workloads import make_workload
+    ex = get_executor()
+    rf, pool = make_workload(name, leading, 16, device="cuda"), make_workload(name, leading, 16, device="cuda")
+    st = rf.steps[0]
+    assert ex.launch_info(st.program, [rf.tensors[r] for r in st.roles], st.grid_dim)["registers_in_smem"] == 8
+    rf.run(ex, torch.cuda.current_stream().cuda_stream)
+    ex.set_option("register_file", 0)
+    try:
+        assert ex.launch_info(st.program, [pool.tensors[r] for r in st.roles], st.grid_dim)["pool_size"] == 12
+        pool.run(ex, torch.cuda.current_stream().cuda_stream)
+    finally:
+        ex.set_option("register_file", 1)
+    torch.cuda.synchronize()
+    for role in rf.outputs:
+        assert bits_equal(rf.tensors[role], pool.tensors[role]), mismatch_report(rf.tensors[role], pool.tensors[role])
+
+
+def test_register_pressure_case_runs_on_the_register_file_kernel():
+    import cases as C
+    ex = get_executor()
+    case = [c for c in C.build_cases() if c.name == "register_pressure_n1000"][0]
+    ts = [t.cuda() for t in case.make(torch.Generator().manual_seed(3))]
+    info = ex.launch_info(case.program, ts, case.grid_dim)
+    assert info["pool_size"] == 7 and info["registers_in_smem"] == 8
 
 
 def test_indirect_launch_runs_lane_broadcasts_of_a_small_pool_program():

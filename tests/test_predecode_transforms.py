@@ -15,6 +15,7 @@ from gint_b200.programs import load_records, recorded
 
 PF_TAKE, PF_ISSUE_1D, PF_TAKE_ISSUE_1D, PF_SKIP, LOAD_1D_FAST, STORE_1D_FAST, PF_ISSUE_1D_FAST, PF_TAKE_ISSUE_1D_FAST, STAGE_ROWS, LOAD_STAGED_ROWS = range(106, 116)
 BCAST, LOAD_2DW_FAST, STORE_2DW_FAST = 116, 120, 121   # Bcast_0..3
+RLOAD, RSTORE = 150, 151                               # virtual registers in shared memory: operand = 512 * register number
 
 
 def fused_table():
@@ -85,6 +86,9 @@ def undo(prog, table):
             i += 1
     # 1b. DupBroadcastW with a built-in lane index -> the format's instruction with an operand
     flat = [(O.DupBroadcastW, op - BCAST) if BCAST <= op < BCAST + 4 else (op, operand) for op, operand in flat]
+    # 1c. registers in shared memory -> the format's per-register opcodes
+    flat = [(O.FLoadReg0 + operand // 512, 0) if op == RLOAD else (O.FStoreReg0 + operand // 512, 0) if op == RSTORE else (op, operand)
+            for op, operand in flat]
     # 2. fast accesses -> the generic opcodes they specialise
     generic = {LOAD_1D_FAST: O.LoadGlobal1DF32, STORE_1D_FAST: O.StoreGlobal1DF32, PF_ISSUE_1D_FAST: PF_ISSUE_1D,
                PF_TAKE_ISSUE_1D_FAST: PF_TAKE_ISSUE_1D, LOAD_2DW_FAST: O.LoadGlobal2DWF32, STORE_2DW_FAST: O.StoreGlobal2DWF32}
@@ -142,6 +146,71 @@ def test_transforms_are_invertible_on_random_programs(family):
         got = transform(pd.program, pd.input_infos, 1, 1)
         want = fold_repeated_loads(normalised(pd.program))
         assert zero_operands(undo(got, table)) == zero_operands(want), seed
+
+
+def test_register_file_stream_is_invertible_and_shorter():
+    """The 4x4 inverse (8 registers, stack depth 5: the 12-slot pool) qualifies for the kernels that keep the registers in shared
+    memory; its stream there undoes to the same program and needs less than half the dispatches."""
+    table = fused_table()
+    prog = recorded("inv4x4_b4194304")
+    for early in (2, 3):
+        got = transform(prog.bytecode, prog.tensor_infos, early, 1)
+        want = normalised(prog.bytecode)
+        if early & 1:
+            want = fold_repeated_loads(want)
+        assert zero_operands(undo(got, table)) == zero_operands(want)
+        members = [m for op, _ in got for m in (table[op] if op in table else [op])]
+        assert not any(O.FLoadReg0 <= m <= O.FStoreReg7 for m in members) and (members.count(RLOAD), members.count(RSTORE)) == (56, 16)
+    assert sum(1 for op, _ in transform(prog.bytecode, prog.tensor_infos, 3, 1) if op != -1) <= 80
+    assert sum(1 for op, _ in transform(prog.bytecode, prog.tensor_infos, 1, 1) if op != -1) >= 160
+    # programs whose pool is smaller than 12 slots keep their registers in the pool
+    lib = capi.load_library()
+    small = recorded("rmsnorm_r64_n4096")
+    code = np.ascontiguousarray(np.asarray(small.bytecode, dtype=np.int32).reshape(-1))
+    ti = capi.HTensorInfo()
+    fill_tensor_info(ti, small.tensor_infos)
+    assert lib.gint_debug_transform(code.ctypes.data_as(ctypes.POINTER(ctypes.c_int32)), code.size, ctypes.byref(ti), len(small.tensor_infos),
+                                    3, 1, None, None, 4096) == 0
+
+
+def _rf_qualifies(bytecode):
+    lib = capi.load_library()
+    code = np.ascontiguousarray(np.asarray(bytecode, dtype=np.int32).reshape(-1))
+    infos = [capi_info()]
+    ti = capi.HTensorInfo()
+    fill_tensor_info(ti, infos)
+    n = lib.gint_debug_transform(code.ctypes.data_as(ctypes.POINTER(ctypes.c_int32)), code.size, ctypes.byref(ti), 1, 2, 0, None, None, 4096)
+    assert n >= 0, n
+    return n > 0
+
+
+def capi_info():
+    from gint_b200.host import frontend as fe
+    return fe.ProgramTensorInfo(4, [], [], [128, 1], [1, 0], [1, 1], [0, 0])
+
+
+def test_register_file_needs_an_unobservable_overlap():
+    """In the 12-slot pool register 7 IS stack slot 4 (register n = pool[11 - n]). A program that can see this keeps the pool
+    layout; one that cannot may keep its registers elsewhere."""
+    from gint_b200.host import frontend as fe
+    one = [fe.LoadImm, 0x3F800000]
+    push5, pop5 = [one] * 5, [[fe.Pop, 0]] * 5
+    tail = [[fe.StoreGlobal1DF32, 0], [0, 0]]
+    # register 7 is written, the stack then grows over it, and it is read afterwards: the overlap is visible
+    seen = [one, [fe.FStoreReg7, 0]] + push5 + pop5 + [[fe.FLoadReg7, 0]] + tail
+    assert not _rf_qualifies(seen)
+    # the same with the register written after the stack has shrunk again
+    unseen = push5 + pop5 + [one, [fe.FStoreReg7, 0], [fe.FLoadReg7, 0]] + tail
+    assert _rf_qualifies(unseen)
+    # a stack value that a register store would clobber
+    clobber = push5 + [one, [fe.FStoreReg7, 0]] + [[fe.FAdd, 0]] * 4 + tail
+    assert not _rf_qualifies(clobber)
+    # a register read before it is written reads the zero the pool starts with: stays in the pool
+    unwritten = push5 + pop5 + [[fe.FLoadReg7, 0]] + tail
+    assert not _rf_qualifies(unwritten)
+    # stack deeper than the 7 slots of the register-file kernels
+    deep = [one, [fe.FStoreReg7, 0]] + [one] * 8 + [[fe.Pop, 0]] * 7 + tail
+    assert not _rf_qualifies(deep)
 
 
 def test_named_programs_get_the_expected_shape():
