@@ -141,7 +141,7 @@ int net_effect(int op)
         for (int j = 0; j < f.len; j++) net += net_effect(f.ops[j]);
         return net;
     }
-    if (op == OP_RLoad) return 1;
+    if (op == OP_RLoad || op == OP_RLoadP || op == OP_RLoadS) return 1;
     if (op == OP_RStore) return -1;
     return kEffects[op].net;
 }
@@ -519,13 +519,61 @@ bool rf_equivalent(const std::vector<Insn> &prog, int P)
     return true;
 }
 
-/* FLoadRegN / FStoreRegN -> RLoad / RStore with the register number in the operand (512 bytes per register and tile). */
+/* FLoadRegN / FStoreRegN -> RLoad / RStore with the register number in the operand (512 bytes per register and tile). The
+ * register area keeps a lane's four width values in four planes, so a lane permutation or shuffle that is applied to freshly
+ * loaded registers is folded into the load (the handler reads other planes; no selects):
+ *   RLoad a, FPermW s                  ->  RLoadP(a, s)
+ *   RLoad a, RLoad b, FShuf2 s         ->  RLoadS(a, b, s)
+ *   RLoad a, RLoad b, Dup2, FShuf2 s1, X1, FShuf2 s2, X2     (two shuffles of the same pair, each consumed at once)
+ *       X = row stores to memory       ->  RLoadS(a, b, s1), X1, RLoadS(a, b, s2), X2
+ *       X = RStore c, RStore d, c != d ->  RLoadS(a, b, s1), RLoadS(a, b, s2), RStore d, RStore c
+ *         (both shuffles read a and b before either store, as the stack copies did in the original -- c or d may be a or b)
+ * Selectors are already clamped to 0..3 (normalise). */
+uint32_t pack_selectors(uint32_t clamped_bytes)
+{
+    return (clamped_bytes & 3u) | ((clamped_bytes >> 8) & 3u) << 2 | ((clamped_bytes >> 16) & 3u) << 4 | ((clamped_bytes >> 24) & 3u) << 6;
+}
 void rf_rewrite(std::vector<Insn> *prog)
 {
     for (Insn &in : *prog) {
         if (in.op >= OP_FLoadReg0 && in.op <= OP_FLoadReg7) in = Insn{OP_RLoad, (uint32_t)(in.op - OP_FLoadReg0) * 512u};
         else if (in.op >= OP_FStoreReg0 && in.op <= OP_FStoreReg7) in = Insn{OP_RStore, (uint32_t)(in.op - OP_FStoreReg0) * 512u};
     }
+    const std::vector<Insn> &p = *prog;
+    std::vector<Insn> out;
+    out.reserve(p.size());
+    auto is_row_store = [](int op) { return op == OP_StoreGlobal2DWF32 || op == OP_StoreGlobal2DWF32Fast; };
+    for (size_t i = 0; i < p.size();) {
+        const size_t left = p.size() - i;
+        if (left >= 7 && p[i].op == OP_RLoad && p[i + 1].op == OP_RLoad && p[i + 2].op == OP_Dup2 && p[i + 3].op == OP_FShuf2 &&
+            p[i + 5].op == OP_FShuf2) {
+            const uint32_t pair = p[i].operand | p[i + 1].operand << 12;
+            const Insn s1{OP_RLoadS, pair | pack_selectors(p[i + 3].operand) << 24}, s2{OP_RLoadS, pair | pack_selectors(p[i + 5].operand) << 24};
+            if (is_row_store(p[i + 4].op) && is_row_store(p[i + 6].op)) {
+                out.insert(out.end(), {s1, p[i + 4], s2, p[i + 6]});
+                i += 7;
+                continue;
+            }
+            if (p[i + 4].op == OP_RStore && p[i + 6].op == OP_RStore && p[i + 4].operand != p[i + 6].operand) {
+                out.insert(out.end(), {s1, s2, p[i + 6], p[i + 4]});
+                i += 7;
+                continue;
+            }
+        }
+        if (left >= 3 && p[i].op == OP_RLoad && p[i + 1].op == OP_RLoad && p[i + 2].op == OP_FShuf2) {
+            out.push_back(Insn{OP_RLoadS, p[i].operand | p[i + 1].operand << 12 | pack_selectors(p[i + 2].operand) << 24});
+            i += 3;
+            continue;
+        }
+        if (left >= 2 && p[i].op == OP_RLoad && p[i + 1].op == OP_FPermW) {
+            out.push_back(Insn{OP_RLoadP, p[i].operand | pack_selectors(p[i + 1].operand) << 16});
+            i += 2;
+            continue;
+        }
+        out.push_back(p[i]);
+        i++;
+    }
+    *prog = out;
 }
 
 uint64_t tensor_extent_bytes(const gint_tensor_info &ti, int t)

@@ -60,45 +60,40 @@
 
 /*
  * Register-operand forms, for the kernels that keep the virtual registers in shared memory (GINT_RF) and the streams made for
- * them. RLoad / RStore carry the register number in their operand word and FPermW / FShuf2 their selectors, so ONE handler
+ * them. RLoad / RStore / RLoadP / RLoadS carry register numbers and lane selectors in their operand words, so ONE handler
  * serves a sequence whatever registers and lane permutations it names -- with the registers in the pool every combination
  * would need a handler of its own. The sequences are the building blocks of the small-matrix programs (gint/host/matrix.py:
  * products of two permuted registers, accumulated or subtracted; shuffles of register pairs; shuffled pairs stored as rows).
  * Numbered after RLoad / RStore (gint_opcodes.h).
  */
-#define GINT_RF_FUSED_FIRST 152
-#define GINT_RF_PP OP_RLoad, OP_FPermW, OP_RLoad, OP_FPermW, OP_FMul     /* perm(r[a]) * perm(r[b]) */
-#define GINT_RF_P1 OP_RLoad, OP_FPermW, OP_RLoad, OP_FMul                /* perm(r[a]) * r[b]       */
-#define GINT_RF_1P OP_RLoad, OP_RLoad, OP_FPermW, OP_FMul                /* r[a] * perm(r[b])       */
+#define GINT_RF_FUSED_FIRST 154
+#define GINT_RF_PP OP_RLoadP, OP_RLoadP, OP_FMul      /* perm(r[a]) * perm(r[b]) */
+#define GINT_RF_P1 OP_RLoadP, OP_RLoad, OP_FMul       /* perm(r[a]) * r[b]       */
+#define GINT_RF_1P OP_RLoad, OP_RLoadP, OP_FMul       /* r[a] * perm(r[b])       */
 #define GINT_RF_FUSED_LIST(X)                                                            \
-    X(GINT_RF_FUSED_FIRST + 0, 5, GINT_RF_PP)                                            \
-    X(GINT_RF_FUSED_FIRST + 1, 4, GINT_RF_P1)                                            \
-    X(GINT_RF_FUSED_FIRST + 2, 4, GINT_RF_1P)                                            \
-    X(GINT_RF_FUSED_FIRST + 3, 6, GINT_RF_PP, OP_FAdd)                                   \
-    X(GINT_RF_FUSED_FIRST + 4, 6, GINT_RF_PP, OP_FSub)                                   \
-    X(GINT_RF_FUSED_FIRST + 5, 6, GINT_RF_PP, OP_FRSub)                                  \
-    X(GINT_RF_FUSED_FIRST + 6, 5, GINT_RF_P1, OP_FAdd)                                   \
-    X(GINT_RF_FUSED_FIRST + 7, 5, GINT_RF_P1, OP_FSub)                                   \
-    X(GINT_RF_FUSED_FIRST + 8, 5, GINT_RF_P1, OP_FRSub)                                  \
-    X(GINT_RF_FUSED_FIRST + 9, 5, GINT_RF_1P, OP_FAdd)                                   \
-    X(GINT_RF_FUSED_FIRST + 10, 5, GINT_RF_1P, OP_FSub)                                  \
-    X(GINT_RF_FUSED_FIRST + 11, 5, GINT_RF_1P, OP_FRSub)                                 \
-    X(GINT_RF_FUSED_FIRST + 12, 7, GINT_RF_PP, OP_FRSub, OP_RStore)                      \
-    X(GINT_RF_FUSED_FIRST + 13, 7, GINT_RF_P1, OP_FSub, OP_RLoad, OP_FMul)               \
-    X(GINT_RF_FUSED_FIRST + 14, 3, OP_RLoad, OP_RLoad, OP_FShuf2)                        \
-    X(GINT_RF_FUSED_FIRST + 15, 7, OP_RLoad, OP_RLoad, OP_FShuf2, OP_RLoad, OP_RLoad, OP_FShuf2, OP_FMul) \
-    X(GINT_RF_FUSED_FIRST + 16, 7, OP_RLoad, OP_RLoad, OP_Dup2, OP_FShuf2, OP_RStore, OP_FShuf2, OP_RStore) \
-    X(GINT_RF_FUSED_FIRST + 17, 7, OP_RLoad, OP_RLoad, OP_Dup2, OP_FShuf2, OP_StoreGlobal2DWF32Fast, OP_FShuf2, OP_StoreGlobal2DWF32Fast) \
-    X(GINT_RF_FUSED_FIRST + 18, 2, OP_RLoad, OP_FMul)                                    \
-    X(GINT_RF_FUSED_FIRST + 19, 2, OP_RLoad, OP_FPermW)                                  \
-    X(GINT_RF_FUSED_FIRST + 20, 3, OP_FMul, OP_FRSub, OP_RStore)                         \
-    X(GINT_RF_FUSED_FIRST + 21, 2, OP_FMul, OP_FRSub)                                    \
-    X(GINT_RF_FUSED_FIRST + 22, 2, OP_FMul, OP_FSub)                                     \
-    X(GINT_RF_FUSED_FIRST + 23, 2, OP_FRSub, OP_RStore)                                  \
-    X(GINT_RF_FUSED_FIRST + 24, 2, OP_LoadStagedRows, OP_RStore)                         \
-    X(GINT_RF_FUSED_FIRST + 25, 2, OP_RStore, OP_RStore)                                 \
-    X(GINT_RF_FUSED_FIRST + 26, 3, OP_Dup, OP_FPermW, OP_FAdd)
-#define GINT_N_RF_FUSED 27
+    X(GINT_RF_FUSED_FIRST + 0, 3, GINT_RF_PP)                                            \
+    X(GINT_RF_FUSED_FIRST + 1, 3, GINT_RF_P1)                                            \
+    X(GINT_RF_FUSED_FIRST + 2, 3, GINT_RF_1P)                                            \
+    X(GINT_RF_FUSED_FIRST + 3, 4, GINT_RF_PP, OP_FAdd)                                   \
+    X(GINT_RF_FUSED_FIRST + 4, 4, GINT_RF_PP, OP_FSub)                                   \
+    X(GINT_RF_FUSED_FIRST + 5, 4, GINT_RF_PP, OP_FRSub)                                  \
+    X(GINT_RF_FUSED_FIRST + 6, 4, GINT_RF_P1, OP_FAdd)                                   \
+    X(GINT_RF_FUSED_FIRST + 7, 4, GINT_RF_P1, OP_FSub)                                   \
+    X(GINT_RF_FUSED_FIRST + 8, 4, GINT_RF_P1, OP_FRSub)                                  \
+    X(GINT_RF_FUSED_FIRST + 9, 5, GINT_RF_PP, OP_FRSub, OP_RStore)                       \
+    X(GINT_RF_FUSED_FIRST + 10, 6, GINT_RF_P1, OP_FSub, OP_RLoad, OP_FMul)               \
+    X(GINT_RF_FUSED_FIRST + 11, 3, OP_RLoadS, OP_RLoadS, OP_FMul)                        \
+    X(GINT_RF_FUSED_FIRST + 12, 4, OP_RLoadS, OP_RLoadS, OP_RStore, OP_RStore)           \
+    X(GINT_RF_FUSED_FIRST + 13, 4, OP_RLoadS, OP_StoreGlobal2DWF32Fast, OP_RLoadS, OP_StoreGlobal2DWF32Fast) \
+    X(GINT_RF_FUSED_FIRST + 14, 2, OP_RLoad, OP_FMul)                                    \
+    X(GINT_RF_FUSED_FIRST + 15, 3, OP_FMul, OP_FRSub, OP_RStore)                         \
+    X(GINT_RF_FUSED_FIRST + 16, 2, OP_FMul, OP_FRSub)                                    \
+    X(GINT_RF_FUSED_FIRST + 17, 2, OP_FMul, OP_FSub)                                     \
+    X(GINT_RF_FUSED_FIRST + 18, 2, OP_FRSub, OP_RStore)                                  \
+    X(GINT_RF_FUSED_FIRST + 19, 2, OP_LoadStagedRows, OP_RStore)                         \
+    X(GINT_RF_FUSED_FIRST + 20, 2, OP_RStore, OP_RStore)                                 \
+    X(GINT_RF_FUSED_FIRST + 21, 3, OP_Dup, OP_FPermW, OP_FAdd)
+#define GINT_N_RF_FUSED 22
 
 /* is `op` a fused handler (of either list)? */
 #define GINT_IS_FUSED(op) (((op) >= GINT_FUSED_FIRST && (op) < GINT_FUSED_FIRST + GINT_N_FUSED) || (op) >= GINT_RF_FUSED_FIRST)
@@ -108,6 +103,6 @@
 #define GINT_OP_USES_OPERAND(op)                                                                                           \
     (((op) >= OP_LoadImm && (op) <= OP_LoadGlobal1DU8) || (op) == OP_FApprox || ((op) >= OP_LoadGlobal1DF32Indirect && (op) <= OP_DupBroadcastW) || \
      (op) == OP_FPermW || (op) == OP_FShuf2 || (op) == OP_PfIssue1D || (op) == OP_PfTakeIssue1D || (op) == OP_PfSkip || ((op) >= OP_LoadGlobal1DF32Fast && (op) <= OP_LoadStagedRows) || \
-     (op) == OP_LoadGlobal2DWF32Fast || (op) == OP_StoreGlobal2DWF32Fast || (op) == OP_RLoad || (op) == OP_RStore)
+     (op) == OP_LoadGlobal2DWF32Fast || (op) == OP_StoreGlobal2DWF32Fast || ((op) >= OP_RLoad && (op) <= OP_RLoadS))
 
 #endif /* GINT_FUSED_H */

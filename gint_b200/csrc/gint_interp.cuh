@@ -662,7 +662,7 @@ template <int OP, int SP, int P, int K_> __host__ __device__ constexpr bool op_v
         /* virtual registers in shared memory: the pool is the operand stack alone, registers are reached through RLoad / RStore */
         if (OP >= OP_FLoadReg0 && OP <= OP_FStoreReg7) return false;
 #else
-        if (OP == OP_RLoad || OP == OP_RStore) return false;
+        if (OP >= OP_RLoad && OP <= OP_RLoadS) return false;
         if (OP >= OP_FLoadReg0 && OP <= OP_FLoadReg7 && (P - 1 - (OP - OP_FLoadReg0)) < 0) return false;
         if (OP >= OP_FStoreReg0 && OP <= OP_FStoreReg7 && (P - 1 - (OP - OP_FStoreReg0)) < 0) return false;
 #endif
@@ -791,6 +791,17 @@ template <int K, int SLOT, int KI> __device__ __forceinline__ void take_rows(uin
     asm volatile("ld.shared.v2.b64 {%%gs%0, %%gs%1}, [%2];" ::"n"(gs<K>(SLOT, KI, 0)), "n"(gs<K>(SLOT, KI, 1)), "r"(at) : "memory");
 }
 
+/* %grf as a value (kernels built with GINT_RF). Not volatile: the register is written once, before the first handler runs, so
+ * the compiler may merge the reads of the K tiles and of the members of a fused sequence. */
+__device__ __forceinline__ uint32_t rf_base()
+{
+    uint32_t v = 0;
+#ifdef GINT_RF
+    asm("mov.b32 %0, %%grf;" : "=r"(v));
+#endif
+    return v;
+}
+
 template <int OP, int SP, int P, int K, int KI>
 __device__ __forceinline__ void exec_tile(const uint32_t operand, const Ctx &cx)
 {
@@ -912,14 +923,36 @@ __device__ __forceinline__ void exec_tile(const uint32_t operand, const Ctx &cx)
     } else if constexpr (OP >= OP_FStoreReg0 && OP <= OP_FStoreReg7) {
         slot_mov<K, P - 1 - (OP - OP_FStoreReg0), T, KI>();
     }
-    /* ---- virtual registers in shared memory (kernels built with GINT_RF): register n of tile k is the 512-byte block
-     * (n * K + k) of the warp's register area, 16 bytes per lane; %grf = address of block 0 plus 16 * lane; operand = 512 n ---- */
-    else if constexpr (OP == OP_RLoad) {
-        asm volatile("{\n\t.reg .b32 ra;\n\tmad.lo.u32 ra, %2, %3, %%grf;\n\tld.shared.v2.b64 {%%gs%0, %%gs%1}, [ra+%4];\n\t}"
-                     ::"n"(LO(SP)), "n"(HI(SP)), "r"(operand), "n"(K), "n"(KI * 512) : "memory");
+    /* ---- virtual registers in shared memory (kernels built with GINT_RF). Register n of tile k is the 512-byte block
+     * (n * K + k) of the warp's register area, kept as four planes of 128 bytes: width value w of lane l at byte 128 w + 4 l.
+     * %grf = address of block 0 plus 4 * lane. A load or store is four conflict-free 4-byte accesses, and a lane permutation
+     * of a register costs nothing: it is the same four loads from other planes (RLoadP = RLoad, FPermW; RLoadS = RLoad a,
+     * RLoad b, FShuf2 -- the host merges them, gint_capi.cu: rf_rewrite). Operands: RLoad / RStore 512 n; RLoadP 512 n in
+     * bits 0..15 and the four 2-bit plane selectors in bits 16..23; RLoadS 512 a in bits 0..11, 512 b in bits 12..23, the
+     * selectors in bits 24..31 (values 0, 1 from register a -- the deeper stack entry --, 2, 3 from b). ---- */
+    else if constexpr (OP == OP_RLoad || OP == OP_RLoadP) {
+        uint32_t o0 = 0, o1 = 128, o2 = 256, o3 = 384;
+        if constexpr (OP == OP_RLoadP) {
+            o0 = (operand >> 9) & 0x180u; o1 = (operand >> 11) & 0x180u; o2 = (operand >> 13) & 0x180u; o3 = (operand >> 15) & 0x180u;
+        }
+        const uint32_t at = rf_base() + (operand & 0xFFFFu) * (uint32_t)K;   // (not volatile: computed once for all K tiles)
+        asm volatile("{\n\t.reg .b32 t<4>;\n\t"
+                     "ld.shared.b32 t0, [%2+%6];\n\tld.shared.b32 t1, [%3+%6];\n\tld.shared.b32 t2, [%4+%6];\n\tld.shared.b32 t3, [%5+%6];\n\t"
+                     "mov.b64 %%gs%0, {t0, t1};\n\tmov.b64 %%gs%1, {t2, t3};\n\t}"
+                     ::"n"(LO(SP)), "n"(HI(SP)), "r"(at + o0), "r"(at + o1), "r"(at + o2), "r"(at + o3), "n"(KI * 512) : "memory");
+    } else if constexpr (OP == OP_RLoadS) {
+        const uint32_t a = rf_base() + (operand & 0xFFFu) * (uint32_t)K, b = rf_base() + ((operand >> 12) & 0xFFFu) * (uint32_t)K;
+        const uint32_t o0 = (operand >> 17) & 0x180u, o1 = (operand >> 19) & 0x180u, o2 = (operand >> 21) & 0x180u, o3 = (operand >> 23) & 0x180u;
+        asm volatile("{\n\t.reg .b32 t<4>;\n\t"
+                     "ld.shared.b32 t0, [%2+%6];\n\tld.shared.b32 t1, [%3+%6];\n\tld.shared.b32 t2, [%4+%6];\n\tld.shared.b32 t3, [%5+%6];\n\t"
+                     "mov.b64 %%gs%0, {t0, t1};\n\tmov.b64 %%gs%1, {t2, t3};\n\t}"
+                     ::"n"(LO(SP)), "n"(HI(SP)), "r"(a + o0), "r"(a + o1), "r"(b + o2), "r"(b + o3), "n"(KI * 512) : "memory");
     } else if constexpr (OP == OP_RStore) {
-        asm volatile("{\n\t.reg .b32 ra;\n\tmad.lo.u32 ra, %2, %3, %%grf;\n\tst.shared.v2.b64 [ra+%4], {%%gs%0, %%gs%1};\n\t}"
-                     ::"n"(LO(T)), "n"(HI(T)), "r"(operand), "n"(K), "n"(KI * 512) : "memory");
+        const uint32_t at = rf_base() + operand * (uint32_t)K;
+        asm volatile("{\n\t.reg .b32 t<4>;\n\t"
+                     "mov.b64 {t0, t1}, %%gs%0;\n\tmov.b64 {t2, t3}, %%gs%1;\n\t"
+                     "st.shared.b32 [%2+%3], t0;\n\tst.shared.b32 [%2+%4], t1;\n\tst.shared.b32 [%2+%5], t2;\n\tst.shared.b32 [%2+%6], t3;\n\t}"
+                     ::"n"(LO(T)), "n"(HI(T)), "r"(at), "n"(KI * 512), "n"(KI * 512 + 128), "n"(KI * 512 + 256), "n"(KI * 512 + 384) : "memory");
     }
     /* ---- warp all-reduce (reduction.py:7-30, nvptx.py:89-104): butterfly 16, 8, 4, 2, 1 per width lane ---- */
     else if constexpr (OP >= OP_WarpAllReduceSum && OP <= OP_WarpAllReduceProd) {
@@ -1122,7 +1155,7 @@ template <int N> __device__ __forceinline__ void pool_clear()
  *   %gbudget     instructions left before the interpreter gives up (only with GINT_GUARD, a debugging aid)
  *   %gring       byte offset of the current slot in the warp's ring of early-issued loads
  *   %gzero       64 bits of zero that reach the kernel as a launch parameter (see fma_barrier)
- *   %grf         shared-memory address of the warp's virtual registers plus 16 * lane (kernels built with GINT_RF)
+ *   %grf         shared-memory address of the warp's virtual registers plus 4 * lane (kernels built with GINT_RF)
  * so no C++ value is live from handler to handler and a handler's basic block can be entered from any other handler.
  */
 template <bool SMEM> __device__ __forceinline__ void state_declare()
@@ -1353,7 +1386,7 @@ __device__ __forceinline__ void geval_direct_body(const LaunchArgs &a)
     {   /* after the staged row blocks: the virtual registers, rf_bytes (512 per register) per tile */
         unsigned char *after = reinterpret_cast<unsigned char *>(tiles_s + kWarpsPerBlock * K);
         const uint32_t rf = (uint32_t)__cvta_generic_to_shared(after + (size_t)(kWarpsPerBlock * K) * (a.ring_bytes + a.row_area_bytes) +
-                                                               (size_t)(warp * K) * a.rf_bytes + lane * 16);
+                                                               (size_t)(warp * K) * a.rf_bytes + lane * 4);
         asm volatile("mov.b32 %%grf, %0;" ::"r"(rf));
     }
 #endif

@@ -159,6 +159,9 @@
  * they name:
  *   RLoad    push register (operand / 512)      -- operand = 512 * register number
  *   RStore   pop into register (operand / 512)
+ *   RLoadP   push a lane permutation of a register: RLoad, FPermW in one (the register area keeps the four width values of a
+ *            lane in four planes, so a permutation is the same four loads from other planes and costs no selects)
+ *   RLoadS   push a shuffle of two registers: RLoad a, RLoad b, FShuf2 in one
  * The host introduces them (gint_capi.cu: rf_transform) only where the reference's overlap of stack and registers in one
  * pool cannot be observed by the program.
  */
@@ -170,11 +173,11 @@
     X(LoadGlobal2DWF32Fast, 120, 0, 1) X(StoreGlobal2DWF32Fast, 121, 1, -1)
 /* the register-file kernels' own opcodes: numbered after the fused handlers of the ordinary kernels (gint_fused.h), so that
  * nothing in the ordinary kernels -- numbering, dispatch keys, generated code -- depends on them */
-#define GINT_RF_OPCODE_LIST(X) X(RLoad, 150, 0, 1) X(RStore, 151, 1, -1)
+#define GINT_RF_OPCODE_LIST(X) X(RLoad, 150, 0, 1) X(RStore, 151, 1, -1) X(RLoadP, 152, 0, 1) X(RLoadS, 153, 0, 1)
 /* opcodes a kernel dispatches on: the 106 of the format, the 16 internal ones and the 28 fused handlers of gint_fused.h; in
  * the register-file kernels also RLoad / RStore and the register-operand fused handlers */
 #define GINT_N_DISPATCH_PLAIN 150
-#define GINT_N_DISPATCH_RF 179
+#define GINT_N_DISPATCH_RF 176
 #ifdef GINT_RF
 #define GINT_N_DISPATCH GINT_N_DISPATCH_RF
 #else
