@@ -40,7 +40,7 @@ L2_BYTES = 126 * 1024 * 1024
 # the same kernels; traffic grows in proportion to the units): dram__bytes_read.sum per unit as captured, plus the unit's
 # output bytes for the write side -- in the captures part of the output is still dirty in L2 when the kernel ends (89 MB
 # of 134 MB written for RMSNorm), so dram__bytes_write.sum itself understates what a launch eventually writes.
-NCU_DRAM_BYTES_PER_UNIT = {"rmsnorm": 143289088 / 8192 + 16384, "bmm4x4": 134688512 / 1048576 + 64, "inv4x4": 67318272 / 1048576 + 64}
+NCU_DRAM_BYTES_PER_UNIT = {"rmsnorm": 143289088 / 8192 + 16384, "bmm4x4": 134688512 / 1048576 + 64, "inv4x4": 67286016 / 1048576 + 64}
 
 
 def measured_peak():
