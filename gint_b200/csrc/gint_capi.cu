@@ -851,6 +851,14 @@ int plan_direct(gint_ctx *ctx, const Program *p, const StreamView &sv, uint32_t 
      * issued early (measured on the batched 4x4 product: its latency is hidden only by more resident warps, which the
      * narrower kernel gives) */
     int k_max = ctx->opt_tiles_per_warp ? ctx->opt_tiles_per_warp : p->prefer_narrow ? 1 : 2;
+    /* ... unless the logical program is a single tile or so: what a warp keeps in flight is (early-issued loads of one logical
+     * program, at most the ring's depth) x K tiles of 512 bytes, and the dispatches are shared by K tiles. Measured on a + b over
+     * 2^26 elements (torch's add: 6.8 TB/s): one tile per logical program 4.3 / 5.9 / 6.4 TB/s at 1 / 2 / 4 tiles per warp;
+     * two tiles 6.1 / 5.8 / 5.8; four tiles 6.5 / 5.9 / 5.9; sixteen 5.9 / 5.8 / 5.8 -- so only the shortest programs go wide */
+    if (!ctx->opt_tiles_per_warp && sv.early && p->n_early > 0) {
+        const int in_flight = p->n_early < p->ring_slots ? p->n_early : p->ring_slots;
+        if (in_flight < 4 && k_max < 4) k_max = 4;
+    }
     /* A short program whose whole grid is gone after at most two rounds of the resident warps is bound by latency, not
      * throughput: what it waits for is a fixed per-block cost (block start, program staging, descriptor decode) and one or
      * two memory round trips per warp. Fewer, fatter blocks are then faster as long as every SM still gets two of them
