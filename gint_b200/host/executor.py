@@ -350,12 +350,17 @@ class B200Executor(BaseExecutor):
             raise AssertionError("programs and args_list must have the same length")
         n = len(programs)
         grid_dim = len(indices)
+        if n == 0 or grid_dim == 0:
+            return
         handles = (ctypes.c_uint64 * n)()
         ptrs = (ctypes.c_uint64 * (n * MAX_N_TENSORS))()
         ctx = None
         for p, (prog, args) in enumerate(zip(programs, args_list)):
             conv = [_convert_arg(a) for a in args]
-            ctx, line = self._cacheline(prog, conv, {})
+            c, line = self._cacheline(prog, conv, {})
+            if ctx is not None and c is not ctx and c.value != ctx.value:
+                raise ValueError("execute_indirect: the programs of one launch must live on one device")
+            ctx = c
             handles[p] = line.handle
             for i, a in enumerate(line.indices):
                 ptrs[p * MAX_N_TENSORS + i] = conv[a].base_ptr
