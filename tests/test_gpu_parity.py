@@ -167,13 +167,13 @@ def test_transformed_streams_give_the_same_bits_as_the_plain_stream(name, leadin
 
 
 @pytest.mark.parametrize("name,leading,inner,out_role,in_role", [("rmsnorm", 2048, 4096, "out", "x"), ("bmm4x4", 524288, 16, "c", "a"),
-                                                                  ("add", 131072, 1, "out", "a")])
+                                                                  ("add", 131072, 1, "out", "a"), ("inv4x4", 524288, 16, "c", "a")])
 def test_output_aliasing_an_input_runs_the_program_as_written(name, leading, inner, out_role, in_role):
     """The output tensor IS one of the inputs. Loads that the pre-decoder moved ahead of stores (the ring of early-issued
     loads, the staged row blocks) would then read stale data, so such a launch must fall back to the untransformed stream;
     the result has to equal the oracle's, which executes the program as written on the same aliased buffers. Checked on a
     sample of the leading units (the oracle is slow) after the whole launch has run."""
-    sample = {"rmsnorm": 64, "bmm4x4": 1000, "add": 4096}[name]
+    sample = {"rmsnorm": 64, "bmm4x4": 1000, "add": 4096, "inv4x4": 1000}[name]
     gpu = make_workload(name, leading, inner, device="cuda")
     cpu = make_workload(name, sample, inner, device="cpu")
     for r, t in cpu.tensors.items():
