@@ -7,6 +7,7 @@ except the one case listed in ``EXPECTED_REFUSALS``. The module is skipped where
 import json
 import os
 import subprocess
+import tempfile
 import sys
 
 import pytest
@@ -31,7 +32,7 @@ EXPECTED_REFUSALS = {"tests.test_frontend.TestFrontendExpression.test_meaningles
 
 
 def run_module(module: str, executor: str = "b200", timeout: int = 1500) -> dict:
-    out_dir = os.path.join(ROOT, "gpurun_out")
+    out_dir = os.environ.get("GINT_RESULTS_DIR") or os.path.join(tempfile.gettempdir(), "gint_ref_suite")   # per-test outcomes as JSON
     os.makedirs(out_dir, exist_ok=True)
     path = os.path.join(out_dir, f"ref_suite__{executor}__{module.split('.')[-1]}.json")
     if os.path.exists(path):
