@@ -29,12 +29,12 @@ CSRC = os.path.join(PKG_DIR, "csrc")
 KERNELS = os.path.join(CSRC, "kernels")
 OBJ_DIR = os.path.join(CSRC, "build")
 LIB_PATH = os.path.join(PKG_DIR, "libgint_b200.so")
-def _dispatch_count(rf: bool = False) -> int:
-    """GINT_N_DISPATCH_PLAIN / GINT_N_DISPATCH_RF of csrc/gint_opcodes.h: the 106 opcodes of the format + the internal ones + the
-    fused handlers; the kernels with the virtual registers in shared memory (``rf``) dispatch on more."""
+def _dispatch_count(family: str = "plain") -> int:
+    """GINT_N_DISPATCH_PLAIN / _RF / _VEC of csrc/gint_opcodes.h: the 106 opcodes of the format + the internal ones + the fused
+    handlers; the kernel families with opcodes of their own (registers in shared memory, vector layout) dispatch on more."""
     import re
     with open(os.path.join(CSRC, "gint_opcodes.h")) as f:
-        return int(re.search(rf"#define GINT_N_DISPATCH_{'RF' if rf else 'PLAIN'} (\d+)", f.read()).group(1))
+        return int(re.search(rf"#define GINT_N_DISPATCH_{family.upper()} (\d+)", f.read()).group(1))
 
 
 N_OPS = _dispatch_count()
@@ -82,9 +82,10 @@ def _build_kernel(src: str, extra: list[str], jump_table: bool, cluster: bool = 
     log = ""
     if jump_table:
         # the register-file kernels' hot handlers are long fused register-operand sequences: cluster them whatever their length
-        rf = stem.startswith("gint_rf")
-        n_ops = _dispatch_count(rf)
-        text, stats = ptx_dispatch.rewrite(open(ptx).read(), 9 * n_ops, n_ops, cluster=cluster, hot=hot_handlers.load(rf), hot_any_size=rf)
+        family = "rf" if stem.startswith("gint_rf") else "vec" if stem.startswith("gint_vec") else "plain"
+        n_ops = _dispatch_count(family)
+        text, stats = ptx_dispatch.rewrite(open(ptx).read(), 9 * n_ops, n_ops, cluster=cluster, hot=hot_handlers.load(family),
+                                           hot_any_size=family == "rf")
         with open(ptx, "w") as f:
             f.write(text)
         log += f"jump table: {stats['cases']} cases over {stats['keys']} keys, {stats['clustered']} small handlers clustered\n"

@@ -16,6 +16,8 @@
 #include <mutex>
 #include <string>
 #include <atomic>
+#include <array>
+#include <map>
 #include <vector>
 
 #include "../../include/gint_b200.h"
@@ -143,6 +145,7 @@ int net_effect(int op)
     }
     if (op == OP_RLoad || op == OP_RLoadP || op == OP_RLoadS) return 1;
     if (op == OP_RStore) return -1;
+    if (op == OP_RemapVN) return 0;
     return kEffects[op].net;
 }
 
@@ -576,6 +579,249 @@ void rf_rewrite(std::vector<Insn> *prog)
     *prog = out;
 }
 
+/*
+ * Vector layout ("vec" streams and kernels). As written, a 1-D tile puts element e of its 128 into lane e % 32, width value
+ * e / 32, so a warp touches a tile with four 4-byte accesses per lane. Where the host has proved a tile full, unit-stride and
+ * 16-byte aligned, lane l could just as well hold elements 4l..4l+3 -- one 16-byte access per lane -- as long as nothing in the
+ * program can tell the difference. vec_transform decides that by abstract interpretation of the straight-line program. Every
+ * pool entry is one of
+ *   V   tile data in the vector layout (from early-issued or fast 1-D loads)
+ *   N   tile data in the natural layout (from every other load)
+ *   W   the same in all lanes; per width value a symbol that names the expression it holds (equal symbols => equal bits)
+ * (a W whose four symbols are equal is uniform and mixes with anything). Element-wise instructions combine like with like; an
+ * instruction that looks across lanes or width values (warp reductions, FPermW, DupBroadcastW, a store that is not a fast
+ * 1-D store) needs N or W and gets a RemapVN in front of it if its operand is V (RemapVN moves the accumulators to where the
+ * natural layout has them, so a reduction afterwards adds the same values in the same order: bit-identical results). The
+ * symbols make the typical epilogue of a row reduction provable: after WarpAllReduceSum and the two FPermW / FAdd steps that add
+ * the four width values, all four symbols are the same expression up to the order of commutative operands, the value is
+ * uniform, and the second pass may multiply vector-layout tiles with it. Anything the analysis does not know ends it: the
+ * program then simply has no vector-layout stream.
+ */
+struct LaneValue {
+    enum Kind : uint8_t { W, V, N } kind;
+    uint32_t sym[4];
+    bool uniform() const { return kind == W && sym[0] == sym[1] && sym[1] == sym[2] && sym[2] == sym[3]; }
+};
+
+struct SymbolTable {
+    std::map<std::array<uint32_t, 5>, uint32_t> ids;
+    uint32_t next = 1;
+    uint32_t fresh() { return next++; }
+    uint32_t make(uint32_t op, uint32_t operand, uint32_t a, uint32_t b = 0, uint32_t c = 0, bool commutative = false)
+    {
+        if (commutative && a > b) std::swap(a, b);
+        const std::array<uint32_t, 5> key{op, operand, a, b, c};
+        auto it = ids.find(key);
+        if (it != ids.end()) return it->second;
+        return ids[key] = next++;
+    }
+};
+
+bool vec_is_unary(int op)
+{
+    return op == OP_FNeg || op == OP_FAddImm || op == OP_FMulImm || op == OP_FMAImm || (op >= OP_FSqrt && op <= OP_FArcTan) ||
+           (op >= OP_FExp && op <= OP_FErf) || op == OP_FRcp;
+}
+bool vec_is_binary(int op)
+{
+    return op == OP_FAdd || op == OP_FMul || op == OP_FSub || op == OP_FRSub || op == OP_FDiv || op == OP_FRDiv || op == OP_FRem ||
+           (op >= OP_FGt && op <= OP_FApprox) || op == OP_FArcTan2 || op == OP_FPow || (op >= OP_IAdd && op <= OP_IXor);
+}
+bool vec_is_commutative(int op) { return op == OP_FAdd || op == OP_FMul || op == OP_IAdd || op == OP_IMul || op == OP_IAnd || op == OP_IOr || op == OP_IXor; }
+
+/* `prog`: the early-issue stream after the fast-access pass, before lowering and fusion. On success `out` is the stream for the
+ * vector-layout kernels (RemapVN inserted) and the counts say how much it is worth. */
+bool vec_transform(const std::vector<Insn> &prog, std::vector<Insn> *out, int *n_vector_accesses, int *n_remaps)
+{
+    SymbolTable st;
+    std::vector<LaneValue> stack;
+    LaneValue regs[8];
+    const uint32_t zero = st.make(OP_LoadImm, 0u, 0u);
+    for (auto &r : regs) r = LaneValue{LaneValue::W, {zero, zero, zero, zero}};
+    out->clear();
+    *n_vector_accesses = 0;
+    *n_remaps = 0;
+    auto join = [](const LaneValue &a, const LaneValue &b, LaneValue::Kind *k) {   // layout of an element-wise result; false: they clash
+        if (a.kind == LaneValue::W && b.kind == LaneValue::W) { *k = LaneValue::W; return true; }
+        const LaneValue &data = a.kind != LaneValue::W ? a : b, &other = a.kind != LaneValue::W ? b : a;
+        if (other.kind == LaneValue::W) {
+            if (data.kind == LaneValue::V && !other.uniform()) return false;   // width w means other elements in the two layouts
+            *k = data.kind;
+            return true;
+        }
+        if (data.kind != other.kind) return false;
+        *k = data.kind;
+        return true;
+    };
+    auto need_natural_top = [&]() {   // the top of the stack must not be in the vector layout
+        if (stack.back().kind == LaneValue::V) {
+            out->push_back(Insn{OP_RemapVN, 0u});
+            stack.back().kind = LaneValue::N;
+            (*n_remaps)++;
+        }
+    };
+    for (const Insn &in : prog) {
+        const int op = in.op;
+        const size_t d = stack.size();
+        if (op == OP_Halt) { out->push_back(in); return true; }
+        if (op == OP_Nop || op == OP_PfIssue1D || op == OP_PfIssue1DFast || op == OP_PfSkip || op == OP_AdvanceBase || op == OP_AdvanceBlock2D ||
+            op == OP_StageRows) {
+            out->push_back(in);
+        } else if (op == OP_Pop) {
+            if (d < 1) return false;
+            stack.pop_back();
+            out->push_back(in);
+        } else if (op == OP_Pop2) {
+            if (d < 2) return false;
+            stack.pop_back(); stack.pop_back();
+            out->push_back(in);
+        } else if (op == OP_Dup) {
+            if (d < 1) return false;
+            stack.push_back(stack[d - 1]);
+            out->push_back(in);
+        } else if (op == OP_Dup2) {
+            if (d < 2) return false;
+            stack.push_back(stack[d - 2]); stack.push_back(stack[d - 1]);
+            out->push_back(in);
+        } else if (op == OP_DupX1) {          // [a, b] -> [b, a, b]
+            if (d < 2) return false;
+            const LaneValue a = stack[d - 2], b = stack[d - 1];
+            stack[d - 2] = b; stack[d - 1] = a; stack.push_back(b);
+            out->push_back(in);
+        } else if (op == OP_DupX2) {          // [a, b, c] -> [c, a, b, c]
+            if (d < 3) return false;
+            const LaneValue a = stack[d - 3], b = stack[d - 2], c = stack[d - 1];
+            stack[d - 3] = c; stack[d - 2] = a; stack[d - 1] = b; stack.push_back(c);
+            out->push_back(in);
+        } else if (op == OP_Swap) {
+            if (d < 2) return false;
+            std::swap(stack[d - 1], stack[d - 2]);
+            out->push_back(in);
+        } else if (op == OP_LoadImm) {
+            const uint32_t s0 = st.make(OP_LoadImm, in.operand, 0u);
+            stack.push_back(LaneValue{LaneValue::W, {s0, s0, s0, s0}});
+            out->push_back(in);
+        } else if (op == OP_LoadImm4F || op == OP_LoadImm4I) {
+            LaneValue v{LaneValue::W, {}};
+            for (int w = 0; w < 4; w++) v.sym[w] = st.make((uint32_t)op, (in.operand >> (8 * w)) & 0xFFu, 0u);
+            stack.push_back(v);
+            out->push_back(in);
+        } else if (op >= OP_FLoadReg0 && op <= OP_FLoadReg7) {
+            stack.push_back(regs[op - OP_FLoadReg0]);
+            out->push_back(in);
+        } else if (op >= OP_FStoreReg0 && op <= OP_FStoreReg7) {
+            if (d < 1) return false;
+            regs[op - OP_FStoreReg0] = stack.back();
+            stack.pop_back();
+            out->push_back(in);
+        } else if (vec_is_unary(op)) {
+            if (d < 1) return false;
+            LaneValue &t = stack.back();
+            if (t.kind == LaneValue::W)
+                for (int w = 0; w < 4; w++) t.sym[w] = st.make((uint32_t)op, in.operand, t.sym[w]);
+            out->push_back(in);
+        } else if (vec_is_binary(op)) {
+            if (d < 2) return false;
+            const LaneValue t = stack[d - 1], s2 = stack[d - 2];
+            LaneValue r{LaneValue::W, {}};
+            if (!join(t, s2, &r.kind)) return false;
+            if (r.kind == LaneValue::W)
+                for (int w = 0; w < 4; w++) r.sym[w] = st.make((uint32_t)op, in.operand, t.sym[w], s2.sym[w], 0u, vec_is_commutative(op));
+            stack.pop_back();
+            stack.back() = r;
+            out->push_back(in);
+        } else if (op == OP_FMA || op == OP_Select) {
+            if (d < 3) return false;
+            const LaneValue t = stack[d - 1], s2 = stack[d - 2], u = stack[d - 3];
+            LaneValue r{LaneValue::W, {}}, ts{LaneValue::W, {}};
+            if (!join(t, s2, &ts.kind)) return false;
+            if (ts.kind == LaneValue::W) {
+                /* stands for "lane-uniform with the widths of both": uniform only if both are */
+                const bool both = t.uniform() && s2.uniform();
+                for (int w = 0; w < 4; w++) ts.sym[w] = both ? 1u : (uint32_t)(w + 2);
+            }
+            if (!join(ts, u, &r.kind)) return false;
+            if (r.kind == LaneValue::W)
+                for (int w = 0; w < 4; w++) r.sym[w] = st.make((uint32_t)op, in.operand, t.sym[w], s2.sym[w], u.sym[w]);
+            stack.pop_back(); stack.pop_back();
+            stack.back() = r;
+            out->push_back(in);
+        } else if (op >= OP_WarpAllReduceSum && op <= OP_WarpAllReduceProd) {
+            if (d < 1) return false;
+            need_natural_top();
+            LaneValue &t = stack.back();
+            if (t.kind == LaneValue::N) {
+                t.kind = LaneValue::W;
+                for (int w = 0; w < 4; w++) t.sym[w] = st.fresh();
+            } else {
+                for (int w = 0; w < 4; w++) t.sym[w] = st.make((uint32_t)op, 0u, t.sym[w]);
+            }
+            out->push_back(in);
+        } else if (op == OP_FPermW) {
+            if (d < 1) return false;
+            need_natural_top();
+            LaneValue &t = stack.back();
+            if (t.kind == LaneValue::W) {
+                const LaneValue o = t;
+                for (int w = 0; w < 4; w++) t.sym[w] = o.sym[(in.operand >> (8 * w)) & 3u];
+            }
+            out->push_back(in);
+        } else if (op == OP_DupBroadcastW) {
+            if (d < 1) return false;
+            need_natural_top();
+            LaneValue v = stack.back();
+            if (v.kind == LaneValue::W) {
+                const uint32_t s0 = v.sym[in.operand & 3u];
+                for (int w = 0; w < 4; w++) v.sym[w] = s0;
+            }
+            stack.push_back(v);
+            out->push_back(in);
+        } else if (op == OP_FShuf2) {
+            if (d < 2) return false;
+            const LaneValue t = stack[d - 1], s2 = stack[d - 2];
+            if (t.kind == LaneValue::V || s2.kind == LaneValue::V) return false;
+            LaneValue r{LaneValue::N, {}};
+            if (t.kind == LaneValue::W && s2.kind == LaneValue::W) {
+                r.kind = LaneValue::W;
+                for (int w = 0; w < 4; w++) r.sym[w] = (w < 2 ? s2 : t).sym[(in.operand >> (8 * w)) & 3u];
+            }
+            stack.pop_back();
+            stack.back() = r;
+            out->push_back(in);
+        } else if (op == OP_PfTake || op == OP_PfTakeIssue1D || op == OP_PfTakeIssue1DFast || op == OP_LoadGlobal1DF32Fast) {
+            stack.push_back(LaneValue{LaneValue::V, {}});
+            (*n_vector_accesses)++;
+            out->push_back(in);
+        } else if (op == OP_StoreGlobal1DF32Fast) {
+            if (d < 1) return false;
+            const LaneValue &t = stack.back();
+            if (!(t.kind == LaneValue::V || t.uniform())) return false;   // (natural-layout data would need the opposite rearrangement)
+            stack.pop_back();
+            (*n_vector_accesses)++;
+            out->push_back(in);
+        } else if (op == OP_LoadGlobal1DF32 || op == OP_LoadGlobal1DF16 || op == OP_LoadGlobal1DBF16 || op == OP_LoadGlobal1DU8 ||
+                   (op >= OP_LoadGlobal2DTF32 && op <= OP_LoadGlobal2DWU8 && !writes_tensor(op)) || op == OP_LoadStagedRows ||
+                   op == OP_LoadGlobal2DWF32Fast) {
+            stack.push_back(LaneValue{LaneValue::N, {}});
+            out->push_back(in);
+        } else if (writes_tensor(op) && op != OP_StoreGlobal1DF32Indirect) {
+            if (d < 1) return false;
+            need_natural_top();
+            stack.pop_back();
+            out->push_back(in);
+        } else {
+            return false;   // gathers and scatters, and whatever this analysis has not been taught
+        }
+        if (stack.size() > (size_t)GINT_MAX_STACK) return false;
+    }
+    return false;   // no Halt
+}
+
+/* A rearrangement is a round trip through shared memory with two warp synchronisations on the critical path of its logical
+ * program; a vector access saves three load/store instructions. Measured on the conductor graph at two tiles per warp: the fused
+ * program (40 vector accesses, 1 rearrangement) 175 -> 169 us, the row-sum program (8 and 1) 49.7 -> 52.3 us. */
+bool vec_worth_it(int n_vector_accesses, int n_remaps) { return n_vector_accesses >= 16 && n_vector_accesses >= 16 * n_remaps; }
+
 uint64_t tensor_extent_bytes(const gint_tensor_info &ti, int t)
 {
     int64_t elems = 1;
@@ -597,6 +843,7 @@ struct Variant {
     bool ok;
     int resident_warps;   // warps of this kernel the whole device holds when a block needs only its minimum of shared memory
     bool rf = false;      // virtual registers in shared memory (pool = operand stack only)
+    bool vec = false;     // 1-D tiles in the vector layout
 };
 
 /* The embedded cubins are loaded once per process (a cudaLibrary_t is not tied to a device or context). */
@@ -609,6 +856,7 @@ struct KernelImage {
     cudaKernel_t kernel;
     bool loaded;
     bool rf;
+    bool vec = false;
 };
 
 KernelImage g_images[] = {
@@ -617,6 +865,9 @@ KernelImage g_images[] = {
 #undef GINT_X_IMG
 #define GINT_X_IMG(P, K) {gint_cubin_rf_##P##_##K, gint_cubin_rf_##P##_##K##_end, "gint_geval_rf_" #P "_" #K, P, K, nullptr, nullptr, false, true},
     GINT_RF_VARIANTS(GINT_X_IMG)
+#undef GINT_X_IMG
+#define GINT_X_IMG(P, K) {gint_cubin_vec_##P##_##K, gint_cubin_vec_##P##_##K##_end, "gint_geval_vec_" #P "_" #K, P, K, nullptr, nullptr, false, false, true},
+    GINT_VEC_VARIANTS(GINT_X_IMG)
 #undef GINT_X_IMG
 #define GINT_X_IMG(P) {gint_cubin_indirect_##P, gint_cubin_indirect_##P##_end, "gint_geval_indirect_" #P, P, 0, nullptr, nullptr, false, false},
     GINT_INDIRECT_VARIANTS(GINT_X_IMG)
@@ -690,7 +941,13 @@ struct Program {
     uint32_t rf_bytes = 0;      // shared memory per tile for the registers: 512 bytes per register
     bool rf_from_early = false;
     uint2 rf_inline[gint::kInlineCodeSlots];
-    PlanMemo memo[3] = {};      // last launch plan of the plain stream [0], of the early-issue stream [1], of the RF stream [2]
+    /* the stream for the vector-layout kernels (nullptr: none): the early-issue stream with RemapVN where a value has to be in
+     * the natural layout; usable whenever the early-issue stream is */
+    uint2 *vec_dev = nullptr;
+    uint32_t vec_slots = 0;
+    int vec_remaps = 0;
+    uint2 vec_inline[gint::kInlineCodeSlots];
+    PlanMemo memo[4] = {};      // last launch plan of the plain stream [0], the early-issue stream [1], the RF stream [2], the vector-layout stream [3]
     std::mutex memo_mu;
 };
 
@@ -749,6 +1006,9 @@ struct gint_ctx {
     int opt_lower = 1;          // DupBroadcastW -> Bcast_k (lower_lane_moves); applies to programs created afterwards
     int opt_rf = 1;             // launches use a program's RF stream (virtual registers in shared memory) when it has one
     int opt_rf_create = 1;      // programs created from now on get an RF stream when they qualify
+    int opt_vec = 0;            // vector-layout stream and kernels for the programs that qualify (creation and launch). Off unless asked
+                                // for: measured on the conductor graph, the fused program alone gains 2-3 % (175 -> 169 us) but the whole
+                                // graph through the benchmark's plan loses 1-2 % (340 -> 345 us)
     /* scratch for indirect launches */
     void *ind_dev = nullptr;
     void *ind_host = nullptr;
@@ -792,10 +1052,10 @@ Program *lookup(gint_ctx *ctx, uint64_t handle)
     return (p && p->live) ? p : nullptr;
 }
 
-Variant *find_variant(gint_ctx *ctx, int P, int K, bool rf = false)
+Variant *find_variant(gint_ctx *ctx, int P, int K, bool rf = false, bool vec = false)
 {
     for (auto &v : ctx->direct)
-        if (v.P == P && v.K == K && v.rf == rf && v.ok) return &v;
+        if (v.P == P && v.K == K && v.rf == rf && v.vec == vec && v.ok) return &v;
     return nullptr;
 }
 
@@ -810,17 +1070,19 @@ struct StreamView {
     int P;                     // pool size of the kernels that run this stream
     bool early;
     bool rf;
+    bool vec;
 };
 
-StreamView stream_view(const Program *p, bool early, bool rf = false)
+StreamView stream_view(const Program *p, bool early, bool rf = false, bool vec = false)
 {
     StreamView v;
     v.early = early;
     v.rf = rf;
-    v.n_slots = rf ? p->rf_slots : early ? p->early_slots : p->n_slots;
+    v.vec = vec;
+    v.n_slots = rf ? p->rf_slots : vec ? p->vec_slots : early ? p->early_slots : p->n_slots;
     v.ring_bytes = early && p->n_early > 0 ? (uint32_t)p->ring_slots * 512u : 0u;
     v.row_area_bytes = early ? p->row_area_bytes : 0u;
-    v.rf_bytes = rf ? p->rf_bytes : 0u;
+    v.rf_bytes = rf ? p->rf_bytes : vec && p->vec_remaps > 0 ? 512u : 0u;   // (vector layout: the exchange area of RemapVN)
     v.P = rf ? p->rf_pool : p->st.pool_size;
     return v;
 }
@@ -865,19 +1127,19 @@ int plan_direct(gint_ctx *ctx, const Program *p, const StreamView &sv, uint32_t 
      * (measured on a+b over 2^20 elements, device time: 7.1 / 6.3 / 5.9 us at 1 / 2 / 4 tiles per warp). */
     bool latency_bound = false;
     if (!ctx->opt_tiles_per_warp && sv.n_slots <= (uint32_t)gint::kInlineCodeSlots) {
-        Variant *v1 = find_variant(ctx, P, 1, sv.rf);
+        Variant *v1 = find_variant(ctx, P, 1, sv.rf, sv.vec);
         if (v1 && v1->resident_warps > 0 && (uint64_t)count <= 2ull * (uint64_t)v1->resident_warps) {
             latency_bound = true;
             k_max = 1;
             for (int K : ks)
-                if (find_variant(ctx, P, K, sv.rf) && blocks_for(count, K) >= 2ull * (uint64_t)ctx->num_sms) { k_max = K; break; }
+                if (find_variant(ctx, P, K, sv.rf, sv.vec) && blocks_for(count, K) >= 2ull * (uint64_t)ctx->num_sms) { k_max = K; break; }
         }
     }
     Geometry best{};
     bool have = false;
     for (int K : ks) {
         if (K > k_max) continue;
-        Variant *v = find_variant(ctx, P, K, sv.rf);
+        Variant *v = find_variant(ctx, P, K, sv.rf, sv.vec);
         if (!v) continue;
         Geometry c{};
         c.v = v;
@@ -945,19 +1207,22 @@ int launch_direct(gint_ctx *ctx, uint64_t handle, const uint64_t *base_ptrs, int
         if (((p->fast_slots >> t) & 1u) && (base_ptrs[t] & 15u) != 0) early = false;   // fast accesses need aligned bases
     /* the stream with the virtual registers in shared memory, when the stream it was made from is the one this launch may use */
     bool rf = ctx->opt_rf && p->rf_dev != nullptr && p->rf_from_early == early;
-    StreamView sv = stream_view(p, early, rf);   // geometry depends on the stream
+    /* the vector-layout stream, for programs that run more than one tile per warp (measured: the conductor graph's fused program
+     * 174 -> 164 us at two tiles per warp; RMSNorm at one tile per warp 110 -> 112 us, so it stays on the ordinary kernel) */
+    bool vec = ctx->opt_vec && p->vec_dev != nullptr && early && !rf && !p->prefer_narrow && ctx->opt_tiles_per_warp != 1;
+    StreamView sv = stream_view(p, early, rf, vec);   // geometry depends on the stream
     Geometry g;
     {
         /* each program remembers its last plan per stream: a launch that repeats the previous one's size skips the occupancy
          * queries (several microseconds), also when the caller alternates between programs */
         std::lock_guard<std::mutex> lk(p->memo_mu);
-        PlanMemo *m = &p->memo[rf ? 2 : early ? 1 : 0];
+        PlanMemo *m = &p->memo[rf ? 2 : vec ? 3 : early ? 1 : 0];
         if (m->valid && m->count == count && m->opt_k == ctx->opt_tiles_per_warp && m->opt_blocks == ctx->opt_max_blocks) {
             g = m->g;
         } else {
             int rc = plan_direct(ctx, p, sv, count, &g);
-            if (rc != GINT_OK && rf) {   // no RF kernel for this tiles-per-warp choice or this much shared memory: the ordinary kernels
-                rf = false;
+            if (rc != GINT_OK && (rf || vec)) {   // no such kernel for this tiles-per-warp choice or this much shared memory: the ordinary kernels
+                rf = vec = false;
                 sv = stream_view(p, early, false);
                 rc = plan_direct(ctx, p, sv, count, &g);   // (remembered under the RF stream's memo: the next launch asks there again)
             }
@@ -965,11 +1230,12 @@ int launch_direct(gint_ctx *ctx, uint64_t handle, const uint64_t *base_ptrs, int
             *m = PlanMemo{true, count, ctx->opt_tiles_per_warp, ctx->opt_max_blocks, g};
         }
         rf = g.v->rf;
-        if (!rf && sv.rf) sv = stream_view(p, early, false);
+        vec = g.v->vec;
+        if ((!rf && sv.rf) || (!vec && sv.vec)) sv = stream_view(p, early, false);
     }
     LaunchArgs a;
     const bool inline_code = sv.n_slots <= (uint32_t)gint::kInlineCodeSlots;
-    a.code = inline_code ? nullptr : (rf ? p->rf_dev : early ? p->early_dev : p->code_dev);
+    a.code = inline_code ? nullptr : (rf ? p->rf_dev : vec ? p->vec_dev : early ? p->early_dev : p->code_dev);
     a.n_slots = sv.n_slots;
     a.n_tensors = (uint32_t)p->n_tensors;
     a.first = first;
@@ -988,7 +1254,7 @@ int launch_direct(gint_ctx *ctx, uint64_t handle, const uint64_t *base_ptrs, int
         for (int t = 0; t < GINT_MAX_TENSORS; t++) a.fp[t] = p->fp[t];
     a.ti = p->ti;
     for (int i = 0; i < n_tensors; i++) a.ti.base_ptr[i] = (int64_t)base_ptrs[i];
-    if (inline_code) memcpy(a.inline_code, rf ? p->rf_inline : early ? p->early_inline : p->code_inline, sizeof(a.inline_code));
+    if (inline_code) memcpy(a.inline_code, rf ? p->rf_inline : vec ? p->vec_inline : early ? p->early_inline : p->code_inline, sizeof(a.inline_code));
     void *args[1] = {&a};
     cudaError_t e = cudaLaunchKernel(g.v->fn, dim3(g.grid), dim3(gint::kThreadsPerBlock), args, g.smem, (cudaStream_t)stream);
     if (e != cudaSuccess) return fail(ctx, GINT_ERR_CUDA, "cudaLaunchKernel", e);
@@ -1122,7 +1388,7 @@ int gint_create(int device, gint_ctx **out)
         if (!im.loaded) continue;
         if (im.K == 0) ctx->indirect.fn = (const void *)im.kernel;
         else if (im.K < 0) ctx->checked.fn = (const void *)im.kernel;
-        else ctx->direct.push_back(Variant{im.P, im.K, (const void *)im.kernel, 0, false, 0, im.rf});
+        else ctx->direct.push_back(Variant{im.P, im.K, (const void *)im.kernel, 0, false, 0, im.rf, im.vec});
     }
     int usable = 0;
     for (auto &v : ctx->direct) {
@@ -1166,6 +1432,7 @@ void gint_destroy(gint_ctx *ctx)
                 if (p->code_dev) cudaFree(p->code_dev);
                 if (p->early_dev) cudaFree(p->early_dev);
                 if (p->rf_dev) cudaFree(p->rf_dev);
+                if (p->vec_dev) cudaFree(p->vec_dev);
                 delete p;
             }
         }
@@ -1208,7 +1475,7 @@ int gint_program_create(gint_ctx *ctx, const int32_t *code, int n_words, const g
     if (ti) p->ti = *ti;
     for (int t = 0; t < GINT_MAX_TENSORS; t++) p->ti.base_ptr[t] = 0;
     compute_footprints(code, p->st.num_instructions, p->ti, n_tensors, p);
-    std::vector<uint2> early, rfs;
+    std::vector<uint2> early, rfs, vecs;
     {
         std::vector<Insn> prog;
         normalise(code, n_words, n_tensors, &prog);
@@ -1258,6 +1525,16 @@ int gint_program_create(gint_ctx *ctx, const int32_t *code, int n_words, const g
             p->fast_slots = apply_fast_accesses(&ei.prog, p->ti, n_tensors) | apply_fast_rows(&ei.prog, p->ti, n_tensors) | staged;
             p->row_area_bytes = row_area;
             if (rf_ok) make_rf(ei.prog, true);
+            if (ctx->opt_vec && p->st.pool_size == 4 && (find_variant(ctx, 4, 1, false, true) || find_variant(ctx, 4, 2, false, true))) {
+                std::vector<Insn> v;
+                int n_vector = 0, n_remaps = 0;
+                if (vec_transform(ei.prog, &v, &n_vector, &n_remaps) && vec_worth_it(n_vector, n_remaps)) {
+                    if (ctx->opt_lower) lower_lane_moves(&v, p->st.pool_size);
+                    if (ctx->opt_fuse) fuse_sequences(&v);
+                    emit_stream(v, &vecs);
+                    p->vec_remaps = n_remaps;
+                }
+            }
             if (ctx->opt_lower) lower_lane_moves(&ei.prog, p->st.pool_size);
             if (ctx->opt_fuse) fuse_sequences(&ei.prog);
             emit_stream(ei.prog, &early);
@@ -1295,10 +1572,12 @@ int gint_program_create(gint_ctx *ctx, const int32_t *code, int n_words, const g
     }
     p->early_slots = (uint32_t)early.size();
     p->rf_slots = (uint32_t)rfs.size();
+    p->vec_slots = (uint32_t)vecs.size();
     for (int i = 0; i < gint::kInlineCodeSlots; i++) {
         p->code_inline[i] = (size_t)i < pre.size() ? pre[(size_t)i] : make_uint2(0u, OP_Halt);
         p->early_inline[i] = (size_t)i < early.size() ? early[(size_t)i] : make_uint2(0u, OP_Halt);
         p->rf_inline[i] = (size_t)i < rfs.size() ? rfs[(size_t)i] : make_uint2(0u, OP_Halt);
+        p->vec_inline[i] = (size_t)i < vecs.size() ? vecs[(size_t)i] : make_uint2(0u, OP_Halt);
     }
     {
         DeviceGuard guard(ctx->device);
@@ -1327,6 +1606,18 @@ int gint_program_create(gint_ctx *ctx, const int32_t *code, int n_words, const g
                 return fail(ctx, GINT_ERR_OUT_OF_MEMORY, "cudaMalloc/cudaMemcpy(register-file program)", e);
             }
         }
+        if (!vecs.empty()) {
+            e = cudaMalloc(&p->vec_dev, vecs.size() * sizeof(uint2));
+            if (e == cudaSuccess) e = cudaMemcpy(p->vec_dev, vecs.data(), vecs.size() * sizeof(uint2), cudaMemcpyHostToDevice);
+            if (e != cudaSuccess) {
+                if (p->vec_dev) cudaFree(p->vec_dev);
+                if (p->rf_dev) cudaFree(p->rf_dev);
+                if (p->early_dev) cudaFree(p->early_dev);
+                cudaFree(p->code_dev);
+                delete p;
+                return fail(ctx, GINT_ERR_OUT_OF_MEMORY, "cudaMalloc/cudaMemcpy(vector-layout program)", e);
+            }
+        }
     }
     p->live = true;
     std::lock_guard<std::mutex> lk(ctx->mu);
@@ -1350,6 +1641,7 @@ int gint_program_destroy(gint_ctx *ctx, uint64_t handle)
     if (p->code_dev) cudaFree(p->code_dev);
     if (p->early_dev) cudaFree(p->early_dev);
     if (p->rf_dev) cudaFree(p->rf_dev);
+    if (p->vec_dev) cudaFree(p->vec_dev);
     delete p;
     return GINT_OK;
 }
@@ -1363,9 +1655,10 @@ int gint_program_launch_info(gint_ctx *ctx, uint64_t handle, uint32_t grid_dim, 
     Geometry g;
     const bool early = ctx->opt_early_issue && p->early_dev != nullptr;
     const bool rf = ctx->opt_rf && p->rf_dev != nullptr && p->rf_from_early == early;
-    StreamView sv = stream_view(p, early, rf);
+    const bool vec = ctx->opt_vec && p->vec_dev != nullptr && early && !rf && !p->prefer_narrow && ctx->opt_tiles_per_warp != 1;
+    StreamView sv = stream_view(p, early, rf, vec);
     int rc = plan_direct(ctx, p, sv, grid_dim ? grid_dim : 1, &g);
-    if (rc != GINT_OK && rf) {
+    if (rc != GINT_OK && (rf || vec)) {
         sv = stream_view(p, early, false);
         rc = plan_direct(ctx, p, sv, grid_dim ? grid_dim : 1, &g);
     }
@@ -1381,6 +1674,7 @@ int gint_program_launch_info(gint_ctx *ctx, uint64_t handle, uint32_t grid_dim, 
     out->num_sms = ctx->num_sms;
     out->early_loads = p->n_early;
     out->registers_in_smem = g.v->rf ? p->st.max_reg_idx + 1 : 0;
+    out->vector_layout = g.v->vec ? 1 : 0;
     return GINT_OK;
 }
 
@@ -1803,6 +2097,14 @@ int gint_debug_transform(const int32_t *code, int n_words, const gint_tensor_inf
             }
         }
     }
+    if (early_issue & 4) {   // the stream for the vector-layout kernels, if the program qualifies (needs the early-issue pass)
+        gint_bytecode_stats st0;
+        analyze(code, n_words, &st0);
+        std::vector<Insn> v;
+        int n_vector = 0, n_remaps = 0;
+        if (!(early_issue & 1) || st0.pool_size != 4 || !vec_transform(prog, &v, &n_vector, &n_remaps) || !vec_worth_it(n_vector, n_remaps)) return 0;
+        prog = v;
+    }
     if (early_issue & 2) {   // the stream for the kernels with virtual registers in shared memory, if the program qualifies
         gint_bytecode_stats st0;
         analyze(code, n_words, &st0);
@@ -1862,6 +2164,10 @@ int gint_set_option(gint_ctx *ctx, const char *name, int value)
     }
     if (strcmp(name, "register_file") == 0) {   // virtual registers in shared memory: programs created and launches made from now on
         ctx->opt_rf = ctx->opt_rf_create = value != 0;
+        return GINT_OK;
+    }
+    if (strcmp(name, "vector_layout") == 0) {   // programs created and launches made from now on
+        ctx->opt_vec = value != 0;
         return GINT_OK;
     }
     if (strcmp(name, "prefetch") == 0) {

@@ -96,7 +96,8 @@
 #define GINT_N_RF_FUSED 22
 
 /* is `op` a fused handler (of either list)? */
-#define GINT_IS_FUSED(op) (((op) >= GINT_FUSED_FIRST && (op) < GINT_FUSED_FIRST + GINT_N_FUSED) || (op) >= GINT_RF_FUSED_FIRST)
+#define GINT_IS_FUSED(op) (((op) >= GINT_FUSED_FIRST && (op) < GINT_FUSED_FIRST + GINT_N_FUSED) || \
+                           ((op) >= GINT_RF_FUSED_FIRST && (op) < GINT_RF_FUSED_FIRST + GINT_N_RF_FUSED))
 #define GINT_MAX_FUSED_LEN 8
 
 /* does the instruction read its operand word? (fused handlers fetch operands only for those that do) */

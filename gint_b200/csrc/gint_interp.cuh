@@ -584,6 +584,7 @@ template <int OP> struct OpInfo;
 GINT_OPCODE_LIST(GINT_X_INFO)
 GINT_INTERNAL_OPCODE_LIST(GINT_X_INFO)
 GINT_RF_OPCODE_LIST(GINT_X_INFO)
+GINT_VEC_OPCODE_LIST(GINT_X_INFO)
 #undef GINT_X_INFO
 
 template <int OP, int SP, int P, int K_ = 1> __host__ __device__ constexpr bool op_valid();
@@ -658,6 +659,9 @@ template <int OP, int SP, int P, int K_> __host__ __device__ constexpr bool op_v
          * program pays for. The one-tile 12-slot kernels (direct, indirect, checked) keep them: they also run the streams of
          * programs with smaller pools, in which DupBroadcastW has become Bcast_k. */
         if (OP >= OP_Bcast_0 && OP <= OP_Bcast_3 && P * K_ >= 24) return false;
+#ifndef GINT_VEC
+        if (OP == OP_RemapVN) return false;
+#endif
 #ifdef GINT_RF
         /* virtual registers in shared memory: the pool is the operand stack alone, registers are reached through RLoad / RStore */
         if (OP >= OP_FLoadReg0 && OP <= OP_FStoreReg7) return false;
@@ -733,7 +737,11 @@ __device__ __forceinline__ void tile_issue(const TileInfo *ti, uint32_t operand,
     const int lane = cx.lane;
     char *base = reinterpret_cast<char *>(ti->ptr[arg]);
     const int2 s1 = ti->s1[arg];
+#ifdef GINT_VEC
+    const uint32_t dst = slot - (uint32_t)(lane * 12) + (uint32_t)(KI * 512);   // (`slot` carries 16 * lane here)
+#else
     const uint32_t dst = slot + (uint32_t)(KI * 512);
+#endif
     const int e = lane + off;
     if (s1.y == 1 && off + 128 <= s1.x) {  // full unit-stride tile
         const char *p0 = base + (long long)off * 4;
@@ -769,14 +777,35 @@ template <int K, int KI>
 __device__ __forceinline__ void tile_issue_fast(const TileInfo *ti, uint32_t operand, const Ctx &cx, uint32_t slot)
 {
     const char *p = fast_tile_address(ti, operand) + cx.lane * 16;
+#ifdef GINT_VEC
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(slot + (uint32_t)(KI * 512)), "l"(p) : "memory");
+#else
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(slot + (uint32_t)(KI * 512 + cx.lane * 12)), "l"(p) : "memory");
+#endif
 }
 template <int K, int SLOT, int KI> __device__ __forceinline__ void take_hidden(uint32_t slot)
 {
     const uint32_t src = slot + (uint32_t)(KI * 512);
+#ifdef GINT_VEC
+    asm volatile("ld.shared.v2.b64 {%%gs%0, %%gs%1}, [%2];" ::"n"(gs<K>(SLOT, KI, 0)), "n"(gs<K>(SLOT, KI, 1)), "r"(src) : "memory");
+    return;
+#endif
     asm volatile("{\n\t.reg .b32 t<4>;\n\t"
                  "ld.shared.b32 t0, [%2];\n\tld.shared.b32 t1, [%2+128];\n\tld.shared.b32 t2, [%2+256];\n\tld.shared.b32 t3, [%2+384];\n\t"
                  "mov.b64 %%gs%0, {t0, t1};\n\tmov.b64 %%gs%1, {t2, t3};\n\t}" ::"n"(gs<K>(SLOT, KI, 0)), "n"(gs<K>(SLOT, KI, 1)), "r"(src) : "memory");
+}
+
+/* four values of a tile in element order at `at` (+ 128 w): the natural layout's read */
+template <int K, int SLOT, int KI> __device__ __forceinline__ void take_natural(uint32_t at)
+{
+    asm volatile("{\n\t.reg .b32 t<4>;\n\t"
+                 "ld.shared.b32 t0, [%2];\n\tld.shared.b32 t1, [%2+128];\n\tld.shared.b32 t2, [%2+256];\n\tld.shared.b32 t3, [%2+384];\n\t"
+                 "mov.b64 %%gs%0, {t0, t1};\n\tmov.b64 %%gs%1, {t2, t3};\n\t}" ::"n"(gs<K>(SLOT, KI, 0)), "n"(gs<K>(SLOT, KI, 1)), "r"(at) : "memory");
+}
+
+template <int K, int SLOT, int KI> __device__ __forceinline__ void put_vector(uint32_t at)
+{
+    asm volatile("st.shared.v2.b64 [%2], {%%gs%0, %%gs%1};" ::"n"(gs<K>(SLOT, KI, 0)), "n"(gs<K>(SLOT, KI, 1)), "r"(at) : "memory");
 }
 
 /* Staged row blocks (StageRows / LoadStagedRows). Row m of the block (lane m's row) has q = 2^lq chunks of 16 bytes; chunk r
@@ -973,11 +1002,25 @@ __device__ __forceinline__ void exec_tile(const uint32_t operand, const Ctx &cx)
     }
     /* ---- global memory (load_store.py) ---- */
     else if constexpr (OP == OP_LoadGlobal1DF32Fast) {  // full unit-stride tile (proved by the host): elem = off + lane + 32 w
+#ifdef GINT_VEC
+        {   // vector layout: lane l holds elements 4l..4l+3 of the tile
+            const char *pv = fast_tile_address(cx.tiles + KI, operand) + cx.lane * 16;
+            asm volatile("ld.global.v2.b64 {%%gs%0, %%gs%1}, [%2];" ::"n"(LO(SP)), "n"(HI(SP)), "l"(pv) : "memory");
+            return;
+        }
+#endif
         const char *p = fast_tile_address(cx.tiles + KI, operand) + cx.lane * 4;
         asm volatile("{\n\t.reg .b32 t<4>;\n\t"
                      "ld.global.b32 t0, [%2];\n\tld.global.b32 t1, [%2+128];\n\tld.global.b32 t2, [%2+256];\n\tld.global.b32 t3, [%2+384];\n\t"
                      "mov.b64 %%gs%0, {t0, t1};\n\tmov.b64 %%gs%1, {t2, t3};\n\t}" ::"n"(LO(SP)), "n"(HI(SP)), "l"(p) : "memory");
     } else if constexpr (OP == OP_StoreGlobal1DF32Fast) {
+#ifdef GINT_VEC
+        {
+            char *pv = fast_tile_address(cx.tiles + KI, operand) + cx.lane * 16;
+            asm volatile("st.global.v2.b64 [%2], {%%gs%0, %%gs%1};" ::"n"(LO(T)), "n"(HI(T)), "l"(pv) : "memory");
+            return;
+        }
+#endif
         char *p = fast_tile_address(cx.tiles + KI, operand) + cx.lane * 4;
         asm volatile("{\n\t.reg .b32 t<4>;\n\t"
                      "mov.b64 {t0, t1}, %%gs%0;\n\tmov.b64 {t2, t3}, %%gs%1;\n\t"
@@ -1043,6 +1086,17 @@ __device__ __forceinline__ void exec_all(const uint32_t operand, const Ctx &cx, 
         };
         (one(KI), ...);
         asm volatile("cp.async.commit_group;" ::: "memory");
+    } else if constexpr (OP == OP_RemapVN) {
+        /* top of the stack from the vector layout (lane l: elements 4l..4l+3 of the tile) to the natural one (lane l: elements
+         * l, l+32, l+64, l+96): through the warp's 512-byte-per-tile exchange area (aux_bytes; after the staged row blocks) */
+        const uint32_t warp = threadIdx.x >> 5;
+        const uint32_t area = cx_after_tiles<K>(cx, warp) + (uint32_t)(kWarpsPerBlock * K) * (cx.args->ring_bytes + cx.args->row_area_bytes) +
+                              warp * (uint32_t)(K * 512);
+        constexpr int T = SP - 1;
+        (put_vector<K, T, KI>(area + (uint32_t)(KI * 512 + cx.lane * 16)), ...);
+        __syncwarp();
+        (take_natural<K, T, KI>(area + (uint32_t)(KI * 512 + cx.lane * 4)), ...);
+        __syncwarp();
     } else if constexpr (OP == OP_LoadStagedRows) {
         /* operand: log2 chunks per row (bits 0..1), which chunk of the lane's row (bits 2..3), area offset (bits 8..23) */
         const uint32_t lq = operand & 3u, part = (operand >> 2) & 3u, area = (operand >> 8) & 0xFFFFu;
@@ -1270,6 +1324,9 @@ __device__ __forceinline__ void interpret(const uint2 *code, uint32_t n_entries,
             GINT_RF_OPCODE_LIST(GINT_X_CASES)
             GINT_RF_FUSED_LIST(GINT_X_FCASES)
 #endif
+#ifdef GINT_VEC
+            GINT_VEC_OPCODE_LIST(GINT_X_CASES)
+#endif
 #undef GINT_X_FCASES
 #undef GINT_X_CASES
 #undef GINT_CASE_SP
@@ -1377,7 +1434,11 @@ __device__ __forceinline__ void geval_direct_body(const LaunchArgs &a)
     cx.args = &a;
     if constexpr (!lean_ctx<P, K>()) {   // after the tile descriptors: the ring of early-issued loads (ring_bytes per tile), then the staged row blocks
         unsigned char *after = reinterpret_cast<unsigned char *>(tiles_s + kWarpsPerBlock * K);
+#ifdef GINT_VEC
+        cx.hidden = (uint32_t)__cvta_generic_to_shared(after + (size_t)(warp * K) * a.ring_bytes + lane * 16);   // lane l owns elements 4l..4l+3
+#else
         cx.hidden = (uint32_t)__cvta_generic_to_shared(after + (size_t)(warp * K) * a.ring_bytes + lane * 4);
+#endif
         cx.rows = (uint32_t)__cvta_generic_to_shared(after + (size_t)(kWarpsPerBlock * K) * a.ring_bytes + (size_t)(warp * K) * a.row_area_bytes);
         cx.rows_stride = a.row_area_bytes;
         cx.ring_mask = (uint32_t)K * a.ring_bytes - 1u;
@@ -1464,6 +1525,12 @@ __device__ __forceinline__ void geval_indirect_body(const IndirectArgs &a)
 #define GINT_DEFINE_RF_KERNEL(P, K)                                                                             \
     extern "C" __global__ void __launch_bounds__(gint::kThreadsPerBlock, GINT_MIN_BLOCKS(P, K))                  \
         gint_geval_rf_##P##_##K(const __grid_constant__ gint::LaunchArgs a)                                      \
+    {                                                                                                           \
+        gint::geval_direct_body<P, K>(a);                                                                       \
+    }
+#define GINT_DEFINE_VEC_KERNEL(P, K)                                                                            \
+    extern "C" __global__ void __launch_bounds__(gint::kThreadsPerBlock, GINT_MIN_BLOCKS(P, K))                  \
+        gint_geval_vec_##P##_##K(const __grid_constant__ gint::LaunchArgs a)                                     \
     {                                                                                                           \
         gint::geval_direct_body<P, K>(a);                                                                       \
     }

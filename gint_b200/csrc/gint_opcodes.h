@@ -176,10 +176,19 @@
 #define GINT_RF_OPCODE_LIST(X) X(RLoad, 150, 0, 1) X(RStore, 151, 1, -1) X(RLoadP, 152, 0, 1) X(RLoadS, 153, 0, 1)
 /* opcodes a kernel dispatches on: the 106 of the format, the 16 internal ones and the 28 fused handlers of gint_fused.h; in
  * the register-file kernels also RLoad / RStore and the register-operand fused handlers */
+/* the vector-layout kernels' own opcode (GINT_VEC, see gint_interp.cuh): in those kernels a 1-D tile that the host proved
+ * full, unit-stride and aligned lives in the pool with lane l holding elements 4l..4l+3 (one 16-byte access per lane) instead of
+ * elements l, l+32, l+64, l+96. Element-wise work does not care; an instruction that looks across lanes or width values does,
+ * and the host puts this in front of it (gint_capi.cu: vec_transform):
+ *   RemapVN   rearrange the top of the stack from the vector layout into the natural one (through shared memory) */
+#define GINT_VEC_OPCODE_LIST(X) X(RemapVN, 180, 1, 0)
 #define GINT_N_DISPATCH_PLAIN 150
 #define GINT_N_DISPATCH_RF 176
-#ifdef GINT_RF
+#define GINT_N_DISPATCH_VEC 181
+#if defined(GINT_RF)
 #define GINT_N_DISPATCH GINT_N_DISPATCH_RF
+#elif defined(GINT_VEC)
+#define GINT_N_DISPATCH GINT_N_DISPATCH_VEC
 #else
 #define GINT_N_DISPATCH GINT_N_DISPATCH_PLAIN
 #endif
@@ -189,6 +198,7 @@ enum gint_opcode {
     GINT_OPCODE_LIST(GINT_X_ENUM)
     GINT_INTERNAL_OPCODE_LIST(GINT_X_ENUM)
     GINT_RF_OPCODE_LIST(GINT_X_ENUM)
+    GINT_VEC_OPCODE_LIST(GINT_X_ENUM)
 #undef GINT_X_ENUM
 };
 

@@ -14,6 +14,7 @@ extern "C" {
 
 #define GINT_DIRECT_VARIANTS(X) X(4, 1) X(4, 2) X(4, 4) X(7, 1) X(7, 2) X(12, 1) X(12, 2)
 #define GINT_RF_VARIANTS(X) X(7, 2)       /* virtual registers in shared memory (GINT_RF): the pool is the operand stack alone */
+#define GINT_VEC_VARIANTS(X) X(4, 1) X(4, 2)   /* 1-D tiles in the vector layout (GINT_VEC): lane l holds elements 4l..4l+3 */
 #define GINT_INDIRECT_VARIANTS(X) X(12)
 #define GINT_CHECKED_VARIANTS(X) X(12)
 
@@ -26,6 +27,11 @@ GINT_DIRECT_VARIANTS(GINT_X_DECL)
     extern const unsigned char gint_cubin_rf_##P##_##K[];     \
     extern const unsigned char gint_cubin_rf_##P##_##K##_end[];
 GINT_RF_VARIANTS(GINT_X_DECL)
+#undef GINT_X_DECL
+#define GINT_X_DECL(P, K)                                     \
+    extern const unsigned char gint_cubin_vec_##P##_##K[];     \
+    extern const unsigned char gint_cubin_vec_##P##_##K##_end[];
+GINT_VEC_VARIANTS(GINT_X_DECL)
 #undef GINT_X_DECL
 #define GINT_X_DECL(P)                                     \
     extern const unsigned char gint_cubin_indirect_##P[];   \

@@ -43,8 +43,8 @@ class BytecodeStatsC(ctypes.Structure):
 
 class LaunchInfoC(ctypes.Structure):
     _fields_ = [(n, c_int32) for n in ("pool_size", "tiles_per_warp", "warps_per_block", "grid_blocks", "smem_bytes",
-                                       "regs_per_thread", "blocks_per_sm", "num_sms", "early_loads", "registers_in_smem")] + \
-               [("reserved", c_int32 * 6)]
+                                       "regs_per_thread", "blocks_per_sm", "num_sms", "early_loads", "registers_in_smem", "vector_layout")] + \
+               [("reserved", c_int32 * 5)]
 
 
 GINT_OK = 0

@@ -46,6 +46,7 @@ def derive() -> dict:
     fused_first = _header_int("GINT_FUSED_FIRST", "gint_fused.h")
     n_dispatch = _header_int("GINT_N_DISPATCH_PLAIN", "gint_opcodes.h")
     n_dispatch_rf = _header_int("GINT_N_DISPATCH_RF", "gint_opcodes.h")     # the register-file kernels dispatch on more opcodes
+    n_dispatch_vec = _header_int("GINT_N_DISPATCH_VEC", "gint_opcodes.h")   # and so do the vector-layout kernels
     buf = (ctypes.c_int32 * (256 * 10))()
     n_fused = lib.gint_debug_fused_table(buf, 256)
     assert n_fused > 0
@@ -57,6 +58,7 @@ def derive() -> dict:
 
     keys: set[tuple[int, int]] = set()       # handlers of the ordinary streams
     rf_keys: set[tuple[int, int]] = set()    # handlers of the streams with the virtual registers in shared memory (their own kernels)
+    vec_keys: set[tuple[int, int]] = set()   # handlers of the vector-layout streams (their own kernels)
     for name in load_records():
         if name == "execute_everything":      # refused by the library (deeper than any kernel's stack)
             continue
@@ -66,10 +68,10 @@ def derive() -> dict:
         fill_tensor_info(ti, prog.tensor_infos)
         cap = code.size + 64
         ops, operands = (ctypes.c_int32 * cap)(), (ctypes.c_uint32 * cap)()
-        for early in (0, 1, 2, 3):            # bit 0: early-issue pass; bit 1: the stream with the registers in shared memory
+        for early in (0, 1, 2, 3, 5):         # bit 0: early-issue pass; bit 1: registers in shared memory; bit 2: vector layout
             n = lib.gint_debug_transform(code.ctypes.data_as(ctypes.POINTER(ctypes.c_int32)), int(code.size), ctypes.byref(ti),
                                          len(prog.tensor_infos), early, 1, ops, operands, cap)
-            if n == 0 and early & 2:          # the program does not qualify for that stream
+            if n == 0 and early & 6:          # the program does not qualify for that stream
                 continue
             assert n > 0, (name, n)
             depth = 0
@@ -77,31 +79,36 @@ def derive() -> dict:
                 op = ops[i]
                 if op < 0:                    # absorbed into the fused handler before it
                     continue
-                (rf_keys if early & 2 else keys).add((depth, op))
+                (rf_keys if early & 2 else vec_keys if early & 4 else keys).add((depth, op))
                 depth += net_of(op)
     return {"n_dispatch": n_dispatch, "n_dispatch_rf": n_dispatch_rf, "fused_first": fused_first,
-            "keys": sorted([d, o] for d, o in keys), "rf_keys": sorted([d, o] for d, o in rf_keys)}
+            "n_dispatch_vec": n_dispatch_vec, "keys": sorted([d, o] for d, o in keys), "rf_keys": sorted([d, o] for d, o in rf_keys),
+            "vec_keys": sorted([d, o] for d, o in vec_keys)}
 
 
-def load(rf: bool = False) -> set[tuple[int, int]]:
+def load(family: str = "plain") -> set[tuple[int, int]]:
     """The committed list as a set of (depth, opcode); empty if the file is absent or was made for another numbering.
-    ``rf``: the list for the kernels that keep the virtual registers in shared memory."""
+    ``family``: "plain", "rf" (the kernels that keep the virtual registers in shared memory) or "vec" (vector layout)."""
+    if family not in ("plain", "rf", "vec"):
+        raise ValueError(f"unknown kernel family {family!r}")
     try:
         with open(TABLE) as f:
             t = json.load(f)
         if t["n_dispatch"] != _header_int("GINT_N_DISPATCH_PLAIN", "gint_opcodes.h") or t["fused_first"] != _header_int("GINT_FUSED_FIRST", "gint_fused.h") or \
-                t["n_dispatch_rf"] != _header_int("GINT_N_DISPATCH_RF", "gint_opcodes.h"):
+                t["n_dispatch_rf"] != _header_int("GINT_N_DISPATCH_RF", "gint_opcodes.h") or \
+                t["n_dispatch_vec"] != _header_int("GINT_N_DISPATCH_VEC", "gint_opcodes.h"):
             return set()
-        return {(d, o) for d, o in t["rf_keys" if rf else "keys"]}
+        keys = t[{"plain": "keys", "rf": "rf_keys", "vec": "vec_keys"}[family]]
     except (OSError, KeyError, ValueError):
         return set()
+    return {(d, o) for d, o in keys}
 
 
 def main() -> None:
     t = derive()
     with open(TABLE, "w") as f:
         json.dump(t, f)
-    print(f"{TABLE}: {len(t['keys'])} handlers, {len(t['rf_keys'])} for the register-file kernels")
+    print(f"{TABLE}: {len(t['keys'])} handlers, {len(t['rf_keys'])} for the register-file kernels, {len(t['vec_keys'])} for the vector-layout kernels")
 
 
 if __name__ == "__main__":

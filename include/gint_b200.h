@@ -77,7 +77,8 @@ typedef struct gint_launch_info {
     int32_t num_sms;
     int32_t early_loads;      /* tile loads per logical program that are started ahead of their use (early issue) */
     int32_t registers_in_smem; /* virtual registers kept in shared memory (the pool then holds the operand stack alone); 0: in the pool */
-    int32_t reserved[6];
+    int32_t vector_layout;    /* 1: full 1-D tiles live in the pool with lane l holding elements 4l..4l+3 (16-byte accesses) */
+    int32_t reserved[5];
 } gint_launch_info;
 
 /* What a checked launch (gint_execute_checked) found; all zero = nothing. The FIRST event is described, `count` counts all. */
@@ -125,8 +126,9 @@ int gint_predecode(const int32_t *code, int n_words, uint32_t *out_keys, int max
  * the fused handler before it. With early_issue != 0 the descriptors in `ti` also decide which 1-D accesses become their
  * "fast" forms (provably full, aligned tiles). early_issue is a bit set: 1 = the early-issue pass, 2 = the stream for the
  * kernels that keep the virtual registers in shared memory (FLoadRegN / FStoreRegN become RLoad / RStore with the register in
- * the operand; returns 0 if the program does not qualify for them). Returns the number of instructions (including the Halt)
- * or < 0. */
+ * the operand; returns 0 if the program does not qualify for them), 4 = the stream for the vector-layout kernels (with 1; RemapVN
+ * inserted where a value must be in the natural layout; 0 if the program does not qualify). Returns the number of instructions
+ * (including the Halt) or < 0. */
 int gint_debug_transform(const int32_t *code, int n_words, const gint_tensor_info *ti, int n_tensors, int early_issue, int fuse,
                          int32_t *out_ops, uint32_t *out_operands, int max_insns);
 
@@ -273,7 +275,10 @@ int gint_execute_indirect_static(gint_ctx *ctx, const uint64_t *handles, int n_p
  * sequences by fused handlers, default; applies to programs created afterwards), "prefetch" (L2 footprint prefetch,
  * default 0), "max_blocks" (cap on the persistent grid, 0 = none), "lower" (1 = lane indices of DupBroadcastW move into the
  * opcode, default; programs created afterwards), "register_file" (1 = programs that need the 12-slot pool only for their
- * virtual registers keep those in shared memory and run on a kernel whose pool is the operand stack alone, default). */
+ * virtual registers keep those in shared memory and run on a kernel whose pool is the operand stack alone, default),
+ * "vector_layout" (1 = programs created from now on whose full 1-D tiles can live in the pool as four consecutive elements
+ * per lane run on the kernels that access them with one 16-byte access per lane; default 0: no measurable gain on the
+ * benchmark programs). */
 int gint_set_option(gint_ctx *ctx, const char *name, int value);
 
 #ifdef __cplusplus

@@ -297,6 +297,70 @@ def test_registers_in_shared_memory_give_the_bits_of_the_pool(name, leading):
         assert bits_equal(rf.tensors[role], pool.tensors[role]), mismatch_report(rf.tensors[role], pool.tensors[role])
 
 
+def test_vector_layout_gives_the_bits_of_the_natural_layout():
+    """The conductor graph's fused program on the vector-layout kernel (an option: its full 1-D tiles live in the pool as four
+    consecutive elements per lane, one rearrangement in front of the warp reduction) and on the ordinary kernel."""
+    from gint_b200.workloads import make_workload
+    ex = get_executor()
+    outs = []
+    try:
+        for on in (1, 0):
+            ex.set_option("vector_layout", on)
+            wl = make_workload("graph", 8192, 1024, device="cuda")
+            st = wl.steps[0]
+            info = ex.launch_info(st.program, [wl.tensors[r] for r in st.roles], st.grid_dim)
+            assert info["vector_layout"] == on and info["pool_size"] == 4
+            assert ex.launch_info(wl.steps[1].program, [wl.tensors[r] for r in wl.steps[1].roles], wl.steps[1].grid_dim)["vector_layout"] == 0
+            wl.run(ex, torch.cuda.current_stream().cuda_stream)
+            torch.cuda.synchronize()
+            outs.append({r: wl.tensors[r].clone() for r in wl.outputs})
+    finally:
+        ex.set_option("vector_layout", 0)
+    for r in outs[0]:
+        assert bits_equal(outs[0][r], outs[1][r]), mismatch_report(outs[0][r], outs[1][r])
+
+
+def test_vector_layout_with_a_reduced_scale_matches_the_oracle():
+    """sum over a 2048-element row (lanes, then width values), then every tile of the row scaled by that sum: the scale is uniform, so
+    the tiles stay in the vector layout; one rearrangement in front of the reduction. Bit-exact against the CPU oracle."""
+    # (-(sum * x + 0.5) * 3, so that the program is not one of those that run one tile per warp: they keep the natural layout)
+    import numpy as np
+    from gint_b200.host import frontend as fe
+    from gint_b200.host.executor import BaseExecutableProgram, ProgramData, ProgramTensorInfo
+    from oracle import oracle
+    n_tiles, rows = 16, 300
+
+    class RowScale(BaseExecutableProgram):
+        def get_program(self, x, y):
+            bc = [[fe.LoadGlobal1DF32, 0]]
+            for i in range(1, n_tiles):
+                bc += [[fe.LoadGlobal1DF32, 16 * 128 * i], [fe.FAdd, 0]]
+            bc += [[fe.WarpAllReduceSum, 0], [fe.Dup, 0], [fe.FPermW, 0x01000302], [fe.FAdd, 0], [fe.Dup, 0], [fe.FPermW, 0x02030001], [fe.FAdd, 0],
+                   [fe.FStoreReg0, 0]]
+            for i in range(n_tiles):
+                bc += [[fe.LoadGlobal1DF32, 16 * 128 * i], [fe.FLoadReg0, 0], [fe.FMul, 0], [fe.FAddImm, 0x3F000000], [fe.FMulImm, 0x40400000], [fe.FNeg, 0],
+                       [fe.StoreGlobal1DF32, 16 * 128 * i + 1]]      # (enough arithmetic per tile for two tiles per warp)
+            bc += [[0, 0]]
+            infos = [ProgramTensorInfo(4, [128 * n_tiles], [rows], [128 * n_tiles, 1], [1, 0], [1, 1], [0, 0]) for _ in (x, y)]
+            return ProgramData(np.array(bc, dtype=np.int32), infos)
+
+    prog = RowScale()
+    x = torch.randn(rows, 128 * n_tiles, generator=torch.Generator().manual_seed(5))
+    want = [x.clone(), torch.zeros_like(x)]
+    pd = prog.get_program(*C.to_interfaces(want))
+    oracle.execute(pd.program, [vars(t) for t in pd.input_infos], want, rows)
+    ex = get_executor()
+    xd, yd = x.cuda(), torch.zeros_like(x).cuda()
+    ex.set_option("vector_layout", 1)       # (off by default; applies to programs created from here on)
+    try:
+        assert ex.launch_info(prog, [xd, yd], rows)["vector_layout"] == 1
+        prog(xd, yd, grid_dim=rows)
+        torch.cuda.synchronize()
+    finally:
+        ex.set_option("vector_layout", 0)
+    assert bits_equal(yd.cpu(), want[1]), mismatch_report(yd.cpu(), want[1])
+
+
 def test_register_pressure_case_runs_on_the_register_file_kernel():
     import cases as C
     ex = get_executor()

@@ -50,12 +50,12 @@ def test_c_header_table_matches_python():
     import re
     rows = re.findall(r"X\((\w+), (\d+), (-?\d+), (-?\d+)\)", open(path).read())
     internal = [r for r in rows if int(r[1]) >= opcodes.N_OPCODES]   # the kernels' internal opcodes sit above the format's 106
-    RF = ("RLoad", "RStore", "RLoadP", "RLoadS")                     # ... those of the register-file kernels after the fused handlers
+    RF = ("RLoad", "RStore", "RLoadP", "RLoadS", "RemapVN")          # ... those of the register-file and vector-layout kernels after the fused handlers
     assert all(r[0].startswith(("Pf", "Bcast_")) or r[0].endswith("Fast") or r[0].endswith("Rows") or r[0] in RF for r in internal)
     # numbered consecutively after the format's
     plain = sorted(int(r[1]) for r in internal if r[0] not in RF)
     assert plain == list(range(opcodes.N_OPCODES, opcodes.N_OPCODES + len(plain)))
-    assert {r[0]: int(r[1]) for r in internal if r[0] in RF} == {"RLoad": 150, "RStore": 151, "RLoadP": 152, "RLoadS": 153}
+    assert {r[0]: int(r[1]) for r in internal if r[0] in RF} == {"RLoad": 150, "RStore": 151, "RLoadP": 152, "RLoadS": 153, "RemapVN": 180}
     rows = [r for r in rows if int(r[1]) < opcodes.N_OPCODES]
     assert len(rows) == opcodes.N_OPCODES
     for name, num, md, net in rows:

@@ -16,6 +16,7 @@ from gint_b200.programs import load_records, recorded
 PF_TAKE, PF_ISSUE_1D, PF_TAKE_ISSUE_1D, PF_SKIP, LOAD_1D_FAST, STORE_1D_FAST, PF_ISSUE_1D_FAST, PF_TAKE_ISSUE_1D_FAST, STAGE_ROWS, LOAD_STAGED_ROWS = range(106, 116)
 BCAST, LOAD_2DW_FAST, STORE_2DW_FAST = 116, 120, 121   # Bcast_0..3
 RLOAD, RSTORE, RLOADP, RLOADS = 150, 151, 152, 153     # virtual registers in shared memory: operand = 512 * register number (+ selectors)
+REMAP_VN = 180                                         # vector layout -> natural layout (vector-layout kernels)
 
 
 def fused_table():
@@ -84,6 +85,7 @@ def undo(prog, table):
             assert op != -1
             flat.append((op, operand))
             i += 1
+    flat = [(op, operand) for op, operand in flat if op != REMAP_VN]     # changes where values sit, not what they are
     # 1b. DupBroadcastW with a built-in lane index -> the format's instruction with an operand
     flat = [(O.DupBroadcastW, op - BCAST) if BCAST <= op < BCAST + 4 else (op, operand) for op, operand in flat]
     # 1c. registers in shared memory -> the format's per-register opcodes; permutations and shuffles folded into a register load
@@ -249,6 +251,73 @@ def test_register_file_needs_an_unobservable_overlap():
     # stack deeper than the 7 slots of the register-file kernels
     deep = [one, [fe.FStoreReg7, 0]] + [one] * 8 + [[fe.Pop, 0]] * 7 + tail
     assert not _rf_qualifies(deep)
+
+
+def _vec_stream(bytecode, infos):
+    """The stream for the vector-layout kernels (early-issue pass + layout analysis, no fusion), or [] if the program does not qualify."""
+    lib = capi.load_library()
+    code = np.ascontiguousarray(np.asarray(bytecode, dtype=np.int32).reshape(-1))
+    ti = capi.HTensorInfo()
+    fill_tensor_info(ti, infos)
+    ops, operands = (ctypes.c_int32 * 4096)(), (ctypes.c_uint32 * 4096)()
+    n = lib.gint_debug_transform(code.ctypes.data_as(ctypes.POINTER(ctypes.c_int32)), code.size, ctypes.byref(ti), len(infos), 5, 0, ops, operands, 4096)
+    assert n >= 0, n
+    return [(ops[i], operands[i]) for i in range(n)]
+
+
+def test_vector_layout_stream_of_the_row_programs():
+    """RMSNorm and the conductor graph's fused program: every tile access is a full aligned 1-D tile, everything between them is
+    element-wise, and the one place that looks across lanes -- the warp reduction of the sum of squares -- gets ONE RemapVN in front
+    of it. What the reduction leaves is provably the same in all lanes and width values (after WarpAllReduceSum and the two
+    FPermW / FAdd steps), so the second pass may multiply vector-layout tiles with it. The stream undoes to the same program."""
+    table = fused_table()
+    for name in ("rmsnorm_r16384_n4096", "graph_fused_r65536_n1024", "graph_fused_r96_n1024"):
+        prog = recorded(name)
+        got = _vec_stream(prog.bytecode, prog.tensor_infos)
+        ops = [op for op, _ in got]
+        assert ops.count(REMAP_VN) == 1 and ops[ops.index(REMAP_VN) + 1] == O.WarpAllReduceSum, name
+        assert zero_operands(undo(got, table)) == zero_operands(fold_repeated_loads(normalised(prog.bytecode))), name
+    # the row-sum program and short rows would qualify, but a handful of loads does not pay for the rearrangement; ragged rows have
+    # masked tiles
+    for name in ("graph_rowsum_r65536_n1024", "rmsnorm_r7_n256", "rmsnorm_r5_n200", "add_n1048576", "bmm4x4_b4194304"):
+        prog = recorded(name)
+        assert _vec_stream(prog.bytecode, prog.tensor_infos) == [], name
+
+
+def test_vector_layout_analysis_refuses_what_it_cannot_prove():
+    from gint_b200.host import frontend as fe
+    n_tiles = 16
+    infos = [fe.ProgramTensorInfo(4, [], [], [128 * n_tiles, 1], [1, 0], [1, 1], [0, 0]) for _ in range(2)]
+
+    def program(per_tile):
+        bc = []
+        for i in range(n_tiles):
+            bc += [[fe.LoadGlobal1DF32, 16 * 128 * i + 0]] + per_tile + [[fe.StoreGlobal1DF32, 16 * 128 * i + 1]]
+        return np.array(bc + [[0, 0]], dtype=np.int32)
+
+    def count(per_tile):
+        return [op for op, _ in _vec_stream(program(per_tile), infos)].count(REMAP_VN)
+
+    assert _vec_stream(program([[fe.FMulImm, 0x40000000]]), infos) != [] and count([[fe.FMulImm, 0x40000000]]) == 0      # element-wise: no rearrangement
+    assert _vec_stream(program([[fe.LoadImm, 0x3F800000], [fe.FAdd, 0]]), infos) != []                                   # a uniform operand mixes with anything
+    # a value that differs per width value (here: 1, 2, 3, 4) means other elements in the two layouts
+    assert _vec_stream(program([[fe.LoadImm4F, 0x04030201], [fe.FMul, 0]]), infos) == []
+    # a lane permutation of tile data needs the natural layout, and the fast store behind it the vector layout again
+    assert _vec_stream(program([[fe.FPermW, 0x00010203]]), infos) == []
+    # ... but a permutation that feeds a reduction is fine: one rearrangement per tile, which is too many to pay off
+    assert _vec_stream(program([[fe.Dup, 0], [fe.FPermW, 0x00010203], [fe.WarpAllReduceSum, 0], [fe.Pop, 0]]), infos) == []
+    # a width-uniform value made from a reduction: sum over lanes, then over the four width values, then used as a scale
+    reduce_all = [[fe.Dup, 0], [fe.WarpAllReduceSum, 0], [fe.Dup, 0], [fe.FPermW, 0x01000302], [fe.FAdd, 0], [fe.Dup, 0], [fe.FPermW, 0x02030001], [fe.FAdd, 0], [fe.FMul, 0]]
+    bc = [[fe.LoadGlobal1DF32, 0]] + reduce_all[1:-1] + [[fe.FStoreReg0, 0]]
+    for i in range(n_tiles):
+        bc += [[fe.LoadGlobal1DF32, 16 * 128 * i + 0], [fe.FLoadReg0, 0], [fe.FMul, 0], [fe.StoreGlobal1DF32, 16 * 128 * i + 1]]
+    got = [op for op, _ in _vec_stream(np.array(bc + [[0, 0]], dtype=np.int32), infos)]
+    assert got.count(REMAP_VN) == 1
+    # the same with only ONE of the two width steps: the scale still differs between width values, the program keeps its layout
+    half = [[fe.LoadGlobal1DF32, 0], [fe.WarpAllReduceSum, 0], [fe.Dup, 0], [fe.FPermW, 0x01000302], [fe.FAdd, 0], [fe.FStoreReg0, 0]]
+    for i in range(n_tiles):
+        half += [[fe.LoadGlobal1DF32, 16 * 128 * i + 0], [fe.FLoadReg0, 0], [fe.FMul, 0], [fe.StoreGlobal1DF32, 16 * 128 * i + 1]]
+    assert _vec_stream(np.array(half + [[0, 0]], dtype=np.int32), infos) == []
 
 
 def test_named_programs_get_the_expected_shape():
